@@ -1,0 +1,204 @@
+/* q36_moe.h -- C ABI of the B200 (sm_100a) MXFP4-weight / E4M3-activation
+ * mixture-of-experts expert path.
+ *
+ * The q36 engine has no plugin registry: its MoE path is a fixed sequence of
+ * kernel launches inside two static functions, moe_ffn (T = 1 decode,
+ * q36_engine.cu:1592-1654) and pf_moe_block (batched / prefill,
+ * q36_engine.cu:3423-3472), over weights laid out by upload()
+ * (q36_engine.cu:202-228).  Each entry point below replaces one of those
+ * launches (or one whole function) and keeps the conventions of the engine's
+ * existing extern "C" launchers (q36_cuda.cu:226-292): raw device pointers,
+ * int dimensions, no structs across the boundary, launch-only (no host
+ * synchronisation, no allocation, capturable in a CUDA graph).  Differences:
+ * every call takes an explicit stream (a cudaStream_t passed as void*; NULL
+ * = the legacy default stream) and returns a status instead of exiting.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless the name starts with "host_".
+ *   - Weights use the engine's "mxfp4-split" layout (`dw.elayout == 2`):
+ *     per resident expert [codes: M*K/2 bytes, row-major, GGUF nibble order]
+ *     [scales: M*K/32 E8M0 bytes, row-major]; expert stride M*K*17/32 bytes;
+ *     only experts [se0, se1) are resident and expert `se0` sits at offset 0.
+ *   - Activations are quantised per (row, 32-element block) to E4M3 codes
+ *     plus one UE8M0 scale byte, value = e4m3(code) * 2^(scale-127).
+ *   - "hw order": inside a 32-block, logical element j is stored at position
+ *     2j (j < 16) or 2(j-16)+1 (j >= 16), the element order of the MXFP4 code
+ *     bytes.  Buffers that only this library reads and writes use hw order;
+ *     q36_moe_quant_e4m3 writes logical order like the engine's kernel.
+ *   - Experts outside [se0, se1) contribute zeros (q36_engine.cu:763-766).
+ */
+#ifndef Q36_MOE_H
+#define Q36_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q36_MOE_OK 0
+#define Q36_MOE_EINVAL (-1)   /* bad argument (NULL, size not supported)        */
+#define Q36_MOE_ECUDA (-2)    /* a CUDA call failed: q36_moe_last_cuda_error()  */
+#define Q36_MOE_ENOSPACE (-3) /* workspace smaller than q36_moe_workspace_bytes */
+#define Q36_MOE_EDEVICE (-4)  /* a bounded device-side wait gave up             */
+
+/* Path selection for the grouped expert FFN. */
+#define Q36_MOE_PATH_AUTO 0
+#define Q36_MOE_PATH_GEMV 1   /* streaming SIMT GEMV (decode-sized groups)      */
+#define Q36_MOE_PATH_TC 2     /* tcgen05 block-scaled grouped GEMM (prefill)    */
+
+const char *q36_moe_strerror(int status);
+int q36_moe_last_cuda_error(void);
+/* Library ABI version; bumped when a signature changes. */
+int q36_moe_abi_version(void);
+
+/* ---- weights ------------------------------------------------------------
+ * Replaces the MXFP4 branch of upload() (q36_engine.cu:202-228). */
+
+/* Bytes per expert in the split layout: M*K/2 + M*K/32. */
+uint64_t q36_moe_expert_stride(int M, int K);
+/* Host -> host: GGUF block_mxfp4 array [n_expert][M][K/32] (17 B blocks,
+ * q36.h:114) -> split planes of experts [e0, e1) in host_dst. */
+int q36_moe_repack_mxfp4(const void *host_blocks, int K, int M, int e0, int e1, void *host_dst);
+/* Host -> device: same, then copies into the caller's device buffer dev_dst
+ * of (e1-e0)*q36_moe_expert_stride(M,K) bytes.  Synchronous, like upload(). */
+int q36_moe_upload_mxfp4(const void *host_blocks, int K, int M, int e0, int e1, void *dev_dst);
+/* Device: split planes -> f32 [n_rows][K] (row r of the expert at W).  The
+ * on-device form of q36_deq_row(Q36_GGML_MXFP4, ...) (q36_dequant.cuh:168-181),
+ * used to prove bit-exact dequantisation. */
+int q36_moe_dequant_mxfp4(const void *W, int M, int K, float *out, void *stream);
+
+/* ---- stages -------------------------------------------------------------- */
+
+/* k_router_topk (q36_ops.cuh:397-431): per row softmax statistics over
+ * n_expert (= 256) logits, top-k (k <= 8) on the raw logits in descending
+ * order with ties to the lower index, weights exp(v-m)/s, renormalised to
+ * sum `scale` when renorm != 0.  logits row t starts at t*row_stride. */
+int q36_moe_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt,
+                        float scale, int renorm, int T, int row_stride, void *stream);
+
+/* k_quant_e4m3 (q36_engine.cu:2412-2428): X [T][K] (f32, or bf16 when
+ * x_is_bf16) -> Xq [T][K] E4M3 bytes in logical order, Xs [T][K/32] UE8M0.
+ * The shared exponent is the exact integer ceil(log2(amax/448)). */
+int q36_moe_quant_e4m3(const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int T, int K,
+                       void *stream);
+
+/* k_moe_dispatch (q36_engine.cu:3387-3392) made deterministic: buckets the
+ * n_entries ids (entry i = t*k + s) by expert in ascending-id order.
+ *   ecount[n_expert]   entries per expert (0 outside [se0,se1))
+ *   eoffs[n_expert+1]  exclusive prefix sum of ecount
+ *   elist[n_entries]   packed buckets: elist[eoffs[e] + p] = p-th entry of e
+ *   pos[n_entries]     inverse: row of entry i in elist, -1 if not resident
+ * ws: q36_moe_dispatch_ws_bytes(n_entries, n_expert) bytes of scratch. */
+uint64_t q36_moe_dispatch_ws_bytes(int n_entries, int n_expert);
+int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1,
+                     int *ecount, int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes,
+                     void *stream);
+
+/* Quantises X [T][K] and writes every token's row to the rows of the sorted
+ * space that its entries occupy: for s < k row pos[t*k+s] (skipped when
+ * negative) and, when shared_row0 >= 0, row shared_row0 + t.  Rows are
+ * written in hw order: Xq_rows [R][K], Xs_rows [R][K/32].  Fuses
+ * k_quant_e4m3 with the gather the engine's GEMM does by `elist`
+ * (q36_engine.cu:2475-2483). */
+int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, int shared_row0,
+                          uint8_t *Xq_rows, uint8_t *Xs_rows, int T, int K, void *stream);
+
+/* The grouped expert FFN over rows already sorted by expert:
+ *   for each group g (rows [goffs[g], goffs[g+1])), weights Wg/Wu/Wd of
+ *   expert g:  h = silu(Wg x) * (Wu x); (hq,hs) = quant_e4m3(h);
+ *   y = Wd dequant(hq,hs)
+ * Replaces k_expert_gemv2 + k_silu_mul_slots + k_expert_gemv
+ * (q36_engine.cu:752-783, 744-746, 711-742) for decode-sized groups and
+ * k_gemm_expert_mma x2 + k_silu_mul + k_gemm_expert_tc (:2435-2524,
+ * q36_ops.cuh:65, :2723-2766) for prefill-sized ones.
+ *   Wg, Wu: [n_group] experts of [FF][D]; Wd: [n_group] of [D][FF]
+ *   goffs[n_group+1]: row offsets (device); Xq_rows/Xs_rows: hw order
+ *   Hq_rows [R][FF], Hs_rows [R][FF/32]: quantised SwiGLU output (hw order)
+ *   Y_rows [R][D] f32
+ * path: Q36_MOE_PATH_GEMV or Q36_MOE_PATH_TC.  ws (tensor-core path only):
+ * q36_moe_ffn_ws_bytes(...) bytes; its first 16 bytes are device status
+ * words, see q36_moe_ws_status. */
+uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
+int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group,
+                              const int *goffs, int R_max, const uint8_t *Xq_rows,
+                              const uint8_t *Xs_rows, uint8_t *Hq_rows, uint8_t *Hs_rows,
+                              float *Y_rows, int D, int FF, int path, void *ws, uint64_t ws_bytes,
+                              void *stream);
+
+/* k_moe_combine / k_moe_combine_pf (q36_engine.cu:785-791, 3393-3401):
+ *   out[t][i] = sum_{s<k} wt[t][s] * Y_rows[pos[t*k+s]][i]          (pos >= 0)
+ *             + (SH_rows ? sigmoid(shgate[t*shgate_stride]) * SH_rows[t][i] : 0)
+ * in slot order; shgate == NULL means gate 1.  */
+int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float *wt,
+                    const float *SH_rows, const float *shgate, int shgate_stride, int D, int k,
+                    int T, void *stream);
+
+/* ---- whole layer -----------------------------------------------------------
+ * One call = moe_ffn (q36_engine.cu:1592-1654) or pf_moe_block (:3423-3472)
+ * from the router logits on:
+ *   route -> dispatch -> quantise -> gate/up + SwiGLU -> down -> combine.
+ * logits [T][logit_stride] f32: columns [0,n_expert) are router logits;
+ * column shgate_col (or < 0 for none: gate = 1) is the shared-expert gate
+ * logit (the engine keeps it at column n_expert, q36_engine.cu:1599-1601).
+ * Sg/Su/Sd: the shared expert's split planes, or NULL for no shared expert;
+ * inc_shared == 0 suppresses its term (non-owner ranks, :3398-3400).
+ * Optional outputs idx_out [T][k], wt_out [T][k] (may be NULL). */
+uint64_t q36_moe_workspace_bytes(int T_max, int n_expert, int k, int D, int FF);
+/* Synchronises `stream` and reports whether a tensor-core launch that used
+ * the workspace `ws` gave up on a bounded wait (Q36_MOE_EDEVICE) or not
+ * (Q36_MOE_OK).  The launch-only entry points cannot report this themselves. */
+int q36_moe_ws_status(const void *ws, void *stream);
+int q36_moe_layer(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                  const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
+                  const void *X, int x_is_bf16, const float *logits, int logit_stride,
+                  int shgate_col, float route_scale, int inc_shared, float *out, int *idx_out,
+                  float *wt_out, int T, int path, void *ws, uint64_t ws_bytes, void *stream);
+/* moe_ffn / pf_moe_block by name: the same call with the path fixed. */
+int q36_moe_decode(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                   const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
+                   const void *X, int x_is_bf16, const float *logits, int logit_stride,
+                   int shgate_col, float route_scale, int inc_shared, float *out, int T, void *ws,
+                   uint64_t ws_bytes, void *stream);
+int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                    const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
+                    const void *X, int x_is_bf16, const float *logits, int logit_stride,
+                    int shgate_col, float route_scale, int inc_shared, float *out, int T, void *ws,
+                    uint64_t ws_bytes, void *stream);
+
+/* Host-buffer form of q36_moe_layer: X, logits and out are HOST pointers
+ * (pinned or pageable); the call copies in, runs the layer and copies out on
+ * `stream`, then synchronises it.  dev_io: device staging of
+ * q36_moe_host_io_bytes(T, D, logit_stride, x_is_bf16) bytes. */
+uint64_t q36_moe_host_io_bytes(int T, int D, int logit_stride, int x_is_bf16);
+int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const void *Sg,
+                       const void *Su, const void *Sd, int n_expert, int se0, int se1, int k,
+                       int D, int FF, const void *host_X, int x_is_bf16, const float *host_logits,
+                       int logit_stride, int shgate_col, float route_scale, int inc_shared,
+                       float *host_out, int T, int path, void *dev_io, void *ws, uint64_t ws_bytes,
+                       void *stream);
+
+/* ---- expert-parallel helpers ----------------------------------------------
+ * Row permutation used either side of the all-to-all: dst[i] = src[index[i]]
+ * for rows of row_bytes bytes (row_bytes % 16 == 0); index[i] < 0 zero-fills. */
+int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
+                        void *stream);
+
+/* ---- tensor-core self-check (the role of test_mma_bs.cu:45-175) ----------
+ * Runs 128 x N x K block-scaled tcgen05 tiles on caller data and returns the
+ * f32 accumulators, so that the operand, scale-factor and descriptor mapping
+ * can be proven against a CPU product on silicon.
+ *   A: one 128-row matrix in the split layout: [128][K/2] MXFP4 code bytes
+ *      (GGUF nibble order) followed by [128][K/32] E8M0 scale bytes
+ *   B_q [N][K] E4M3 (hw order), B_s [N][K/32] UE8M0
+ *   D [N][128] f32: D[n][m] = sum_k A[m][k] * B[n][k]
+ * K % 512 == 0, 1 <= N <= 4096.  ws: 512 + q36_moe_ffn_ws_bytes(1,N,128,K)
+ * bytes.  Synchronous; returns Q36_MOE_EDEVICE if a bounded wait gave up. */
+int q36_moe_tc_selftest(const uint8_t *A, const uint8_t *B_q, const uint8_t *B_s, float *D, int N,
+                        int K, void *ws, uint64_t ws_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q36_MOE_H */

@@ -1,0 +1,80 @@
+// Shared device/host helpers for the MXFP4 x E4M3 MoE expert path (sm_100a).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/q36_moe.h"
+
+#define Q36_QK 32  // elements per MXFP4 / activation scale block (q36.h:107)
+
+// Every kernel opens with this so that it may be launched with the
+// programmatic-dependent-launch attribute, as the reference's kernels are
+// (q36_ops.cuh:21-30); without the attribute it is a no-op.
+#define Q36_GDS() cudaGridDependencySynchronize()
+
+namespace q36 {
+
+// Last CUDA error seen by an entry point of this thread (0 = none).
+int &last_cuda_error();
+int check_launch();  // cudaGetLastError() -> status code
+
+// Smallest e2 with amax <= 448 * 2^e2, clamped to [-127,127]; 0 -> -127.
+// Integer form of ceil(log2(amax/448)) (q36_engine.cu:2421); 448 = 1.75 * 2^8.
+__device__ __forceinline__ int e2_of_amax(float amax) {
+    const uint32_t u = __float_as_uint(amax);
+    if (u == 0) return -127;
+    int e2 = (int)(u >> 23) - 135 + ((u & 0x7FFFFFu) > 0x600000u ? 1 : 0);
+    return max(-127, min(127, e2));
+}
+// 2^-e2 as the reference builds it (q36_engine.cu:2423-2425): exponent bits
+// only, so e2 = 127 yields 0.0f.
+__device__ __forceinline__ float inv_scale_of_e2(int e2) { return __uint_as_float((uint32_t)(127 - e2) << 23); }
+// 2^(s-127) for a UE8M0 byte; s = 0 is the denormal 2^-127.
+__device__ __forceinline__ float ue8m0_to_f32(uint32_t s) { return __uint_as_float(s ? (s << 23) : 0x00400000u); }
+
+// f32 -> E4M3, round-to-nearest-even, saturate to +-448 (NaN -> 0x7F).
+__device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
+    return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+// two E4M3 bytes (low byte first) -> two f32
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint16_t p) {
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)p, __NV_E4M3);
+    return __half22float2(*reinterpret_cast<__half2 *>(&h));
+}
+// one packed byte of two E2M1 codes (low nibble first) -> two f32 in the TRUE
+// E2M1 convention {0,.5,1,1.5,2,3,4,6}; the block scale is then 2^(e-127),
+// whose product equals the reference's doubled table times 2^(e-128)
+// (q36_dequant.cuh:80-103).
+__device__ __forceinline__ float2 e2m1x2_to_f32x2(uint32_t byte) {
+    uint32_t h2;
+    asm("{\n\t.reg .b8 b;\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.u8.u16 b, t;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b;\n\t}"
+        : "=r"(h2)
+        : "r"(byte));
+    return __half22float2(*reinterpret_cast<__half2 *>(&h2));
+}
+
+// Position of logical element j (0..31) of a 32-block in the order the MXFP4
+// code bytes imply: code byte i holds element i (low nibble) and element i+16
+// (high nibble) (q36_dequant.cuh:109-112), so consecutive nibbles are elements
+// 0,16,1,17,...  Activations are stored in that same order so that weights
+// are consumed byte for byte as they sit in the GGUF block.
+__host__ __device__ __forceinline__ int hw_pos(int j) { return (j < 16) ? (2 * j) : (2 * (j - 16) + 1); }
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }   // q36_ops.cuh:58
+__device__ __forceinline__ float sigm_f(float x) { return 1.f / (1.f + __expf(-x)); } // q36_ops.cuh:59
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace q36

@@ -1,0 +1,41 @@
+// Internal launcher prototypes shared by the translation units of libq36moe.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q36 {
+
+constexpr int DISPATCH_MAX_GROUPS = 512;  // upper bound on expert groups per call
+
+// moe_route.cu
+int launch_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale,
+                       int renorm, int T, int row_stride, cudaStream_t st);
+uint64_t dispatch_ws_bytes(int n_entries, int n_expert);
+// soffs (optional): receives {s0, s1}, the row range of the shared expert's group
+int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *ecount, int *eoffs,
+                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st);
+int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K, const int *pos,
+                 int k, int shared_row0, bool scatter, cudaStream_t st);
+
+// moe_gemv.cu
+// Sg/Su/Sd + soffs[2]: one extra group (the shared expert) with its own planes and row range, or NULL
+int launch_gateup_gemv(const void *Wg, const void *Wu, int n_group, const int *goffs, const void *Sg,
+                       const void *Su, const int *soffs, const uint8_t *Xq, const uint8_t *Xs,
+                       uint8_t *Hq, uint8_t *Hs, int D, int FF, cudaStream_t st);
+int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *Sd, const int *soffs,
+                     const uint8_t *Hq, const uint8_t *Hs, float *Y, int D, int FF, cudaStream_t st);
+int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
+                   const float *shgate, int shgate_stride, int D, int k, int T, cudaStream_t st);
+int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
+                       cudaStream_t st);
+int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st);
+
+// moe_tc.cu
+int launch_gateup_tc(const void *Wg, const void *Wu, int n_group, const int *goffs, int R_max,
+                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF,
+                     void *ws, int *status, cudaStream_t st);
+int launch_down_tc(const void *Wd, int n_group, const int *goffs, int R_max, const uint8_t *Hq,
+                   const uint8_t *Hs, float *Y, int D, int FF, void *ws, int *status, cudaStream_t st);
+uint64_t tc_ws_bytes(int n_group, int R_max, int D, int FF);
+
+}  // namespace q36

@@ -1,0 +1,321 @@
+// extern "C" entry points of libq36moe (declared in include/q36_moe.h).
+#include <cuda_bf16.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace q36 {
+
+int &last_cuda_error() {
+    static thread_local int e = 0;
+    return e;
+}
+int check_launch() {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+static int ck(cudaError_t e) {
+    if (e != cudaSuccess) { last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+
+static inline uint64_t al(uint64_t x) { return (x + 255) & ~(uint64_t)255; }
+
+// Carves the caller's workspace of one layer call.  Every region is 256-byte
+// aligned; the first 256 bytes hold the device-side status words of the
+// tensor-core launches.
+struct LayerWs {
+    int *status;          // [4]
+    int *idx; float *wt;  // [T*k]
+    int *ecount, *eoffs, *soffs, *elist, *pos;
+    void *disp;
+    uint8_t *Xq, *Xs, *Hq, *Hs;
+    float *Y;
+    void *tc[4];
+    uint64_t total;
+};
+static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
+    LayerWs w;
+    uint8_t *p = (uint8_t *)base;
+    uint64_t o = 0;
+    const uint64_t R = (uint64_t)T * (k + 1), n = (uint64_t)T * k;
+    auto take = [&](uint64_t bytes) { uint8_t *r = p + o; o += al(bytes); return (void *)r; };
+    w.status = (int *)take(256);
+    w.idx = (int *)take(n * 4);
+    w.wt = (float *)take(n * 4);
+    w.ecount = (int *)take((uint64_t)E * 4);
+    w.eoffs = (int *)take((uint64_t)(E + 1) * 4);
+    w.soffs = (int *)take(8);
+    w.elist = (int *)take(n * 4);
+    w.pos = (int *)take(n * 4);
+    w.disp = take(dispatch_ws_bytes((int)n, E));
+    w.Xq = (uint8_t *)take(R * D);
+    w.Xs = (uint8_t *)take(R * (D / Q36_QK));
+    w.Hq = (uint8_t *)take(R * FF);
+    w.Hs = (uint8_t *)take(R * (FF / Q36_QK));
+    w.Y = (float *)take(R * D * 4);
+    for (int i = 0; i < 4; i++) w.tc[i] = take(tc_ws_bytes(i & 1 ? 1 : E, (int)R, D, FF));
+    w.total = o;
+    return w;
+}
+
+static int pick_path(int path, int T) {
+    if (path == Q36_MOE_PATH_GEMV || path == Q36_MOE_PATH_TC) return path;
+    // The engine switches from its GEMV kernels to its tiled kernels at 14
+    // rows (q36_engine.cu:2217-2221); the same threshold is the default here.
+    return (T < 14) ? Q36_MOE_PATH_GEMV : Q36_MOE_PATH_TC;
+}
+
+static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                      const void *Sd, int E, int se0, int se1, int k, int D, int FF, const void *X,
+                      int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
+                      float route_scale, int inc_shared, float *out, int *idx_out, float *wt_out, int T,
+                      int path, void *ws, uint64_t ws_bytes, cudaStream_t st) {
+    if (!Wg || !Wu || !Wd || !X || !logits || !out || !ws) return Q36_MOE_EINVAL;
+    if (T <= 0 || k <= 0 || k > 8 || E <= 0 || E > DISPATCH_MAX_GROUPS || se0 < 0 || se1 > E || se0 >= se1)
+        return Q36_MOE_EINVAL;
+    if (D % 128 || FF % 128 || logit_stride < E) return Q36_MOE_EINVAL;
+    const LayerWs w = carve(ws, T, E, k, D, FF);
+    if (w.total > ws_bytes) return Q36_MOE_ENOSPACE;
+    const bool shared = Sg && Su && Sd && inc_shared;
+    const int n = T * k, R = T * (k + 1);
+    int rc;
+    if ((rc = ck(cudaMemsetAsync(w.status, 0, 16, st)))) return rc;
+    if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
+    if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
+                              shared ? n + T : n, st)))
+        return rc;
+    if ((rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
+    const int ng = se1 - se0;
+    const int *goffs = w.eoffs + se0;
+    if (pick_path(path, T) == Q36_MOE_PATH_GEMV) {
+        if ((rc = launch_gateup_gemv(Wg, Wu, ng, goffs, shared ? Sg : nullptr, shared ? Su : nullptr, w.soffs, w.Xq,
+                                     w.Xs, w.Hq, w.Hs, D, FF, st)))
+            return rc;
+        if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
+            return rc;
+    } else {
+        if ((rc = launch_gateup_tc(Wg, Wu, ng, goffs, R, w.Xq, w.Xs, w.Hq, w.Hs, D, FF, w.tc[0], w.status + 0, st)))
+            return rc;
+        if (shared && (rc = launch_gateup_tc(Sg, Su, 1, w.soffs, R, w.Xq, w.Xs, w.Hq, w.Hs, D, FF, w.tc[1],
+                                             w.status + 1, st)))
+            return rc;
+        if ((rc = launch_down_tc(Wd, ng, goffs, R, w.Hq, w.Hs, w.Y, D, FF, w.tc[2], w.status + 2, st))) return rc;
+        if (shared && (rc = launch_down_tc(Sd, 1, w.soffs, R, w.Hq, w.Hs, w.Y, D, FF, w.tc[3], w.status + 3, st)))
+            return rc;
+    }
+    const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
+    if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
+                             T, st)))
+        return rc;
+    if (idx_out && (rc = ck(cudaMemcpyAsync(idx_out, w.idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
+    if (wt_out && (rc = ck(cudaMemcpyAsync(wt_out, w.wt, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
+    return Q36_MOE_OK;
+}
+
+}  // namespace q36
+
+using namespace q36;
+
+extern "C" {
+
+const char *q36_moe_strerror(int s) {
+    switch (s) {
+        case Q36_MOE_OK: return "ok";
+        case Q36_MOE_EINVAL: return "invalid argument";
+        case Q36_MOE_ECUDA: return "CUDA error (see q36_moe_last_cuda_error)";
+        case Q36_MOE_ENOSPACE: return "workspace too small";
+        case Q36_MOE_EDEVICE: return "a bounded device-side wait gave up";
+        default: return "unknown status";
+    }
+}
+int q36_moe_last_cuda_error(void) { return last_cuda_error(); }
+int q36_moe_abi_version(void) { return 1; }
+
+uint64_t q36_moe_expert_stride(int M, int K) { return (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK); }
+
+int q36_moe_repack_mxfp4(const void *host_blocks, int K, int M, int e0, int e1, void *host_dst) {
+    if (!host_blocks || !host_dst || K % Q36_QK || M <= 0 || e0 < 0 || e1 <= e0) return Q36_MOE_EINVAL;
+    const uint64_t nbr = K / Q36_QK, qs_e = (uint64_t)M * (K / 2), es_e = (uint64_t)M * nbr;
+    const uint8_t *src = (const uint8_t *)host_blocks;
+    for (int ex = e0; ex < e1; ex++) {
+        uint8_t *qd = (uint8_t *)host_dst + (uint64_t)(ex - e0) * (qs_e + es_e), *ed = qd + qs_e;
+        const uint8_t *blk = src + (uint64_t)ex * M * nbr * 17;
+        for (uint64_t i = 0; i < (uint64_t)M * nbr; i++, blk += 17) {
+            ed[i] = blk[0];
+            memcpy(qd + i * 16, blk + 1, 16);
+        }
+    }
+    return Q36_MOE_OK;
+}
+
+int q36_moe_upload_mxfp4(const void *host_blocks, int K, int M, int e0, int e1, void *dev_dst) {
+    if (!dev_dst) return Q36_MOE_EINVAL;
+    const uint64_t bytes = (uint64_t)(e1 - e0) * q36_moe_expert_stride(M, K);
+    void *tmp = malloc(bytes);
+    if (!tmp) return Q36_MOE_ENOSPACE;
+    int rc = q36_moe_repack_mxfp4(host_blocks, K, M, e0, e1, tmp);
+    if (rc == Q36_MOE_OK) rc = ck(cudaMemcpy(dev_dst, tmp, bytes, cudaMemcpyHostToDevice));
+    free(tmp);
+    return rc;
+}
+
+int q36_moe_dequant_mxfp4(const void *W, int M, int K, float *out, void *stream) {
+    if (!W || !out || K % Q36_QK) return Q36_MOE_EINVAL;
+    return launch_dequant_mxfp4(W, M, K, out, (cudaStream_t)stream);
+}
+
+int q36_moe_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale, int renorm,
+                        int T, int row_stride, void *stream) {
+    if (!logits || !idx || !wt || k <= 0 || k > 32 || k > n_expert) return Q36_MOE_EINVAL;
+    if (n_expert != 256 && n_expert != 128 && n_expert != 64 && n_expert != 32) return Q36_MOE_EINVAL;
+    if (T < 0 || row_stride < n_expert) return Q36_MOE_EINVAL;
+    return launch_router_topk(logits, n_expert, k, idx, wt, scale, renorm, T, row_stride, (cudaStream_t)stream);
+}
+
+int q36_moe_quant_e4m3(const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int T, int K, void *stream) {
+    if (!X || !Xq || !Xs || K % Q36_QK || T < 0) return Q36_MOE_EINVAL;
+    return launch_quant(X, x_is_bf16, Xq, Xs, T, K, nullptr, 0, -1, false, (cudaStream_t)stream);
+}
+
+uint64_t q36_moe_dispatch_ws_bytes(int n_entries, int n_expert) { return dispatch_ws_bytes(n_entries, n_expert); }
+
+int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1, int *ecount,
+                     int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes, void *stream) {
+    if (!expert_of_entry || !ecount || !eoffs || !elist || !pos || !ws) return Q36_MOE_EINVAL;
+    if (n_entries < 0 || n_expert <= 0 || n_expert > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (ws_bytes < dispatch_ws_bytes(n_entries, n_expert)) return Q36_MOE_ENOSPACE;
+    return launch_dispatch(expert_of_entry, n_entries, n_expert, se0, se1, ecount, eoffs, elist, pos, ws, nullptr, 0,
+                           0, (cudaStream_t)stream);
+}
+
+int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, int shared_row0, uint8_t *Xq_rows,
+                          uint8_t *Xs_rows, int T, int K, void *stream) {
+    if (!X || !Xq_rows || !Xs_rows || (k > 0 && !pos) || K % Q36_QK || T < 0) return Q36_MOE_EINVAL;
+    return launch_quant(X, x_is_bf16, Xq_rows, Xs_rows, T, K, pos, k, shared_row0, true, (cudaStream_t)stream);
+}
+
+uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) { return 256 + 2 * al(tc_ws_bytes(n_group, R_max, D, FF)); }
+
+int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
+                              int R_max, const uint8_t *Xq_rows, const uint8_t *Xs_rows, uint8_t *Hq_rows,
+                              uint8_t *Hs_rows, float *Y_rows, int D, int FF, int path, void *ws, uint64_t ws_bytes,
+                              void *stream) {
+    if (!Wg || !Wu || !Wd || !goffs || !Xq_rows || !Xs_rows || !Hq_rows || !Hs_rows || !Y_rows) return Q36_MOE_EINVAL;
+    if (n_group <= 0 || n_group > DISPATCH_MAX_GROUPS || D % 128 || FF % 128 || R_max <= 0) return Q36_MOE_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    if (path == Q36_MOE_PATH_GEMV) {
+        if ((rc = launch_gateup_gemv(Wg, Wu, n_group, goffs, nullptr, nullptr, nullptr, Xq_rows, Xs_rows, Hq_rows,
+                                     Hs_rows, D, FF, st)))
+            return rc;
+        return launch_down_gemv(Wd, n_group, goffs, nullptr, nullptr, Hq_rows, Hs_rows, Y_rows, D, FF, st);
+    }
+    if (!ws || ws_bytes < q36_moe_ffn_ws_bytes(n_group, R_max, D, FF)) return Q36_MOE_ENOSPACE;
+    uint8_t *p = (uint8_t *)ws;
+    const uint64_t one = al(tc_ws_bytes(n_group, R_max, D, FF));
+    if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
+    if ((rc = launch_gateup_tc(Wg, Wu, n_group, goffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, p + 256,
+                               (int *)p, st)))
+        return rc;
+    return launch_down_tc(Wd, n_group, goffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + one, (int *)p + 1, st);
+}
+
+int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float *wt, const float *SH_rows,
+                    const float *shgate, int shgate_stride, int D, int k, int T, void *stream) {
+    if (!out || !Y_rows || !pos || !wt || D % 4 || k <= 0 || T < 0) return Q36_MOE_EINVAL;
+    return launch_combine(out, Y_rows, pos, wt, SH_rows, shgate, shgate_stride, D, k, T, (cudaStream_t)stream);
+}
+
+uint64_t q36_moe_workspace_bytes(int T_max, int n_expert, int k, int D, int FF) {
+    if (T_max <= 0 || n_expert <= 0 || k <= 0) return 0;
+    return carve(nullptr, T_max, n_expert, k, D, FF).total;
+}
+
+int q36_moe_ws_status(const void *ws, void *stream) {
+    int h[4] = {0, 0, 0, 0};
+    int rc = ck(cudaMemcpyAsync(h, ws, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    if (rc) return rc;
+    if ((rc = ck(cudaStreamSynchronize((cudaStream_t)stream)))) return rc;
+    return (h[0] | h[1] | h[2] | h[3]) ? Q36_MOE_EDEVICE : Q36_MOE_OK;
+}
+
+int q36_moe_layer(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd,
+                  int n_expert, int se0, int se1, int k, int D, int FF, const void *X, int x_is_bf16,
+                  const float *logits, int logit_stride, int shgate_col, float route_scale, int inc_shared,
+                  float *out, int *idx_out, float *wt_out, int T, int path, void *ws, uint64_t ws_bytes,
+                  void *stream) {
+    return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
+                      shgate_col, route_scale, inc_shared, out, idx_out, wt_out, T, path, ws, ws_bytes,
+                      (cudaStream_t)stream);
+}
+int q36_moe_decode(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd,
+                   int n_expert, int se0, int se1, int k, int D, int FF, const void *X, int x_is_bf16,
+                   const float *logits, int logit_stride, int shgate_col, float route_scale, int inc_shared,
+                   float *out, int T, void *ws, uint64_t ws_bytes, void *stream) {
+    return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
+                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_GEMV, ws, ws_bytes,
+                      (cudaStream_t)stream);
+}
+int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd,
+                    int n_expert, int se0, int se1, int k, int D, int FF, const void *X, int x_is_bf16,
+                    const float *logits, int logit_stride, int shgate_col, float route_scale, int inc_shared,
+                    float *out, int T, void *ws, uint64_t ws_bytes, void *stream) {
+    return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
+                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_TC, ws, ws_bytes,
+                      (cudaStream_t)stream);
+}
+
+uint64_t q36_moe_host_io_bytes(int T, int D, int logit_stride, int x_is_bf16) {
+    return al((uint64_t)T * D * (x_is_bf16 ? 2 : 4)) + al((uint64_t)T * logit_stride * 4) + al((uint64_t)T * D * 4);
+}
+
+int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                       const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF, const void *host_X,
+                       int x_is_bf16, const float *host_logits, int logit_stride, int shgate_col, float route_scale,
+                       int inc_shared, float *host_out, int T, int path, void *dev_io, void *ws, uint64_t ws_bytes,
+                       void *stream) {
+    if (!host_X || !host_logits || !host_out || !dev_io || T <= 0) return Q36_MOE_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint64_t xb = (uint64_t)T * D * (x_is_bf16 ? 2 : 4), lb = (uint64_t)T * logit_stride * 4,
+                   ob = (uint64_t)T * D * 4;
+    uint8_t *dX = (uint8_t *)dev_io, *dL = dX + al(xb), *dO = dL + al(lb);
+    int rc;
+    if ((rc = ck(cudaMemcpyAsync(dX, host_X, xb, cudaMemcpyHostToDevice, st)))) return rc;
+    if ((rc = ck(cudaMemcpyAsync(dL, host_logits, lb, cudaMemcpyHostToDevice, st)))) return rc;
+    if ((rc = layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, dX, x_is_bf16, (const float *)dL,
+                         logit_stride, shgate_col, route_scale, inc_shared, (float *)dO, nullptr, nullptr, T, path, ws,
+                         ws_bytes, st)))
+        return rc;
+    if ((rc = ck(cudaMemcpyAsync(host_out, dO, ob, cudaMemcpyDeviceToHost, st)))) return rc;
+    if ((rc = ck(cudaStreamSynchronize(st)))) return rc;
+    if (pick_path(path, T) == Q36_MOE_PATH_TC) return q36_moe_ws_status(ws, stream);
+    return Q36_MOE_OK;
+}
+
+int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes, void *stream) {
+    if (!src || !index || !dst || row_bytes % 16 || n_rows < 0) return Q36_MOE_EINVAL;
+    return launch_gather_rows(src, index, dst, n_rows, row_bytes, (cudaStream_t)stream);
+}
+
+int q36_moe_tc_selftest(const uint8_t *A_codes_scales, const uint8_t *B_q, const uint8_t *B_s, float *Dout, int N,
+                        int K, void *ws, uint64_t ws_bytes, void *stream) {
+    // A_codes_scales: one "expert" of 128 rows in the split layout
+    // [128][K/2] codes then [128][K/32] scales; Dout: [N][128] (token-major).
+    if (!A_codes_scales || !B_q || !B_s || !Dout || !ws || N <= 0 || N > 4096 || K % 512) return Q36_MOE_EINVAL;
+    if (ws_bytes < 512 + tc_ws_bytes(1, N, 128, K)) return Q36_MOE_ENOSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    int h[2] = {0, N};
+    int *goffs = (int *)((uint8_t *)ws + 256);
+    int rc;
+    if ((rc = ck(cudaMemsetAsync(ws, 0, 16, st)))) return rc;
+    if ((rc = ck(cudaMemcpyAsync(goffs, h, sizeof h, cudaMemcpyHostToDevice, st)))) return rc;
+    if ((rc = launch_down_tc(A_codes_scales, 1, goffs, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws, st)))
+        return rc;
+    return q36_moe_ws_status(ws, stream);
+}
+
+}  // extern "C"

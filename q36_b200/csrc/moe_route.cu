@@ -1,0 +1,234 @@
+// Routing, deterministic dispatch and the activation quantiser.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace q36 {
+
+// ---------------------------------------------------------------- router
+// One warp per token row; each lane holds n_expert/32 logits in registers.
+// Same selection rule as k_router_topk (q36_ops.cuh:397-431): arg-max on the
+// raw logits, ties to the lower expert id, k rounds with the winner masked.
+template <int PER_LANE>
+__device__ __forceinline__ void route_row(const float *__restrict__ l, int k, int *idx, float *wt,
+                                          float scale, int renorm, int lane) {
+    float v[PER_LANE];
+#pragma unroll
+    for (int j = 0; j < PER_LANE; j++) v[j] = l[lane + j * 32];
+    float m = -1e30f;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; j++) m = fmaxf(m, v[j]);
+    m = warp_max(m);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; j++) s += expf(v[j] - m);
+    s = warp_sum(s);
+    float w_keep = 0.f, wsum = 0.f;  // lane r keeps the weight of round r
+    for (int r = 0; r < k; r++) {
+        float bm = -1e30f;
+        int bj = 0;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; j++)
+            if (v[j] > bm) { bm = v[j]; bj = j; }
+        float wv = bm;
+        int wi = lane + bj * 32;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+            if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
+        }
+        const float w = expf(wv - m) / s;
+        if (lane == r) { w_keep = w; idx[r] = wi; }
+        wsum += w;
+        if (lane == (wi & 31)) {
+#pragma unroll
+            for (int j = 0; j < PER_LANE; j++)
+                if (j == (wi >> 5)) v[j] = -1e30f;
+        }
+    }
+    if (lane < k) wt[lane] = renorm ? (w_keep / wsum * scale) : (w_keep * scale);
+}
+
+__global__ void k_router_topk(const float *__restrict__ logits, int n_expert, int k, int *idx,
+                              float *wt, float scale, int renorm, int T, int row_stride) {
+    Q36_GDS();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    const float *l = logits + (size_t)warp * row_stride;
+    if (n_expert == 256) route_row<8>(l, k, idx + (size_t)warp * k, wt + (size_t)warp * k, scale, renorm, lane);
+    else if (n_expert == 128) route_row<4>(l, k, idx + (size_t)warp * k, wt + (size_t)warp * k, scale, renorm, lane);
+    else if (n_expert == 64) route_row<2>(l, k, idx + (size_t)warp * k, wt + (size_t)warp * k, scale, renorm, lane);
+    else route_row<1>(l, k, idx + (size_t)warp * k, wt + (size_t)warp * k, scale, renorm, lane);
+}
+
+// -------------------------------------------------------------- dispatch
+// Stable counting sort of entry ids by expert in three launches.  Entries are
+// cut into chunks of DISPATCH_CHUNK; inside a chunk warp w owns entries
+// [32w, 32w+32).
+//   k_dispatch_count : per (chunk, expert) counts and each entry's rank among
+//                      the chunk's earlier entries of the same expert
+//   k_dispatch_scan  : per expert exclusive scan over chunks, then over experts
+//   k_dispatch_place : elist / pos from eoffs + chunk base + rank
+// The order inside a bucket is ascending entry id, one of the orders the
+// engine's atomic k_moe_dispatch (q36_engine.cu:3387-3392) can produce.
+constexpr int DISPATCH_CHUNK = 1024;
+constexpr int DISPATCH_MAX_E = 512;
+
+__global__ void __launch_bounds__(DISPATCH_CHUNK)
+k_dispatch_count(const int *__restrict__ eid, int n, int n_expert, int se0, int se1,
+                 int *__restrict__ chunk_cnt, int *__restrict__ lrank) {
+    Q36_GDS();
+    __shared__ unsigned short cnt[DISPATCH_CHUNK / 32][DISPATCH_MAX_E];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < (DISPATCH_CHUNK / 32) * DISPATCH_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * DISPATCH_CHUNK + tid;
+    int e = -1;
+    if (i < n) {
+        e = eid[i];
+        if (e < se0 || e >= se1 || e >= n_expert) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && r_in_warp == 0) cnt[warp][e] = (unsigned short)__popc(peers);
+    __syncthreads();
+    for (int x = tid; x < n_expert; x += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < DISPATCH_CHUNK / 32; w++) {
+            const int c = cnt[w][x];
+            cnt[w][x] = (unsigned short)run;
+            run += c;
+        }
+        chunk_cnt[(size_t)blockIdx.x * n_expert + x] = run;
+    }
+    __syncthreads();
+    if (i < n) lrank[i] = (e >= 0) ? (cnt[warp][e] + r_in_warp) : -1;
+}
+
+__global__ void k_dispatch_scan(int *__restrict__ chunk_cnt, int n_chunk, int n_expert,
+                                int *__restrict__ ecount, int *__restrict__ eoffs,
+                                int *__restrict__ soffs, int s0, int s1) {
+    Q36_GDS();
+    __shared__ int tot[DISPATCH_MAX_E];
+    for (int x = threadIdx.x; x < n_expert; x += blockDim.x) {
+        int run = 0;
+        for (int c = 0; c < n_chunk; c++) {
+            const int v = chunk_cnt[(size_t)c * n_expert + x];
+            chunk_cnt[(size_t)c * n_expert + x] = run;
+            run += v;
+        }
+        tot[x] = run;
+        ecount[x] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int x = 0; x < n_expert; x++) { eoffs[x] = run; run += tot[x]; }
+        eoffs[n_expert] = run;
+        if (soffs) { soffs[0] = s0; soffs[1] = s1; }
+    }
+}
+
+__global__ void k_dispatch_place(const int *__restrict__ eid, int n, int n_expert,
+                                 const int *__restrict__ chunk_base, const int *__restrict__ lrank,
+                                 const int *__restrict__ eoffs, int *__restrict__ elist,
+                                 int *__restrict__ pos) {
+    Q36_GDS();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = lrank[i];
+    if (r < 0) { pos[i] = -1; return; }
+    const int e = eid[i];
+    const int p = eoffs[e] + chunk_base[(size_t)(i / DISPATCH_CHUNK) * n_expert + e] + r;
+    elist[p] = i;
+    pos[i] = p;
+}
+
+// ------------------------------------------------------------- quantiser
+// One warp per (row, 32-block), one lane per element, as k_quant_e4m3 does
+// (q36_engine.cu:2412-2428).  SCATTER = false: logical order into Xq[T][K].
+// SCATTER = true: hw order into every row of the sorted space the token feeds.
+template <bool BF16, bool SCATTER>
+__global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ Xq,
+                             uint8_t *__restrict__ Xs, int T, int K, const int *__restrict__ pos,
+                             int k, int shared_row0) {
+    Q36_GDS();
+    const int nb = K / Q36_QK;
+    const long gwarp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gwarp >= (long)T * nb) return;
+    const int t = (int)(gwarp / nb), b = (int)(gwarp % nb);
+    const size_t off = (size_t)t * K + (size_t)b * Q36_QK + lane;
+    const float v = BF16 ? __bfloat162float(((const __nv_bfloat16 *)X)[off]) : ((const float *)X)[off];
+    const float a = warp_max(fabsf(v));
+    const int e2 = e2_of_amax(a);
+    const uint8_t q = f32_to_e4m3(v * inv_scale_of_e2(e2));
+    if (!SCATTER) {
+        Xq[off] = q;
+        if (lane == 0) Xs[(size_t)t * nb + b] = (uint8_t)(127 + e2);
+    } else {
+        // gather the block's 32 codes in hw order: lane p receives the code of
+        // the element that lives at position p
+        const int src = (lane & 1) ? (16 + (lane >> 1)) : (lane >> 1);
+        const uint32_t qp = __shfl_sync(0xffffffffu, (uint32_t)q, src);
+        // pack 4 positions per lane (lanes 0..7 hold the 32 bytes)
+        uint32_t w = qp;
+        w |= __shfl_down_sync(0xffffffffu, qp, 1) << 8;
+        w |= __shfl_down_sync(0xffffffffu, qp, 2) << 16;
+        w |= __shfl_down_sync(0xffffffffu, qp, 3) << 24;
+        const uint32_t word = __shfl_sync(0xffffffffu, w, (lane & 7) * 4);
+        // lane l writes word (l & 7) of destination (l >> 3), 4 destinations a pass
+        const int n_dst = k + (shared_row0 >= 0 ? 1 : 0);
+        for (int d0 = 0; d0 < n_dst; d0 += 4) {
+            const int d = d0 + (lane >> 3);
+            if (d < n_dst) {
+                const int row = (d < k) ? pos[(size_t)t * k + d] : (shared_row0 + t);
+                if (row >= 0) {
+                    ((uint32_t *)(Xq + (size_t)row * K + (size_t)b * Q36_QK))[lane & 7] = word;
+                    if ((lane & 7) == 0) Xs[(size_t)row * nb + b] = (uint8_t)(127 + e2);
+                }
+            }
+        }
+    }
+}
+
+// -------------------------------------------------------------- launchers
+int launch_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale,
+                       int renorm, int T, int row_stride, cudaStream_t st) {
+    if (T <= 0) return Q36_MOE_OK;
+    k_router_topk<<<(T + 7) / 8, 256, 0, st>>>(logits, n_expert, k, idx, wt, scale, renorm, T, row_stride);
+    return check_launch();
+}
+
+uint64_t dispatch_ws_bytes(int n_entries, int n_expert) {
+    const uint64_t n_chunk = ((uint64_t)n_entries + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
+    return (n_chunk * n_expert + (uint64_t)n_entries) * sizeof(int) + 256;
+}
+
+int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *ecount, int *eoffs,
+                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st) {
+    const int n_chunk = (n + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
+    int *chunk_cnt = (int *)ws;
+    int *lrank = chunk_cnt + (size_t)n_chunk * n_expert;
+    if (n > 0) k_dispatch_count<<<n_chunk, DISPATCH_CHUNK, 0, st>>>(eid, n, n_expert, se0, se1, chunk_cnt, lrank);
+    k_dispatch_scan<<<1, 256, 0, st>>>(chunk_cnt, n_chunk, n_expert, ecount, eoffs, soffs, s0, s1);
+    if (n > 0) k_dispatch_place<<<(n + 255) / 256, 256, 0, st>>>(eid, n, n_expert, chunk_cnt, lrank, eoffs, elist, pos);
+    return check_launch();
+}
+
+int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K, const int *pos,
+                 int k, int shared_row0, bool scatter, cudaStream_t st) {
+    if (T <= 0) return Q36_MOE_OK;
+    const long warps = (long)T * (K / Q36_QK);
+    const unsigned grid = (unsigned)((warps + 7) / 8);
+    if (scatter) {
+        if (bf16) k_quant_e4m3<true, true><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, pos, k, shared_row0);
+        else k_quant_e4m3<false, true><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, pos, k, shared_row0);
+    } else {
+        if (bf16) k_quant_e4m3<true, false><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, nullptr, 0, -1);
+        else k_quant_e4m3<false, false><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, nullptr, 0, -1);
+    }
+    return check_launch();
+}
+
+}  // namespace q36

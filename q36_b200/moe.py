@@ -1,0 +1,290 @@
+"""Host-side binding of libq36moe.so (the C ABI in include/q36_moe.h).
+
+torch is used for device memory and streams only; every computation goes
+through the C entry points.  The library must have been built
+(`python -m q36_b200.build`): importing this module without it raises.
+
+`MoELayer` mirrors what the q36 engine keeps per layer for this path: the
+expert weights in the split-plane layout of upload() (q36_engine.cu:202-228),
+the shared expert, the expert shard [se0, se1) (q36_engine.cu:57-60) and the
+scratch that `moe_ffn` / `pf_moe_block` use (q36_engine.cu:1592-1654,
+3423-3472).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libq36moe.so")
+
+PATH_AUTO, PATH_GEMV, PATH_TC = 0, 1, 2
+OK, EINVAL, ECUDA, ENOSPACE, EDEVICE = 0, -1, -2, -3, -4
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m q36_b200.build` "
+        "(there is no CPU or PyTorch fallback for this path)")
+
+lib = C.CDLL(LIB_PATH)
+vp, i32, u64, f32 = C.c_void_p, C.c_int, C.c_uint64, C.c_float
+
+_SIGS = {
+    "q36_moe_strerror": (C.c_char_p, [i32]),
+    "q36_moe_last_cuda_error": (i32, []),
+    "q36_moe_abi_version": (i32, []),
+    "q36_moe_expert_stride": (u64, [i32, i32]),
+    "q36_moe_repack_mxfp4": (i32, [vp, i32, i32, i32, i32, vp]),
+    "q36_moe_upload_mxfp4": (i32, [vp, i32, i32, i32, i32, vp]),
+    "q36_moe_dequant_mxfp4": (i32, [vp, i32, i32, vp, vp]),
+    "q36_moe_router_topk": (i32, [vp, i32, i32, vp, vp, f32, i32, i32, i32, vp]),
+    "q36_moe_quant_e4m3": (i32, [vp, i32, vp, vp, i32, i32, vp]),
+    "q36_moe_dispatch_ws_bytes": (u64, [i32, i32]),
+    "q36_moe_dispatch": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, u64, vp]),
+    "q36_moe_quant_scatter": (i32, [vp, i32, vp, i32, i32, vp, vp, i32, i32, vp]),
+    "q36_moe_ffn_ws_bytes": (u64, [i32, i32, i32, i32]),
+    "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, u64, vp]),
+    "q36_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "q36_moe_workspace_bytes": (u64, [i32, i32, i32, i32, i32]),
+    "q36_moe_ws_status": (i32, [vp, vp]),
+    "q36_moe_layer": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, vp, vp, i32, i32, vp, u64, vp]),
+    "q36_moe_decode": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
+    "q36_moe_prefill": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
+    "q36_moe_host_io_bytes": (u64, [i32, i32, i32, i32]),
+    "q36_moe_layer_host": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, i32, vp, vp, u64, vp]),
+    "q36_moe_gather_rows": (i32, [vp, vp, vp, i32, i32, vp]),
+    "q36_moe_tc_selftest": (i32, [vp, vp, vp, vp, i32, i32, vp, u64, vp]),
+}
+for _n, (_r, _a) in _SIGS.items():
+    _f = getattr(lib, _n)
+    _f.restype, _f.argtypes = _r, _a
+
+
+class MoEError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != OK:
+        msg = lib.q36_moe_strerror(rc).decode()
+        extra = f" (cudaError {lib.q36_moe_last_cuda_error()})" if rc == ECUDA else ""
+        raise MoEError(f"{what}: {msg}{extra}")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def expert_stride(M: int, K: int) -> int:
+    return int(lib.q36_moe_expert_stride(M, K))
+
+
+def upload_mxfp4(blocks: np.ndarray, K: int, M: int, e0: int, e1: int, device="cuda") -> torch.Tensor:
+    """GGUF blocks uint8 [E, M, K/32, 17] (host) -> split planes on the device."""
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    dst = torch.empty((e1 - e0) * expert_stride(M, K), dtype=torch.uint8, device=device)
+    check(lib.q36_moe_upload_mxfp4(b.ctypes.data, K, M, e0, e1, dst.data_ptr()), "upload_mxfp4")
+    return dst
+
+
+def dequant_mxfp4(W: torch.Tensor, M: int, K: int) -> torch.Tensor:
+    out = torch.empty((M, K), dtype=torch.float32, device=W.device)
+    check(lib.q36_moe_dequant_mxfp4(W.data_ptr(), M, K, out.data_ptr(), stream_ptr()), "dequant_mxfp4")
+    return out
+
+
+def router_topk(logits: torch.Tensor, n_expert: int, k: int = 8, scale: float = 1.0, renorm: bool = True):
+    T, stride = logits.shape
+    idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    check(lib.q36_moe_router_topk(logits.data_ptr(), n_expert, k, idx.data_ptr(), wt.data_ptr(), scale,
+                                  int(renorm), T, stride, stream_ptr()), "router_topk")
+    return idx, wt
+
+
+def quant_e4m3(X: torch.Tensor):
+    T, K = X.shape
+    bf = X.dtype == torch.bfloat16
+    assert bf or X.dtype == torch.float32
+    Xq = torch.empty((T, K), dtype=torch.uint8, device=X.device)
+    Xs = torch.empty((T, K // 32), dtype=torch.uint8, device=X.device)
+    check(lib.q36_moe_quant_e4m3(X.data_ptr(), int(bf), Xq.data_ptr(), Xs.data_ptr(), T, K, stream_ptr()), "quant_e4m3")
+    return Xq, Xs
+
+
+def dispatch(eid: torch.Tensor, n_expert: int, se0: int = 0, se1: int | None = None):
+    se1 = n_expert if se1 is None else se1
+    n = eid.numel()
+    dev = eid.device
+    ecount = torch.empty(n_expert, dtype=torch.int32, device=dev)
+    eoffs = torch.empty(n_expert + 1, dtype=torch.int32, device=dev)
+    elist = torch.full((max(n, 1),), -1, dtype=torch.int32, device=dev)
+    pos = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    wsb = int(lib.q36_moe_dispatch_ws_bytes(n, n_expert))
+    ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+    check(lib.q36_moe_dispatch(eid.data_ptr(), n, n_expert, se0, se1, ecount.data_ptr(), eoffs.data_ptr(),
+                               elist.data_ptr(), pos.data_ptr(), ws.data_ptr(), wsb, stream_ptr()), "dispatch")
+    return ecount, eoffs, elist[:n], pos[:n]
+
+
+def quant_scatter(X: torch.Tensor, pos: torch.Tensor | None, k: int, shared_row0: int, R: int):
+    T, K = X.shape
+    bf = X.dtype == torch.bfloat16
+    Xq = torch.zeros((R, K), dtype=torch.uint8, device=X.device)
+    Xs = torch.full((R, K // 32), 127, dtype=torch.uint8, device=X.device)
+    check(lib.q36_moe_quant_scatter(X.data_ptr(), int(bf), ptr(pos), k, shared_row0, Xq.data_ptr(), Xs.data_ptr(),
+                                    T, K, stream_ptr()), "quant_scatter")
+    return Xq, Xs
+
+
+def expert_ffn_sorted(Wg, Wu, Wd, n_group: int, goffs: torch.Tensor, Xq: torch.Tensor, Xs: torch.Tensor,
+                      D: int, FF: int, path: int, sync_check: bool = True):
+    R = Xq.shape[0]
+    dev = Xq.device
+    Hq = torch.zeros((R, FF), dtype=torch.uint8, device=dev)
+    Hs = torch.zeros((R, FF // 32), dtype=torch.uint8, device=dev)
+    Y = torch.zeros((R, D), dtype=torch.float32, device=dev)
+    wsb = int(lib.q36_moe_ffn_ws_bytes(n_group, R, D, FF))
+    ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+    check(lib.q36_moe_expert_ffn_sorted(Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), n_group, goffs.data_ptr(), R,
+                                        Xq.data_ptr(), Xs.data_ptr(), Hq.data_ptr(), Hs.data_ptr(), Y.data_ptr(),
+                                        D, FF, path, ws.data_ptr(), wsb, stream_ptr()), "expert_ffn_sorted")
+    if path == PATH_TC and sync_check:
+        check(lib.q36_moe_ws_status(ws.data_ptr(), stream_ptr()), "expert_ffn_sorted (device status)")
+    return Hq, Hs, Y
+
+
+def combine(Y, pos, wt, SH, shgate, shgate_stride: int, D: int, k: int, T: int):
+    out = torch.empty((T, D), dtype=torch.float32, device=Y.device)
+    check(lib.q36_moe_combine(out.data_ptr(), Y.data_ptr(), pos.data_ptr(), wt.data_ptr(), ptr(SH), ptr(shgate),
+                              shgate_stride, D, k, T, stream_ptr()), "combine")
+    return out
+
+
+def gather_rows(src: torch.Tensor, index: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+    n_rows = index.numel() if n_rows is None else n_rows
+    row_bytes = src.shape[1] * src.element_size()
+    dst = torch.empty((n_rows, src.shape[1]), dtype=src.dtype, device=src.device)
+    check(lib.q36_moe_gather_rows(src.data_ptr(), index.data_ptr(), dst.data_ptr(), n_rows, row_bytes, stream_ptr()),
+          "gather_rows")
+    return dst
+
+
+def tc_selftest(A: torch.Tensor, Bq: torch.Tensor, Bs: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """A: split layout of one 128-row matrix; returns D [N,128]; raises on a device-side timeout."""
+    D = torch.zeros((N, 128), dtype=torch.float32, device=A.device)
+    wsb = 512 + int(lib.q36_moe_ffn_ws_bytes(1, N, 128, K))
+    ws = torch.zeros(wsb, dtype=torch.uint8, device=A.device)
+    check(lib.q36_moe_tc_selftest(A.data_ptr(), Bq.data_ptr(), Bs.data_ptr(), D.data_ptr(), N, K, ws.data_ptr(), wsb,
+                                  stream_ptr()), "tc_selftest")
+    return D
+
+
+class MoELayer:
+    """One MoE layer resident on one GPU: routed experts [se0, se1) of n_expert,
+    plus (optionally) the shared expert."""
+
+    def __init__(self, n_expert=256, k=8, D=2048, FF=512, se0=0, se1=None, device="cuda"):
+        self.E, self.k, self.D, self.FF = n_expert, k, D, FF
+        self.se0, self.se1 = se0, (n_expert if se1 is None else se1)
+        self.device = torch.device(device)
+        self.Wg = self.Wu = self.Wd = None
+        self.Sg = self.Su = self.Sd = None
+        self._ws = None
+        self._ws_T = 0
+        self._io = None
+
+    # ---- weights
+    def load_gguf_blocks(self, gate, up, down, sgate=None, sup=None, sdown=None):
+        """GGUF MXFP4 blocks (numpy uint8) for ALL n_expert experts; only the shard is uploaded."""
+        D, FF = self.D, self.FF
+        self.Wg = upload_mxfp4(gate, D, FF, self.se0, self.se1, self.device)
+        self.Wu = upload_mxfp4(up, D, FF, self.se0, self.se1, self.device)
+        self.Wd = upload_mxfp4(down, FF, D, self.se0, self.se1, self.device)
+        if sgate is not None:
+            self.Sg = upload_mxfp4(sgate, D, FF, 0, 1, self.device)
+            self.Su = upload_mxfp4(sup, D, FF, 0, 1, self.device)
+            self.Sd = upload_mxfp4(sdown, FF, D, 0, 1, self.device)
+        return self
+
+    def set_device_planes(self, Wg, Wu, Wd, Sg=None, Su=None, Sd=None):
+        """Planes already on the device in the split layout (uint8 tensors)."""
+        self.Wg, self.Wu, self.Wd, self.Sg, self.Su, self.Sd = Wg, Wu, Wd, Sg, Su, Sd
+        return self
+
+    def random_planes(self, seed: int, shared: bool = True):
+        """Synthetic weights generated on the device: uniform code nibbles, scale bytes in [118,130]."""
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        n = self.se1 - self.se0
+
+        def planes(ne, M, K):
+            t = torch.randint(0, 256, (ne, expert_stride(M, K)), dtype=torch.uint8, device=self.device, generator=g)
+            t[:, M * K // 2:] = torch.randint(118, 131, (ne, M * K // 32), dtype=torch.uint8, device=self.device,
+                                              generator=g)
+            return t.reshape(-1)
+
+        self.Wg, self.Wu, self.Wd = planes(n, self.FF, self.D), planes(n, self.FF, self.D), planes(n, self.D, self.FF)
+        if shared:
+            self.Sg, self.Su, self.Sd = planes(1, self.FF, self.D), planes(1, self.FF, self.D), planes(1, self.D, self.FF)
+        return self
+
+    # ---- scratch
+    def workspace(self, T: int) -> torch.Tensor:
+        if self._ws is None or T > self._ws_T:
+            nbytes = int(lib.q36_moe_workspace_bytes(T, self.E, self.k, self.D, self.FF))
+            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            self._ws_T = T
+        return self._ws
+
+    # ---- compute
+    def forward(self, X: torch.Tensor, logits: torch.Tensor, out: torch.Tensor | None = None, path: int = PATH_AUTO,
+                shgate_col: int | None = None, route_scale: float = 1.0, inc_shared: bool = True,
+                want_routing: bool = False, ws: torch.Tensor | None = None, stream=None):
+        """X [T,D] f32|bf16, logits [T,stride] f32 (device).  Launch-only."""
+        T = X.shape[0]
+        bf = X.dtype == torch.bfloat16
+        stride = logits.shape[1]
+        if shgate_col is None:
+            shgate_col = self.E if stride > self.E else -1
+        if out is None:
+            out = torch.empty((T, self.D), dtype=torch.float32, device=X.device)
+        ws = self.workspace(T) if ws is None else ws
+        idx = torch.empty((T, self.k), dtype=torch.int32, device=X.device) if want_routing else None
+        wt = torch.empty((T, self.k), dtype=torch.float32, device=X.device) if want_routing else None
+        check(lib.q36_moe_layer(self.Wg.data_ptr(), self.Wu.data_ptr(), self.Wd.data_ptr(), ptr(self.Sg), ptr(self.Su),
+                                ptr(self.Sd), self.E, self.se0, self.se1, self.k, self.D, self.FF, X.data_ptr(), int(bf),
+                                logits.data_ptr(), stride, shgate_col, route_scale, int(inc_shared), out.data_ptr(),
+                                ptr(idx), ptr(wt), T, path, ws.data_ptr(), ws.numel(), stream_ptr(stream)), "moe_layer")
+        return (out, idx, wt) if want_routing else out
+
+    def check_device_status(self):
+        if self._ws is not None:
+            check(lib.q36_moe_ws_status(self._ws.data_ptr(), stream_ptr()), "device status")
+
+    def forward_host(self, X: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, path: int = PATH_AUTO,
+                     shgate_col: int | None = None, route_scale: float = 1.0, inc_shared: bool = True, stream=None):
+        """Host-buffer form: X, logits, out are CPU tensors (pinned for speed); synchronous."""
+        T = X.shape[0]
+        bf = X.dtype == torch.bfloat16
+        stride = logits.shape[1]
+        if shgate_col is None:
+            shgate_col = self.E if stride > self.E else -1
+        ws = self.workspace(T)
+        need = int(lib.q36_moe_host_io_bytes(T, self.D, stride, int(bf)))
+        if self._io is None or self._io.numel() < need:
+            self._io = torch.empty(need, dtype=torch.uint8, device=self.device)
+        check(lib.q36_moe_layer_host(self.Wg.data_ptr(), self.Wu.data_ptr(), self.Wd.data_ptr(), ptr(self.Sg),
+                                     ptr(self.Su), ptr(self.Sd), self.E, self.se0, self.se1, self.k, self.D, self.FF,
+                                     X.data_ptr(), int(bf), logits.data_ptr(), stride, shgate_col, route_scale,
+                                     int(inc_shared), out.data_ptr(), T, path, self._io.data_ptr(), ws.data_ptr(),
+                                     ws.numel(), stream_ptr(stream)), "moe_layer_host")
+        return out

@@ -198,30 +198,52 @@ int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, i
     return launch_quant(X, x_is_bf16, Xq_rows, Xs_rows, T, K, pos, k, shared_row0, true, (cudaStream_t)stream);
 }
 
-uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) { return 256 + 2 * al(tc_ws_bytes(n_group, R_max, D, FF)); }
+uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) {
+    return 256 + 2 * al(tc_ws_bytes(n_group, R_max, D, FF)) + 2 * al(tc_ws_bytes(1, R_max, D, FF));
+}
 
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
-                              int R_max, const uint8_t *Xq_rows, const uint8_t *Xs_rows, uint8_t *Hq_rows,
-                              uint8_t *Hs_rows, float *Y_rows, int D, int FF, int path, void *ws, uint64_t ws_bytes,
+                              const void *Sg, const void *Su, const void *Sd, const int *soffs, int R_max,
+                              const uint8_t *Xq_rows, const uint8_t *Xs_rows, uint8_t *Hq_rows, uint8_t *Hs_rows,
+                              float *Y_rows, int D, int FF, int path, int stages, void *ws, uint64_t ws_bytes,
                               void *stream) {
     if (!Wg || !Wu || !Wd || !goffs || !Xq_rows || !Xs_rows || !Hq_rows || !Hs_rows || !Y_rows) return Q36_MOE_EINVAL;
     if (n_group <= 0 || n_group > DISPATCH_MAX_GROUPS || D % 128 || FF % 128 || R_max <= 0) return Q36_MOE_EINVAL;
+    if (!(stages & 3) || (path != Q36_MOE_PATH_GEMV && path != Q36_MOE_PATH_TC)) return Q36_MOE_EINVAL;
+    const bool shared = Sg && Su && Sd && soffs;
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
     if (path == Q36_MOE_PATH_GEMV) {
-        if ((rc = launch_gateup_gemv(Wg, Wu, n_group, goffs, nullptr, nullptr, nullptr, Xq_rows, Xs_rows, Hq_rows,
-                                     Hs_rows, D, FF, st)))
+        if ((stages & 1) && (rc = launch_gateup_gemv(Wg, Wu, n_group, goffs, shared ? Sg : nullptr, shared ? Su : nullptr,
+                                                     soffs, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, st)))
             return rc;
-        return launch_down_gemv(Wd, n_group, goffs, nullptr, nullptr, Hq_rows, Hs_rows, Y_rows, D, FF, st);
+        if ((stages & 2) && (rc = launch_down_gemv(Wd, n_group, goffs, shared ? Sd : nullptr, soffs, Hq_rows, Hs_rows,
+                                                   Y_rows, D, FF, st)))
+            return rc;
+        return Q36_MOE_OK;
     }
     if (!ws || ws_bytes < q36_moe_ffn_ws_bytes(n_group, R_max, D, FF)) return Q36_MOE_ENOSPACE;
     uint8_t *p = (uint8_t *)ws;
-    const uint64_t one = al(tc_ws_bytes(n_group, R_max, D, FF));
+    const uint64_t one = al(tc_ws_bytes(n_group, R_max, D, FF)), sh = al(tc_ws_bytes(1, R_max, D, FF));
+    int *status = (int *)p;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
-    if ((rc = launch_gateup_tc(Wg, Wu, n_group, goffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, p + 256,
-                               (int *)p, st)))
-        return rc;
-    return launch_down_tc(Wd, n_group, goffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + one, (int *)p + 1, st);
+    if (stages & 1) {
+        if ((rc = launch_gateup_tc(Wg, Wu, n_group, goffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, p + 256,
+                                   status, st)))
+            return rc;
+        if (shared && (rc = launch_gateup_tc(Sg, Su, 1, soffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF,
+                                             p + 256 + 2 * one, status + 1, st)))
+            return rc;
+    }
+    if (stages & 2) {
+        if ((rc = launch_down_tc(Wd, n_group, goffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + one, status + 2,
+                                 st)))
+            return rc;
+        if (shared && (rc = launch_down_tc(Sd, 1, soffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + 2 * one + sh,
+                                           status + 3, st)))
+            return rc;
+    }
+    return Q36_MOE_OK;
 }
 
 int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float *wt, const float *SH_rows,
@@ -240,7 +262,11 @@ int q36_moe_ws_status(const void *ws, void *stream) {
     int rc = ck(cudaMemcpyAsync(h, ws, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     if (rc) return rc;
     if ((rc = ck(cudaStreamSynchronize((cudaStream_t)stream)))) return rc;
-    return (h[0] | h[1] | h[2] | h[3]) ? Q36_MOE_EDEVICE : Q36_MOE_OK;
+    if (h[0] | h[1] | h[2] | h[3]) {
+        last_cuda_error() = 200000 + (h[0] ? h[0] : h[1] ? h[1] : h[2] ? h[2] : h[3]);   // which wait gave up
+        return Q36_MOE_EDEVICE;
+    }
+    return Q36_MOE_OK;
 }
 
 int q36_moe_layer(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd,

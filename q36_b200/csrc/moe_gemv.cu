@@ -252,8 +252,8 @@ __global__ void k_dequant_mxfp4(const uint8_t *__restrict__ W, int M, int K, flo
 #pragma unroll
     for (int j = 0; j < 16; j++) {
         const float2 v = e2m1x2_to_f32x2((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
-        o[j] = v.x * d;
-        o[j + 16] = v.y * d;
+        o[j] = v.x * d + 0.f;        // "+ 0" turns the -0 of code 8 into the +0 the integer table gives
+        o[j + 16] = v.y * d + 0.f;
     }
 }
 

@@ -63,12 +63,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises *abort_flag) when it gives up or
 // when another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag) {
+// `where` identifies the waiter (role * 256 + stage or tile parity) and is what the status word receives.
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where) {
     for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
         if (mbar_try(a, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1;
+    atomicCAS(status, 0, where);
     return false;
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
@@ -179,7 +181,11 @@ __global__ void k_tc_plan(const int *__restrict__ goffs, int n_group, int m_tile
 template <int NA>
 struct TcCfg {
     static constexpr int STAGES = (NA == 2) ? 4 : 6;
-    static constexpr int A_BYTES = TC_M * 128;               // 16 KB per A operand per stage
+    static constexpr int A_BYTES = TC_M * 128;               // 16 KB of shared memory per A operand per stage
+    // What the A box signals on the mbarrier: the PACKED bytes read from global memory (64 B per row), not
+    // the 128 B per row it occupies after expansion.  Measured on B200: expecting 16 KB leaves the barrier
+    // pending for ever, expecting 8 KB completes it.
+    static constexpr int A_TX_BYTES = TC_M * 64;
     static constexpr int B_BYTES = TC_N * 128;               // 16 KB
     static constexpr int SF_BYTES = 512;
     static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + (NA + 1) * SF_BYTES;
@@ -240,11 +246,11 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
                 const TcTile t = tab[ti];
                 const int slabs = (t.nrows + 15) / 16;
-                const uint32_t tx = NA * Cfg::A_BYTES + slabs * 2048;
+                const uint32_t tx = NA * Cfg::A_TX_BYTES + slabs * 2048;
                 for (int ks = 0; ks < k_steps; ks++, it++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag))) break;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, tx);
                     tma_load_3d(sb, &mapA0, ks * TC_KSTEP, t.mt * TC_M, t.g, full0 + 8 * s);
@@ -263,12 +269,12 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
                 const TcTile t = tab[ti];
                 const int n_mma = max(16, (t.nrows + 15) & ~15);
                 // accumulators must have been drained by the epilogue of the previous tile
-                if (!(ok = mbar_wait(acc_empty, (tcount & 1) ^ 1, &abort_flag))) break;
+                if (!(ok = mbar_wait(acc_empty, (tcount & 1) ^ 1, &abort_flag, status, 0x200))) break;
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ks++, it++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag))) break;
+                    if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
                     tc_fence_after();
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     const uint32_t sf = sb + NA * Cfg::A_BYTES + Cfg::B_BYTES;
@@ -299,7 +305,7 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
         bool ok = true;
         for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
             const TcTile t = tab[ti];
-            if (!(ok = mbar_wait(acc_full, tcount & 1, &abort_flag))) break;
+            if (!(ok = mbar_wait(acc_full, tcount & 1, &abort_flag, status, 0x400))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;   // weight row (output feature) of this thread
             for (int c0 = 0; c0 < t.nrows; c0 += 32) {
@@ -359,7 +365,7 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
                     if (!ok) break;
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag))) break;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
                     uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
                     *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
                     if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
@@ -378,7 +384,7 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
     if (abort_flag) {
         // leave copies that may still be in flight time to land before the block retires
         for (int i = 0; i < 200; i++) __nanosleep(1000);
-        if (threadIdx.x == 0) atomicExch(status, 1);
+        if (threadIdx.x == 0) atomicCAS(status, 0, 1);
     }
     if (warp == 1) {
         tc_fence_after();

@@ -46,7 +46,8 @@ _SIGS = {
     "q36_moe_dispatch": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, u64, vp]),
     "q36_moe_quant_scatter": (i32, [vp, i32, vp, i32, i32, vp, vp, i32, i32, vp]),
     "q36_moe_ffn_ws_bytes": (u64, [i32, i32, i32, i32]),
-    "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, vp, u64, vp]),
+    "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32,
+                                        i32, vp, u64, vp]),
     "q36_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "q36_moe_workspace_bytes": (u64, [i32, i32, i32, i32, i32]),
     "q36_moe_ws_status": (i32, [vp, vp]),
@@ -70,7 +71,7 @@ class MoEError(RuntimeError):
 def check(rc: int, what: str = "") -> None:
     if rc != OK:
         msg = lib.q36_moe_strerror(rc).decode()
-        extra = f" (cudaError {lib.q36_moe_last_cuda_error()})" if rc == ECUDA else ""
+        extra = f" (code {lib.q36_moe_last_cuda_error()})" if rc in (ECUDA, EDEVICE) else ""
         raise MoEError(f"{what}: {msg}{extra}")
 
 
@@ -146,17 +147,25 @@ def quant_scatter(X: torch.Tensor, pos: torch.Tensor | None, k: int, shared_row0
 
 
 def expert_ffn_sorted(Wg, Wu, Wd, n_group: int, goffs: torch.Tensor, Xq: torch.Tensor, Xs: torch.Tensor,
-                      D: int, FF: int, path: int, sync_check: bool = True):
+                      D: int, FF: int, path: int, sync_check: bool = True, shared=None, soffs=None, stages: int = 3,
+                      bufs=None, ws=None):
+    """Grouped expert FFN over sorted rows.  shared = (Sg, Su, Sd) planes of the extra group whose rows are
+    [soffs[0], soffs[1]).  bufs = (Hq, Hs, Y) to reuse; returns (Hq, Hs, Y)."""
     R = Xq.shape[0]
     dev = Xq.device
-    Hq = torch.zeros((R, FF), dtype=torch.uint8, device=dev)
-    Hs = torch.zeros((R, FF // 32), dtype=torch.uint8, device=dev)
-    Y = torch.zeros((R, D), dtype=torch.float32, device=dev)
+    if bufs is None:
+        bufs = (torch.zeros((R, FF), dtype=torch.uint8, device=dev),
+                torch.zeros((R, FF // 32), dtype=torch.uint8, device=dev),
+                torch.zeros((R, D), dtype=torch.float32, device=dev))
+    Hq, Hs, Y = bufs
     wsb = int(lib.q36_moe_ffn_ws_bytes(n_group, R, D, FF))
-    ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
-    check(lib.q36_moe_expert_ffn_sorted(Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), n_group, goffs.data_ptr(), R,
-                                        Xq.data_ptr(), Xs.data_ptr(), Hq.data_ptr(), Hs.data_ptr(), Y.data_ptr(),
-                                        D, FF, path, ws.data_ptr(), wsb, stream_ptr()), "expert_ffn_sorted")
+    if ws is None:
+        ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+    Sg, Su, Sd = shared if shared is not None else (None, None, None)
+    check(lib.q36_moe_expert_ffn_sorted(Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), n_group, goffs.data_ptr(),
+                                        ptr(Sg), ptr(Su), ptr(Sd), ptr(soffs), R, Xq.data_ptr(), Xs.data_ptr(),
+                                        Hq.data_ptr(), Hs.data_ptr(), Y.data_ptr(), D, FF, path, stages, ws.data_ptr(),
+                                        ws.numel(), stream_ptr()), "expert_ffn_sorted")
     if path == PATH_TC and sync_check:
         check(lib.q36_moe_ws_status(ws.data_ptr(), stream_ptr()), "expert_ffn_sorted (device status)")
     return Hq, Hs, Y

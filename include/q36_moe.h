@@ -96,6 +96,28 @@ int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, in
                      int *ecount, int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes,
                      void *stream);
 
+/* No counterpart in the reference.  q36_moe_dispatch for callers that have no
+ * scratch to hand over and may not allocate any: code that runs in the
+ * engine's per-step path, where every buffer was sized and allocated once at
+ * engine creation (q36_engine.cu:1467-1512) and an allocation could
+ * synchronise the device in the middle of a step (the engine caches its own
+ * for that reason, q36_cuda.cu:285-287), or a host that only passes its input
+ * and output arrays through a fixed plugin signature.  The scratch is a
+ * 96 KiB array built into the library image (held by every GPU that loads the
+ * library until the process exits); the call allocates and frees nothing.
+ *   Limits: n_entries <= 16384, n_expert <= 512; larger sizes return
+ *   Q36_MOE_ENOSPACE with a message on stderr.
+ *   The first call on each device looks up the array's device address; make
+ *   that first call before starting any stream capture.
+ *   Every call shares the one array: two calls whose kernels overlap on the
+ *   GPU (different streams, no ordering between them) race on it.  Calls on
+ *   one stream, or otherwise ordered, are safe.  Nothing in the array needs
+ *   clearing between calls.
+ * Outputs are identical to q36_moe_dispatch's. */
+#define Q36_MOE_NOALLOC_MAX_ENTRIES 16384
+int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entries, int n_expert, int se0,
+                             int se1, int *ecount, int *eoffs, int *elist, int *pos, void *stream);
+
 /* Quantises X [T][K] and writes every token's row to the rows of the sorted
  * space that its entries occupy: for s < k row pos[t*k+s] (skipped when
  * negative) and, when shared_row0 >= 0, row shared_row0 + t.  Rows are

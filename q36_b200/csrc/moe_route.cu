@@ -1,4 +1,6 @@
 // Routing, deterministic dispatch and the activation quantiser.
+#include <stdio.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -232,3 +234,43 @@ int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K
 }
 
 }  // namespace q36
+
+// ------------------------------------------------- dispatch without a workspace
+// Scratch of q36_moe_dispatch_noalloc: the per-(chunk, expert) counters and the per-entry ranks of the three
+// dispatch kernels for at most Q36_MOE_NOALLOC_MAX_ENTRIES entries and 512 experts.  It lives in the library
+// image: every GPU that loads the library carries these 96 KiB until the process exits.
+static constexpr int NOALLOC_MAX_ENTRIES = 16384;
+static constexpr int NOALLOC_MAX_EXPERTS = q36::DISPATCH_MAX_E;
+static constexpr size_t NOALLOC_SCRATCH_INTS =
+    (size_t)(NOALLOC_MAX_ENTRIES / q36::DISPATCH_CHUNK) * NOALLOC_MAX_EXPERTS + NOALLOC_MAX_ENTRIES;
+static __device__ __align__(256) int g_noalloc_scratch[NOALLOC_SCRATCH_INTS];
+
+// Device address of the array above, looked up once per device.  In host code the symbol is only a
+// stand-in: kernels must be given the address cudaGetSymbolAddress returns for the CURRENT device.
+static int *g_noalloc_ptr[64] = {nullptr};
+
+extern "C" int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1,
+                                        int *ecount, int *eoffs, int *elist, int *pos, void *stream) {
+    if (!expert_of_entry || !ecount || !eoffs || !elist || !pos) return Q36_MOE_EINVAL;
+    if (n_entries < 0 || n_expert <= 0) return Q36_MOE_EINVAL;
+    if (n_entries > NOALLOC_MAX_ENTRIES || n_expert > NOALLOC_MAX_EXPERTS) {
+        fprintf(stderr,
+                "q36_moe_dispatch_noalloc: %d entries / %d experts exceed the built-in scratch (max %d entries, %d "
+                "experts); use q36_moe_dispatch with a caller workspace\n",
+                n_entries, n_expert, NOALLOC_MAX_ENTRIES, NOALLOC_MAX_EXPERTS);
+        return Q36_MOE_ENOSPACE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) { q36::last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    if (!g_noalloc_ptr[dev]) {   // first call on this device: resolve the array's device address
+        int *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) { q36::last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+        g_noalloc_ptr[dev] = p;
+    }
+    // Nothing in the scratch has to start at zero: k_dispatch_count writes every counter of every chunk it
+    // covers and the rank of every entry before the later kernels read them.
+    return q36::launch_dispatch(expert_of_entry, n_entries, n_expert, se0, se1, ecount, eoffs, elist, pos,
+                                g_noalloc_ptr[dev], nullptr, 0, 0, (cudaStream_t)stream);
+}

@@ -31,11 +31,15 @@ int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows,
 int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st);
 
 // moe_tc.cu
-int launch_gateup_tc(const void *Wg, const void *Wu, int n_group, const int *goffs, int R_max,
-                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF,
-                     void *ws, int *status, cudaStream_t st);
-int launch_down_tc(const void *Wd, int n_group, const int *goffs, int R_max, const uint8_t *Hq,
-                   const uint8_t *Hs, float *Y, int D, int FF, void *ws, int *status, cudaStream_t st);
-uint64_t tc_ws_bytes(int n_group, int R_max, int D, int FF);
+// One plan per grouped-FFN call (groups = n_group routed + the shared expert's when soffs != NULL), then the
+// gate/up and the down launch read it.  status: 4 ints, [0] gate/up, [1] down.
+uint64_t tc_ws_bytes();
+int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
+                   cudaStream_t st);
+int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
+                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
+                     int *status, cudaStream_t st);
+int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs,
+                   float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st);
 
 }  // namespace q36

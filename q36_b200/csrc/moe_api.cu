@@ -34,7 +34,7 @@ struct LayerWs {
     void *disp;
     uint8_t *Xq, *Xs, *Hq, *Hs;
     float *Y;
-    void *tc[4];
+    void *plan;
     uint64_t total;
 };
 static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
@@ -57,7 +57,7 @@ static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
     w.Hq = (uint8_t *)take(R * FF);
     w.Hs = (uint8_t *)take(R * (FF / Q36_QK));
     w.Y = (float *)take(R * D * 4);
-    for (int i = 0; i < 4; i++) w.tc[i] = take(tc_ws_bytes(i & 1 ? 1 : E, (int)R, D, FF));
+    w.plan = take(tc_ws_bytes());
     w.total = o;
     return w;
 }
@@ -98,13 +98,11 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
             return rc;
     } else {
-        if ((rc = launch_gateup_tc(Wg, Wu, ng, goffs, R, w.Xq, w.Xs, w.Hq, w.Hs, D, FF, w.tc[0], w.status + 0, st)))
+        if ((rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
+        if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, ng, R, w.Xq, w.Xs, w.Hq, w.Hs, D,
+                                   FF, w.plan, w.status + 0, st)))
             return rc;
-        if (shared && (rc = launch_gateup_tc(Sg, Su, 1, w.soffs, R, w.Xq, w.Xs, w.Hq, w.Hs, D, FF, w.tc[1],
-                                             w.status + 1, st)))
-            return rc;
-        if ((rc = launch_down_tc(Wd, ng, goffs, R, w.Hq, w.Hs, w.Y, D, FF, w.tc[2], w.status + 2, st))) return rc;
-        if (shared && (rc = launch_down_tc(Sd, 1, w.soffs, R, w.Hq, w.Hs, w.Y, D, FF, w.tc[3], w.status + 3, st)))
+        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, ng, R, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
             return rc;
     }
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
@@ -199,7 +197,8 @@ int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, i
 }
 
 uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) {
-    return 256 + 2 * al(tc_ws_bytes(n_group, R_max, D, FF)) + 2 * al(tc_ws_bytes(1, R_max, D, FF));
+    (void)n_group; (void)R_max; (void)D; (void)FF;
+    return 256 + tc_ws_bytes();
 }
 
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
@@ -224,25 +223,16 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     }
     if (!ws || ws_bytes < q36_moe_ffn_ws_bytes(n_group, R_max, D, FF)) return Q36_MOE_ENOSPACE;
     uint8_t *p = (uint8_t *)ws;
-    const uint64_t one = al(tc_ws_bytes(n_group, R_max, D, FF)), sh = al(tc_ws_bytes(1, R_max, D, FF));
     int *status = (int *)p;
+    void *plan = p + 256;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
-    if (stages & 1) {
-        if ((rc = launch_gateup_tc(Wg, Wu, n_group, goffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, p + 256,
-                                   status, st)))
-            return rc;
-        if (shared && (rc = launch_gateup_tc(Sg, Su, 1, soffs, R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF,
-                                             p + 256 + 2 * one, status + 1, st)))
-            return rc;
-    }
-    if (stages & 2) {
-        if ((rc = launch_down_tc(Wd, n_group, goffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + one, status + 2,
-                                 st)))
-            return rc;
-        if (shared && (rc = launch_down_tc(Sd, 1, soffs, R_max, Hq_rows, Hs_rows, Y_rows, D, FF, p + 256 + 2 * one + sh,
-                                           status + 3, st)))
-            return rc;
-    }
+    if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, st))) return rc;
+    if ((stages & 1) && (rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, n_group, R_max,
+                                               Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, plan, status, st)))
+        return rc;
+    if ((stages & 2) && (rc = launch_down_tc(Wd, shared ? Sd : nullptr, n_group, R_max, Hq_rows, Hs_rows, Y_rows, D, FF,
+                                             plan, status + 1, st)))
+        return rc;
     return Q36_MOE_OK;
 }
 
@@ -332,14 +322,15 @@ int q36_moe_tc_selftest(const uint8_t *A_codes_scales, const uint8_t *B_q, const
     // A_codes_scales: one "expert" of 128 rows in the split layout
     // [128][K/2] codes then [128][K/32] scales; Dout: [N][128] (token-major).
     if (!A_codes_scales || !B_q || !B_s || !Dout || !ws || N <= 0 || N > 4096 || K % 512) return Q36_MOE_EINVAL;
-    if (ws_bytes < 512 + tc_ws_bytes(1, N, 128, K)) return Q36_MOE_ENOSPACE;
+    if (ws_bytes < 512 + tc_ws_bytes()) return Q36_MOE_ENOSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     int h[2] = {0, N};
     int *goffs = (int *)((uint8_t *)ws + 256);
     int rc;
     if ((rc = ck(cudaMemsetAsync(ws, 0, 16, st)))) return rc;
     if ((rc = ck(cudaMemcpyAsync(goffs, h, sizeof h, cudaMemcpyHostToDevice, st)))) return rc;
-    if ((rc = launch_down_tc(A_codes_scales, 1, goffs, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws, st)))
+    if ((rc = launch_tc_plan(goffs, 1, nullptr, 128, K, (uint8_t *)ws + 512, (int *)ws, st))) return rc;
+    if ((rc = launch_down_tc(A_codes_scales, nullptr, 1, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws + 1, st)))
         return rc;
     return q36_moe_ws_status(ws, stream);
 }

@@ -33,12 +33,22 @@
 namespace q36 {
 
 constexpr int TC_M = 128;        // weight rows per tile (UMMA M)
-constexpr int TC_N = 128;        // token rows per tile (max UMMA N)
 constexpr int TC_KSTEP = 128;    // K elements per pipeline stage (= 128 B per row in smem)
 constexpr int TC_THREADS = 320;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 struct TcTile { int g, mt, row0, nrows; };
+
+// Work plan of one grouped-FFN call, built on the device by k_tc_plan and read by both MMA launches.
+// Groups are ranked by size (largest first); base[w][r] is the first tile of rank r for launch w
+// (0 = gate/up, 1 = down), so a tile index maps to (group, token tile, row tile) by a binary search.
+struct TcPlan {
+    int n_groups, n_tiles[2], pad;
+    int order[DISPATCH_MAX_GROUPS + 1];   // rank -> group
+    int row0[DISPATCH_MAX_GROUPS + 1];    // group -> first row of the sorted space
+    int cnt[DISPATCH_MAX_GROUPS + 1];     // group -> rows
+    int base[2][DISPATCH_MAX_GROUPS + 2];
+};
 
 // ------------------------------------------------------------------ PTX
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -135,98 +145,115 @@ __device__ __forceinline__ uint32_t idesc_mx(int n, int kb) {
            ((uint32_t)(TC_M >> 4) << 24) | ((uint32_t)kb << 29);
 }
 
-// ------------------------------------------------------------- tile plan
-// One block.  Orders the groups by size (largest first) and expands them into
-// (group, row-tile, token-tile) work items.
-__global__ void k_tc_plan(const int *__restrict__ goffs, int n_group, int m_tiles, TcTile *tab,
-                          int *n_tiles, int max_tiles, int *status) {
-    Q36_GDS();
-    __shared__ int cnt[DISPATCH_MAX_GROUPS], order[DISPATCH_MAX_GROUPS], base[DISPATCH_MAX_GROUPS + 1];
-    const int tid = threadIdx.x;
-    for (int g = tid; g < n_group; g += blockDim.x) cnt[g] = max(0, goffs[g + 1] - goffs[g]);
-    __syncthreads();
-    for (int g = tid; g < n_group; g += blockDim.x) {
-        int r = 0;
-        for (int h = 0; h < n_group; h++) r += (cnt[h] > cnt[g]) || (cnt[h] == cnt[g] && h < g);
-        order[r] = g;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        status[0] = 0;
-        int run = 0;
-        for (int r = 0; r < n_group; r++) {
-            base[r] = run;
-            run += ((cnt[order[r]] + TC_N - 1) / TC_N) * m_tiles;
-        }
-        base[n_group] = run;
-        *n_tiles = min(run, max_tiles);
-    }
-    __syncthreads();
-    for (int r = 0; r < n_group; r++) {
-        const int g = order[r], n = cnt[g];
-        const int nt = (n + TC_N - 1) / TC_N;
-        for (int i = tid; i < nt * m_tiles; i += blockDim.x) {
-            const int idx = base[r] + i;
-            if (idx < max_tiles) {
-                const int ti = i / m_tiles, mt = i % m_tiles;
-                tab[idx] = TcTile{g, mt, goffs[g] + ti * TC_N, min(TC_N, n - ti * TC_N)};
-            }
-        }
-    }
-}
-
-// ------------------------------------------------------------ main kernel
-// NA = 2: gate/up (two A operands, SwiGLU + E4M3 requantisation epilogue)
-// NA = 1: down (one A operand, f32 rows out)
+// ------------------------------------------------------------ configuration
+// NA = 2: gate/up (two A operands, SwiGLU + E4M3 requantisation epilogue), token tile 112
+// NA = 1: down (one A operand, f32 rows out), token tile 128
+// The token tile of gate/up is 112 so that TWO accumulator sets (gate + up each) and the scale
+// columns fit the 512 TMEM columns: the epilogue of one tile overlaps the MMAs of the next.
 template <int NA>
 struct TcCfg {
+    static constexpr int N = (NA == 2) ? 112 : 128;          // token rows per tile (max UMMA N)
     static constexpr int STAGES = (NA == 2) ? 4 : 6;
     static constexpr int A_BYTES = TC_M * 128;               // 16 KB of shared memory per A operand per stage
     // What the A box signals on the mbarrier: the PACKED bytes read from global memory (64 B per row), not
     // the 128 B per row it occupies after expansion.  Measured on B200: expecting 16 KB leaves the barrier
     // pending for ever, expecting 8 KB completes it.
     static constexpr int A_TX_BYTES = TC_M * 64;
-    static constexpr int B_BYTES = TC_N * 128;               // 16 KB
+    static constexpr int B_BYTES = 128 * 128;                // 16 KB slot (N rows used)
     static constexpr int SF_BYTES = 512;
     static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + (NA + 1) * SF_BYTES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-    static constexpr int ACC_COLS = NA * TC_N;               // accumulator columns per tile
-    static constexpr int SF_COL0 = ACC_COLS;                 // scale columns follow the accumulators
+    static constexpr int ACC_STRIDE = (NA == 2) ? 256 : 128; // TMEM columns between the two accumulator sets
+    static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // scale columns: A0 (4), [A1 (4)], B (4)
     static constexpr int TMEM_COLS = 512;
+    static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
 };
+
+// ------------------------------------------------------------- tile plan
+// One block.  Ranks the groups by size and lays the prefix sums of their tile counts.
+__global__ void __launch_bounds__(512)
+k_tc_plan(const int *__restrict__ goffs, int n_group, const int *__restrict__ soffs, TcPlan *plan, int mt_gu,
+          int mt_dn, int *status) {
+    Q36_GDS();
+    __shared__ int cnt[DISPATCH_MAX_GROUPS + 1], order[DISPATCH_MAX_GROUPS + 1], tg[DISPATCH_MAX_GROUPS + 1],
+        td[DISPATCH_MAX_GROUPS + 1];
+    const int tid = threadIdx.x;
+    const int G = n_group + (soffs ? 1 : 0);
+    for (int g = tid; g < G; g += blockDim.x) {
+        const int r0 = (g < n_group) ? goffs[g] : soffs[0];
+        const int r1 = (g < n_group) ? goffs[g + 1] : soffs[1];
+        cnt[g] = max(0, r1 - r0);
+        plan->row0[g] = r0;
+        plan->cnt[g] = cnt[g];
+    }
+    if (tid < 4) status[tid] = 0;
+    __syncthreads();
+    for (int g = tid; g < G; g += blockDim.x) {
+        int r = 0;
+        for (int h = 0; h < G; h++) r += (cnt[h] > cnt[g]) || (cnt[h] == cnt[g] && h < g);
+        order[r] = g;
+    }
+    __syncthreads();
+    for (int r = tid; r < G; r += blockDim.x) {
+        const int n = cnt[order[r]];
+        tg[r] = ((n + TcCfg<2>::N - 1) / TcCfg<2>::N) * mt_gu;
+        td[r] = ((n + TcCfg<1>::N - 1) / TcCfg<1>::N) * mt_dn;
+        plan->order[r] = order[r];
+    }
+    __syncthreads();
+    for (int r = tid; r <= G; r += blockDim.x) {
+        int a = 0, b = 0;
+        for (int h = 0; h < r; h++) { a += tg[h]; b += td[h]; }
+        plan->base[0][r] = a;
+        plan->base[1][r] = b;
+        if (r == G) { plan->n_tiles[0] = a; plan->n_tiles[1] = b; plan->n_groups = G; }
+    }
+}
+
+// ------------------------------------------------------------ main kernel
+struct TcMaps { CUtensorMap a0, a1, s0, s1, b16, bfull; };
 
 template <int NA>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
-              const __grid_constant__ CUtensorMap mapB,
-              const uint8_t *__restrict__ sfA0, const uint8_t *__restrict__ sfA1, uint64_t sfA_stride,
-              const uint8_t *__restrict__ sfB, const TcTile *__restrict__ tab, const int *__restrict__ n_tiles_p,
-              uint8_t *__restrict__ Hq, uint8_t *__restrict__ Hs, float *__restrict__ Y,
-              int M_total, int K, int *__restrict__ status) {
+k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ sfA0, const uint8_t *__restrict__ sfA1,
+              uint64_t sfA_stride, const uint8_t *__restrict__ sfS0, const uint8_t *__restrict__ sfS1, int n_routed,
+              const uint8_t *__restrict__ sfB, const TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
+              uint8_t *__restrict__ Hs, float *__restrict__ Y, int M_total, int K, int *__restrict__ status) {
     using Cfg = TcCfg<NA>;
+    constexpr int W = (NA == 2) ? 0 : 1;
     Q36_GDS();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    // bars: full[STAGES], empty[STAGES], acc_full, acc_empty
+    // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
+    __shared__ int s_order[DISPATCH_MAX_GROUPS + 1], s_row0[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1],
+        s_base[DISPATCH_MAX_GROUPS + 2];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::STAGES);
-    const uint32_t acc_full = smem_u32(bars + 2 * Cfg::STAGES), acc_empty = smem_u32(bars + 2 * Cfg::STAGES + 1);
-    const int n_tiles = *n_tiles_p;
+    const uint32_t acc_full0 = smem_u32(bars + 2 * Cfg::STAGES), acc_empty0 = smem_u32(bars + 2 * Cfg::STAGES + 2);
+    const int n_tiles = plan->n_tiles[W];
+    const int G = plan->n_groups;
     const int k_steps = K / TC_KSTEP;
     const int nb = K / Q36_QK;
+    const int m_tiles = M_total / TC_M;
 
+    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
+        s_base[i] = plan->base[W][i];
+        if (i < G) { s_order[i] = plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = plan->cnt[i]; }
+    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < Cfg::STAGES; s++) {
             mbar_init(full0 + 8 * s, 1 + 4);   // producer's expect_tx arrive + one arrive per scale warp
             mbar_init(empty0 + 8 * s, 1);      // tcgen05.commit
         }
-        mbar_init(acc_full, 1);                // tcgen05.commit
-        mbar_init(acc_empty, 4);               // one arrive per epilogue warp
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full0 + 8 * b, 1);   // tcgen05.commit
+            mbar_init(acc_empty0 + 8 * b, 4);  // one arrive per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -238,25 +265,45 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
 
+    // tile index -> work item: rank by binary search over the tile prefix sums, row tile fastest
+    auto get_tile = [&](int ti) {
+        int lo = 0, hi = G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_base[mid] <= ti) lo = mid; else hi = mid - 1;
+        }
+        const int g = s_order[lo], local = ti - s_base[lo];
+        const int nt = local / m_tiles, mt = local - nt * m_tiles;
+        return TcTile{g, mt, s_row0[g] + nt * Cfg::N, min(Cfg::N, s_cnt[g] - nt * Cfg::N)};
+    };
+
     if (warp == 0) {
         // ---------------------------------------------------- TMA producer
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
-                const TcTile t = tab[ti];
+                const TcTile t = get_tile(ti);
+                const bool sh = t.g >= n_routed;
+                const CUtensorMap *ma0 = sh ? &maps.s0 : &maps.a0, *ma1 = sh ? &maps.s1 : &maps.a1;
+                const int ge = sh ? 0 : t.g;
+                const bool full_box = t.nrows >= Cfg::B_FULL_MIN;
                 const int slabs = (t.nrows + 15) / 16;
-                const uint32_t tx = NA * Cfg::A_TX_BYTES + slabs * 2048;
+                const uint32_t tx = NA * Cfg::A_TX_BYTES + (full_box ? Cfg::N * 128 : slabs * 2048);
                 for (int ks = 0; ks < k_steps; ks++, it++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, tx);
-                    tma_load_3d(sb, &mapA0, ks * TC_KSTEP, t.mt * TC_M, t.g, full0 + 8 * s);
-                    if (NA == 2) tma_load_3d(sb + Cfg::A_BYTES, &mapA1, ks * TC_KSTEP, t.mt * TC_M, t.g, full0 + 8 * s);
-                    for (int i = 0; i < slabs; i++)
-                        tma_load_2d(sb + NA * Cfg::A_BYTES + i * 2048, &mapB, ks * TC_KSTEP, t.row0 + 16 * i, full0 + 8 * s);
+                    tma_load_3d(sb, ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                    if (NA == 2) tma_load_3d(sb + Cfg::A_BYTES, ma1, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                    if (full_box) {
+                        tma_load_2d(sb + NA * Cfg::A_BYTES, &maps.bfull, ks * TC_KSTEP, t.row0, full0 + 8 * s);
+                    } else {
+                        for (int i = 0; i < slabs; i++)
+                            tma_load_2d(sb + NA * Cfg::A_BYTES + i * 2048, &maps.b16, ks * TC_KSTEP, t.row0 + 16 * i, full0 + 8 * s);
+                    }
                 }
             }
         }
@@ -266,10 +313,12 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-                const TcTile t = tab[ti];
-                const int n_mma = max(16, (t.nrows + 15) & ~15);
-                // accumulators must have been drained by the epilogue of the previous tile
-                if (!(ok = mbar_wait(acc_empty, (tcount & 1) ^ 1, &abort_flag, status, 0x200))) break;
+                const TcTile t = get_tile(ti);
+                const int n_mma = (t.nrows >= Cfg::B_FULL_MIN) ? Cfg::N : max(16, (t.nrows + 15) & ~15);
+                const uint32_t buf = tcount & 1;
+                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE;
+                // this accumulator set must have been drained by the epilogue two tiles ago
+                if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
                 tc_fence_after();
                 for (int ks = 0; ks < k_steps; ks++, it++) {
                     const int s = it % Cfg::STAGES;
@@ -288,24 +337,25 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
                         const uint32_t id = idesc_mx(n_mma, kb);
                         const uint64_t bd = desc_sw128(sb + NA * Cfg::A_BYTES + kb * 32);
                         const uint32_t sfid = (uint32_t)kb << 30;
-                        tc_mma(tmem, desc_sw128(sb + kb * 32), bd, id, t_sfa0 | sfid, t_sfb | sfid, acc);
+                        tc_mma(d_tmem, desc_sw128(sb + kb * 32), bd, id, t_sfa0 | sfid, t_sfb | sfid, acc);
                         if (NA == 2)
-                            tc_mma(tmem + TC_N, desc_sw128(sb + Cfg::A_BYTES + kb * 32), bd, id, (t_sfa0 + 4) | sfid, t_sfb | sfid, acc);
+                            tc_mma(d_tmem + Cfg::N, desc_sw128(sb + Cfg::A_BYTES + kb * 32), bd, id, (t_sfa0 + 4) | sfid, t_sfb | sfid, acc);
                     }
                     tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
                 }
-                if (ok) tc_commit(acc_full);     // accumulators complete
+                if (ok) tc_commit(acc_full0 + 8 * buf);     // accumulators complete
             }
         }
     } else if (warp < 6) {
         // -------------------------------------------------------- epilogue
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
-        const uint32_t tq = tmem + ((uint32_t)(q * 32) << 16);
         uint32_t tcount = 0;
         bool ok = true;
         for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-            const TcTile t = tab[ti];
-            if (!(ok = mbar_wait(acc_full, tcount & 1, &abort_flag, status, 0x400))) break;
+            const TcTile t = get_tile(ti);
+            const uint32_t buf = tcount & 1;
+            const uint32_t tq = tmem + buf * Cfg::ACC_STRIDE + ((uint32_t)(q * 32) << 16);
+            if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;   // weight row (output feature) of this thread
             for (int c0 = 0; c0 < t.nrows; c0 += 32) {
@@ -313,7 +363,7 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
                 tc_ld32(tq + c0, g);
                 if (NA == 2) {
                     uint32_t u[32];
-                    tc_ld32(tq + TC_N + c0, u);
+                    tc_ld32(tq + Cfg::N + c0, u);
                     tc_ld_wait();
                     const int blk = mrow / Q36_QK;           // this warp's 32 rows are one scale block
                     const int nbh = M_total / Q36_QK;
@@ -337,44 +387,52 @@ k_grouped_mma(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty);
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
         }
     } else {
         // --------------------------------------------------- scale loaders
+        // Work items are (tile, group of 4 K-steps): one 16-byte load per operand row covers four stages.
+        // The loads of the NEXT item are issued before the current item waits for its stages.
         const int i = threadIdx.x - 6 * 32;      // 0..127: row of the tile
         const int w4 = i >> 5, m0 = i & 31;
         const uint32_t my_off = m0 * 16 + w4 * 4; // byte offset of this row's word in the 32x16 B image
+        const int groups = k_steps / 4;
+        const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+        auto fetch = [&](int ti, int kg, uint4 &a0, uint4 &a1, uint4 &b) {
+            const TcTile t = get_tile(ti);
+            const bool sh = t.g >= n_routed;
+            const size_t arow = (size_t)(sh ? 0 : t.g) * sfA_stride + (size_t)(t.mt * TC_M + i) * nb + 16 * kg;
+            a0 = __ldg(reinterpret_cast<const uint4 *>((sh ? sfS0 : sfA0) + arow));
+            a1 = ones;
+            if (NA == 2) a1 = __ldg(reinterpret_cast<const uint4 *>((sh ? sfS1 : sfA1) + arow));
+            b = ones;
+            if (i < t.nrows) b = __ldg(reinterpret_cast<const uint4 *>(sfB + (size_t)(t.row0 + i) * nb + 16 * kg));
+        };
         uint32_t it = 0;
         bool ok = true;
-        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
-            const TcTile t = tab[ti];
-            const uint8_t *ra0 = sfA0 + (size_t)t.g * sfA_stride + (size_t)(t.mt * TC_M + i) * nb;
-            const uint8_t *ra1 = (NA == 2) ? (sfA1 + (size_t)t.g * sfA_stride + (size_t)(t.mt * TC_M + i) * nb) : nullptr;
-            const bool bvalid = i < t.nrows;
-            const uint8_t *rb = sfB + (size_t)(t.row0 + (bvalid ? i : 0)) * nb;
-            for (int k4 = 0; k4 < k_steps; k4 += 4) {   // 16 scale bytes = 4 stages per load
-                const uint4 a0 = __ldg(reinterpret_cast<const uint4 *>(ra0 + 4 * k4));
-                uint4 a1 = make_uint4(0, 0, 0, 0);
-                if (NA == 2) a1 = __ldg(reinterpret_cast<const uint4 *>(ra1 + 4 * k4));
-                uint4 b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-                if (bvalid) b = __ldg(reinterpret_cast<const uint4 *>(rb + 4 * k4));
-                const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w},
-                               wb[4] = {b.x, b.y, b.z, b.w};
+        int ti = blockIdx.x, kg = 0;
+        uint4 a0, a1, b, na0 = ones, na1 = ones, nb4 = ones;
+        if (ti < n_tiles) fetch(ti, kg, a0, a1, b);
+        while (ti < n_tiles && ok) {
+            int nti = ti, nkg = kg + 1;
+            if (nkg == groups) { nkg = 0; nti = ti + gridDim.x; }
+            if (nti < n_tiles) fetch(nti, nkg, na0, na1, nb4);
+            const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w}, wb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-                for (int j = 0; j < 4; j++, it++) {
-                    if (!ok) break;
-                    const int s = it % Cfg::STAGES;
-                    const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
-                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
-                    *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
-                    if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
-                    *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(full0 + 8 * s);
-                }
+            for (int j = 0; j < 4; j++, it++) {
+                if (!ok) break;
+                const int s = it % Cfg::STAGES;
+                const uint32_t ph = (it / Cfg::STAGES) & 1;
+                if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
+                uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
+                *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
+                if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
+                *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
             }
+            a0 = na0; a1 = na1; b = nb4; ti = nti; kg = nkg;
         }
     }
 
@@ -420,13 +478,13 @@ static int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_
     if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
     return Q36_MOE_OK;
 }
-// activation rows: [R][K] bytes, boxes of 16 rows x 128 B
-static int make_map_rows(CUtensorMap *m, const void *base, int R, int K) {
+// activation rows: [R][K] bytes, boxes of box_rows rows x 128 B
+static int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)R};
     cuuint64_t strides[1] = {(cuuint64_t)K};
-    cuuint32_t box[2] = {128, 16}, el[2] = {1, 1};
+    cuuint32_t box[2] = {128, (cuuint32_t)box_rows}, el[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, el,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -445,51 +503,58 @@ static int sm_count() {
     return n;
 }
 
-// ws layout: [n_tiles int][pad to 64][tile table]; the status word lives with the caller
-static int tc_max_tiles(int n_group, int R_max, int m_tiles) { return ((R_max + TC_N - 1) / TC_N + n_group) * m_tiles; }
-uint64_t tc_ws_bytes(int n_group, int R_max, int D, int FF) {
-    const int mt = (D > FF ? D : FF) / TC_M;
-    return 64 + (uint64_t)tc_max_tiles(n_group, R_max, mt) * sizeof(TcTile);
+uint64_t tc_ws_bytes() { return (sizeof(TcPlan) + 255) & ~(uint64_t)255; }
+
+int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
+                   cudaStream_t st) {
+    if (n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    k_tc_plan<<<1, 512, 0, st>>>(goffs, n_group, soffs, (TcPlan *)plan, FF / TC_M, D / TC_M, status);
+    return check_launch();
 }
 
+// A0/A1: routed experts' planes (A1 unused for NA = 1); S0/S1: the shared expert's planes or NULL.
 template <int NA>
-static int run_grouped(const void *A0, const void *A1, int n_group, const int *goffs, int R_max, const uint8_t *Bq,
-                       const uint8_t *Bs, uint8_t *Hq, uint8_t *Hs, float *Y, int M, int K, void *ws, int *status,
-                       cudaStream_t st) {
+static int run_grouped(const void *A0, const void *A1, const void *S0, const void *S1, int n_group, int R_max,
+                       const uint8_t *Bq, const uint8_t *Bs, uint8_t *Hq, uint8_t *Hs, float *Y, int M, int K,
+                       const void *plan, int *status, cudaStream_t st) {
     using Cfg = TcCfg<NA>;
-    if (M % TC_M || K % (4 * TC_KSTEP) || n_group > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (M % TC_M || K % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK);
-    CUtensorMap mA0, mA1, mB;
+    const uint64_t plane = (uint64_t)M * (K / 2);
+    if (NA == 1) A1 = A0;
+    if (!S0) { S0 = A0; S1 = A1; }
+    if (NA == 1) S1 = S0;
+    TcMaps maps;
     int rc;
-    if ((rc = make_map_codes(&mA0, A0, M, K, n_group, estride))) return rc;
-    if ((rc = make_map_codes(&mA1, NA == 2 ? A1 : A0, M, K, n_group, estride))) return rc;
-    if ((rc = make_map_rows(&mB, Bq, R_max, K))) return rc;
-    int *n_tiles = (int *)ws;
-    TcTile *tab = (TcTile *)((uint8_t *)ws + 64);
-    const int m_tiles = M / TC_M;
-    const int max_tiles = tc_max_tiles(n_group, R_max, m_tiles);
-    k_tc_plan<<<1, 512, 0, st>>>(goffs, n_group, m_tiles, tab, n_tiles, max_tiles, status);
+    if ((rc = make_map_codes(&maps.a0, A0, M, K, n_group, estride))) return rc;
+    if ((rc = make_map_codes(&maps.a1, A1, M, K, n_group, estride))) return rc;
+    if ((rc = make_map_codes(&maps.s0, S0, M, K, 1, estride))) return rc;
+    if ((rc = make_map_codes(&maps.s1, S1, M, K, 1, estride))) return rc;
+    if ((rc = make_map_rows(&maps.b16, Bq, R_max, K, 16))) return rc;
+    if ((rc = make_map_rows(&maps.bfull, Bq, R_max, K, Cfg::N))) return rc;
     static bool attr_set[3] = {false, false, false};
     if (!attr_set[NA]) {
         if (cudaFuncSetAttribute(k_grouped_mma<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
             return check_launch();
         attr_set[NA] = true;
     }
-    const int grid = min(sm_count(), max_tiles);
+    const int m_tiles = M / TC_M;
+    const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
+    const int grid = (int)min((long)sm_count(), max_tiles);
     k_grouped_mma<NA><<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(
-        mA0, mA1, mB, (const uint8_t *)A0 + (uint64_t)M * (K / 2), (const uint8_t *)(NA == 2 ? A1 : A0) + (uint64_t)M * (K / 2),
-        estride, Bs, tab, n_tiles, Hq, Hs, Y, M, K, status);
+        maps, (const uint8_t *)A0 + plane, (const uint8_t *)A1 + plane, estride, (const uint8_t *)S0 + plane,
+        (const uint8_t *)S1 + plane, n_group, Bs, (const TcPlan *)plan, Hq, Hs, Y, M, K, status);
     return check_launch();
 }
 
-int launch_gateup_tc(const void *Wg, const void *Wu, int n_group, const int *goffs, int R_max, const uint8_t *Xq,
-                     const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, void *ws, int *status,
-                     cudaStream_t st) {
-    return run_grouped<2>(Wg, Wu, n_group, goffs, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, ws, status, st);
+int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
+                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
+                     int *status, cudaStream_t st) {
+    return run_grouped<2>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
 }
-int launch_down_tc(const void *Wd, int n_group, const int *goffs, int R_max, const uint8_t *Hq, const uint8_t *Hs,
-                   float *Y, int D, int FF, void *ws, int *status, cudaStream_t st) {
-    return run_grouped<1>(Wd, nullptr, n_group, goffs, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, ws, status, st);
+int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs,
+                   float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
+    return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
 }
 
 }  // namespace q36

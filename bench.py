@@ -291,7 +291,9 @@ def run_ours(args):
     if world == 1 and not args.no_prefill:
         prefill = bench_prefill(moe, synth, layers, args.prefill_tokens, bf16_peak, peak_kind, dev)
 
-    launches_per_layer = 8 if (stack is None) else stack.launches_per_layer
+    # kernels of this library per layer step at decode sizes: front (router+dispatch+plan), quantise-scatter,
+    # fused FFN, combine on the tensor-core path; front, quantise, gate/up, down, combine on the GEMV path
+    launches_per_layer = (4 if path != moe.PATH_GEMV else 5) if (stack is None) else stack.launches_per_layer
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -317,48 +319,83 @@ def run_ours(args):
 
 
 def roofline_decode(moe, layers, dX, dL, T, path, hbm_peak, peak_kind, dev):
-    """Times the gate/up and the down launch of every layer with CUDA events (cold weights: each layer is
-    distinct) and sets the algorithmic bytes of the launch against the duration."""
+    """Times the expert-FFN launch(es) of every layer with CUDA events on the launching stream (cold weights:
+    every layer is distinct) and sets the algorithmic bytes of a launch against its duration.  On the
+    tensor-core path at decode sizes gate/up and down are ONE persistent launch (k_ffn_fused_small); on the
+    GEMV path they are two and the gate/up launch (2/3 of the bytes) is the dominant kernel."""
     import torch
     NL = len(layers)
-    use = moe.PATH_GEMV if path in (moe.PATH_AUTO, moe.PATH_GEMV) and T < 14 else moe.PATH_TC
+    use = moe.PATH_GEMV if path == moe.PATH_GEMV else moe.PATH_TC
+    fused = use == moe.PATH_TC and T <= 16
     n, R = T * K8, T * (K8 + 1)
     soffs = torch.tensor([n, n + T], dtype=torch.int32, device=dev)
-    t_gu, t_dn, touched = [], [], []
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    bufs = wsb = None
-    for rep in range(2):
+    touched, staged = [], []
+    wsb = torch.empty(int(moe.lib.q36_moe_ffn_ws_bytes(E, R, D, FF)), dtype=torch.uint8, device=dev)
+    bufs = (torch.zeros((R, FF), dtype=torch.uint8, device=dev), torch.zeros((R, FF // 32), dtype=torch.uint8, device=dev),
+            torch.zeros((R, D), dtype=torch.float32, device=dev))
+    for l in range(NL):                                   # stage every layer's sorted rows once (untimed)
+        idx, wt = moe.router_topk(dL[l], E, K8)
+        ec, eo, el, pos = moe.dispatch(idx.reshape(-1), E)
+        Xq, Xs = moe.quant_scatter(dX[l], pos, K8, n, R)
+        staged.append((eo, Xq, Xs))
+        touched.append(int((ec > 0).sum().item()))
+
+    def run_stage(stages):
         for l in range(NL):
             ly = layers[l]
-            idx, wt = moe.router_topk(dL[l], E, K8)
-            ec, eo, el, pos = moe.dispatch(idx.reshape(-1), E)
-            Xq, Xs = moe.quant_scatter(dX[l], pos, K8, n, R)
-            args = dict(shared=(ly.Sg, ly.Su, ly.Sd), soffs=soffs, sync_check=False, bufs=bufs, ws=wsb)
-            torch.cuda.synchronize()
-            evs[0].record()
-            bufs = moe.expert_ffn_sorted(ly.Wg, ly.Wu, ly.Wd, E, eo, Xq, Xs, D, FF, use, stages=1, **args)
-            evs[1].record()
-            moe.expert_ffn_sorted(ly.Wg, ly.Wu, ly.Wd, E, eo, Xq, Xs, D, FF, use, stages=2, **{**args, "bufs": bufs})
-            evs[2].record()
-            torch.cuda.synchronize()
-            if rep == 1:
-                t_gu.append(evs[0].elapsed_time(evs[1]))
-                t_dn.append(evs[1].elapsed_time(evs[2]))
-                touched.append(int((ec > 0).sum().item()))
+            eo, Xq, Xs = staged[l]
+            moe.expert_ffn_sorted(ly.Wg, ly.Wu, ly.Wd, E, eo, Xq, Xs, D, FF, use, stages=stages, bufs=bufs, ws=wsb,
+                                  shared=(ly.Sg, ly.Su, ly.Sd), soffs=soffs, sync_check=False, max_group_rows=T)
+
+    def time_stage(stages):
+        """One CUDA graph with the launch of every layer back to back (no host gaps), replayed under events."""
+        run_stage(stages)
+        torch.cuda.synchronize()
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                run_stage(stages)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * NL)
+
+    if fused:
+        t_a, t_b = [time_stage(3)], [0.0]
+    else:
+        t_a, t_b = [time_stage(1)], [time_stage(2)]
+    if use == moe.PATH_TC:
+        moe.check(moe.lib.q36_moe_ws_status(wsb.data_ptr(), moe.stream_ptr()), "device status")
     U = sum(touched) / len(touched)                       # distinct routed experts touched per layer
-    gu_bytes = (U + 1) * (EXPERT_BYTES * 2 // 3) + R * (D + D // 32) + R * (FF + FF // 32)
-    dn_bytes = (U + 1) * (EXPERT_BYTES // 3) + R * (FF + FF // 32) + R * D * 4
-    gu_ms, dn_ms = sum(t_gu) / len(t_gu), sum(t_dn) / len(t_dn)
-    ach = gu_bytes / (gu_ms * 1e-3) / 1e9
+    x_bytes, h_bytes, y_bytes = R * (D + D // 32), R * (FF + FF // 32), R * D * 4
+    gu_bytes = (U + 1) * (EXPERT_BYTES * 2 // 3) + x_bytes + h_bytes
+    dn_bytes = (U + 1) * (EXPERT_BYTES // 3) + h_bytes + y_bytes
+    a_ms, b_ms = sum(t_a) / len(t_a), sum(t_b) / len(t_b)
+    extra = {"distinct_experts_per_layer": U}
+    if fused:
+        nbytes = gu_bytes + dn_bytes
+        ach = nbytes / (a_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": "k_ffn_fused_small (plan + gate/up + SwiGLU + down in one launch)",
+                "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
+                "bytes_per_launch": nbytes, "us_per_launch": a_ms * 1e3, "peak_kind": peak_kind,
+                "frac_of_8TBps_nominal": ach / 8000.0}
+        return roof, extra
+    ach = gu_bytes / (a_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": "k_gateup_gemv" if use == moe.PATH_GEMV else "k_grouped_mma<2>",
             "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
-            "bytes_per_launch": gu_bytes, "us_per_launch": gu_ms * 1e3, "peak_kind": peak_kind,
+            "bytes_per_launch": gu_bytes, "us_per_launch": a_ms * 1e3, "peak_kind": peak_kind,
             "frac_of_8TBps_nominal": ach / 8000.0}
-    ach_d = dn_bytes / (dn_ms * 1e-3) / 1e9
-    extra = {"roofline_down": {"bound": "hbm", "kernel": "k_down_gemv" if use == moe.PATH_GEMV else "k_grouped_mma<1>",
-                               "achieved": ach_d, "peak": hbm_peak, "unit": "GB/s", "frac": ach_d / hbm_peak,
-                               "bytes_per_launch": dn_bytes, "us_per_launch": dn_ms * 1e3},
-             "distinct_experts_per_layer": U}
+    ach_d = dn_bytes / (b_ms * 1e-3) / 1e9
+    extra["roofline_down"] = {"bound": "hbm", "kernel": "k_down_gemv" if use == moe.PATH_GEMV else "k_grouped_mma<1>",
+                              "achieved": ach_d, "peak": hbm_peak, "unit": "GB/s", "frac": ach_d / hbm_peak,
+                              "bytes_per_launch": dn_bytes, "us_per_launch": b_ms * 1e3}
     return roof, extra
 
 

@@ -146,13 +146,17 @@ uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
 /* Sg/Su/Sd (or NULL): one extra group, the shared expert, with its own planes
  * and the row range [soffs[0], soffs[1]) (device ints).  stages: bit 0 runs
  * gate/up + SwiGLU, bit 1 runs down; 3 = both (the intermediate Hq/Hs is the
- * hand-over, so the halves can be launched and timed separately). */
+ * hand-over, so the halves can be launched and timed separately).
+ * max_group_rows: an upper bound on the rows of any single group when the
+ * caller knows one (decode: the number of tokens), else 0.  With the
+ * tensor-core path, stages == 3 and a bound <= 16, gate/up and down run as
+ * ONE persistent launch. */
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group,
                               const int *goffs, const void *Sg, const void *Su, const void *Sd,
                               const int *soffs, int R_max, const uint8_t *Xq_rows,
                               const uint8_t *Xs_rows, uint8_t *Hq_rows, uint8_t *Hs_rows,
-                              float *Y_rows, int D, int FF, int path, int stages, void *ws,
-                              uint64_t ws_bytes, void *stream);
+                              float *Y_rows, int D, int FF, int path, int stages, int max_group_rows,
+                              void *ws, uint64_t ws_bytes, void *stream);
 
 /* k_moe_combine / k_moe_combine_pf (q36_engine.cu:785-791, 3393-3401):
  *   out[t][i] = sum_{s<k} wt[t][s] * Y_rows[pos[t*k+s]][i]          (pos >= 0)

@@ -12,13 +12,37 @@
 // Every kernel opens with this so that it may be launched with the
 // programmatic-dependent-launch attribute, as the reference's kernels are
 // (q36_ops.cuh:21-30); without the attribute it is a no-op.
-#define Q36_GDS() cudaGridDependencySynchronize()
+// The trigger lets the next kernel of the stream start launching while this one runs; the synchronise makes
+// this kernel wait for the complete previous grid before it touches global memory.
+#define Q36_GDS()                                \
+    do {                                         \
+        cudaTriggerProgrammaticLaunchCompletion(); \
+        cudaGridDependencySynchronize();         \
+    } while (0)
 
 namespace q36 {
 
 // Last CUDA error seen by an entry point of this thread (0 = none).
 int &last_cuda_error();
 int check_launch();  // cudaGetLastError() -> status code
+bool pdl_enabled();  // false when the environment variable Q36_NOPDL is set (as in the engine, q36_engine.cu:2251-2286)
+
+// Kernel launch with the programmatic-dependent-launch attribute: the launch may be processed while the
+// previous kernel of the stream is still running; every kernel waits in Q36_GDS() before its first access.
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // Smallest e2 with amax <= 448 * 2^e2, clamped to [-127,127]; 0 -> -127.
 // Integer form of ceil(log2(amax/448)) (q36_engine.cu:2421); 448 = 1.75 * 2^8.

@@ -1,5 +1,6 @@
 // Internal launcher prototypes shared by the translation units of libq36moe.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -16,6 +17,13 @@ int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *
                     int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st);
 int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K, const int *pos,
                  int k, int shared_row0, bool scatter, cudaStream_t st);
+
+// Router + dispatch (+ tensor-core work plan when plan != NULL, + quantise-and-scatter of X when X != NULL)
+// in one single-block launch; T * k <= 1024.
+int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
+                       int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
+                       void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
+                       int shared_row0, cudaStream_t st);
 
 // moe_gemv.cu
 // Sg/Su/Sd + soffs[2]: one extra group (the shared expert) with its own planes and row range, or NULL
@@ -37,9 +45,19 @@ uint64_t tc_ws_bytes();
 int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
                    cudaStream_t st);
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
-                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
+                     int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
                      int *status, cudaStream_t st);
-int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs,
+int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq, const uint8_t *Hs,
                    float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st);
+
+// host helpers of moe_tc.cu shared with moe_tc_fused.cu
+int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride);
+int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows);
+int sm_count();
+
+// moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
+int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                           const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
+                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st);
 
 }  // namespace q36

@@ -17,6 +17,11 @@ int check_launch() {
     if (e != cudaSuccess) { last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
     return Q36_MOE_OK;
 }
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) on = getenv("Q36_NOPDL") ? 0 : 1;
+    return on != 0;
+}
 static int ck(cudaError_t e) {
     if (e != cudaSuccess) { last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
     return Q36_MOE_OK;
@@ -64,9 +69,11 @@ static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
 
 static int pick_path(int path, int T) {
     if (path == Q36_MOE_PATH_GEMV || path == Q36_MOE_PATH_TC) return path;
-    // The engine switches from its GEMV kernels to its tiled kernels at 14
-    // rows (q36_engine.cu:2217-2221); the same threshold is the default here.
-    return (T < 14) ? Q36_MOE_PATH_GEMV : Q36_MOE_PATH_TC;
+    // The engine switches from its GEMV kernels to its tiled kernels at 14 rows (q36_engine.cu:2217-2221).
+    // Measured on B200 the tensor-core path is at least as fast at every T (its weight stream needs no ALU
+    // decode), so AUTO always takes it; the GEMV stays selectable.
+    (void)T;
+    return Q36_MOE_PATH_TC;
 }
 
 static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
@@ -83,27 +90,46 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     const bool shared = Sg && Su && Sd && inc_shared;
     const int n = T * k, R = T * (k + 1);
     int rc;
-    if ((rc = ck(cudaMemsetAsync(w.status, 0, 16, st)))) return rc;
-    if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
-    if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
-                              shared ? n + T : n, st)))
-        return rc;
-    if ((rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
+    const bool use_tc = pick_path(path, T) == Q36_MOE_PATH_TC;
+    const bool fused_front = n <= 1024;
+    const bool fused_quant = fused_front && T <= 2;     // beyond a couple of rows the scatter serialises inside one block: measured slower than a launch
+    if (fused_front) {
+        if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, se0, se1, w.idx, w.wt, w.ecount, w.eoffs,
+                                     w.elist, w.pos, w.soffs, n, shared ? n + T : n, use_tc ? w.plan : nullptr, D, FF,
+                                     w.status, fused_quant ? X : nullptr, x_is_bf16, w.Xq, w.Xs, shared ? n : -1, st)))
+            return rc;
+    } else {
+        if ((rc = ck(cudaMemsetAsync(w.status, 0, 16, st)))) return rc;
+        if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
+        if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
+                                  shared ? n + T : n, st)))
+            return rc;
+    }
+    if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
     const int ng = se1 - se0;
     const int *goffs = w.eoffs + se0;
-    if (pick_path(path, T) == Q36_MOE_PATH_GEMV) {
+    if (!use_tc) {
         if ((rc = launch_gateup_gemv(Wg, Wu, ng, goffs, shared ? Sg : nullptr, shared ? Su : nullptr, w.soffs, w.Xq,
                                      w.Xs, w.Hq, w.Hs, D, FF, st)))
             return rc;
         if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
             return rc;
     } else {
-        if ((rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
-        if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, ng, R, w.Xq, w.Xs, w.Hq, w.Hs, D,
-                                   FF, w.plan, w.status + 0, st)))
+        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st)))
             return rc;
-        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, ng, R, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+        static const bool no_fuse = getenv("Q36_NOFUSE") != nullptr;
+        if (T <= 16 && !no_fuse) {
+            // decode: gate/up and down in one persistent launch
+            if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
+                                             ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, st)))
+                return rc;
+        } else {
+        if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, ng, R, T, w.Xq, w.Xs, w.Hq, w.Hs,
+                                   D, FF, w.plan, w.status + 0, st)))
             return rc;
+        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, ng, R, T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+            return rc;
+        }
     }
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
     if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
@@ -204,8 +230,8 @@ uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) {
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
                               const void *Sg, const void *Su, const void *Sd, const int *soffs, int R_max,
                               const uint8_t *Xq_rows, const uint8_t *Xs_rows, uint8_t *Hq_rows, uint8_t *Hs_rows,
-                              float *Y_rows, int D, int FF, int path, int stages, void *ws, uint64_t ws_bytes,
-                              void *stream) {
+                              float *Y_rows, int D, int FF, int path, int stages, int max_group_rows, void *ws,
+                              uint64_t ws_bytes, void *stream) {
     if (!Wg || !Wu || !Wd || !goffs || !Xq_rows || !Xs_rows || !Hq_rows || !Hs_rows || !Y_rows) return Q36_MOE_EINVAL;
     if (n_group <= 0 || n_group > DISPATCH_MAX_GROUPS || D % 128 || FF % 128 || R_max <= 0) return Q36_MOE_EINVAL;
     if (!(stages & 3) || (path != Q36_MOE_PATH_GEMV && path != Q36_MOE_PATH_TC)) return Q36_MOE_EINVAL;
@@ -227,10 +253,14 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     void *plan = p + 256;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
     if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, st))) return rc;
+    if (stages == 3 && max_group_rows > 0 && max_group_rows <= 16)
+        return launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, n_group,
+                                      R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, st);
+    const int mgr = max_group_rows > 0 ? max_group_rows : R_max;
     if ((stages & 1) && (rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, n_group, R_max,
-                                               Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, plan, status, st)))
+                                               mgr, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, plan, status, st)))
         return rc;
-    if ((stages & 2) && (rc = launch_down_tc(Wd, shared ? Sd : nullptr, n_group, R_max, Hq_rows, Hs_rows, Y_rows, D, FF,
+    if ((stages & 2) && (rc = launch_down_tc(Wd, shared ? Sd : nullptr, n_group, R_max, mgr, Hq_rows, Hs_rows, Y_rows, D, FF,
                                              plan, status + 1, st)))
         return rc;
     return Q36_MOE_OK;
@@ -330,7 +360,7 @@ int q36_moe_tc_selftest(const uint8_t *A_codes_scales, const uint8_t *B_q, const
     if ((rc = ck(cudaMemsetAsync(ws, 0, 16, st)))) return rc;
     if ((rc = ck(cudaMemcpyAsync(goffs, h, sizeof h, cudaMemcpyHostToDevice, st)))) return rc;
     if ((rc = launch_tc_plan(goffs, 1, nullptr, 128, K, (uint8_t *)ws + 512, (int *)ws, st))) return rc;
-    if ((rc = launch_down_tc(A_codes_scales, nullptr, 1, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws + 1, st)))
+    if ((rc = launch_down_tc(A_codes_scales, nullptr, 1, N, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws + 1, st)))
         return rc;
     return q36_moe_ws_status(ws, stream);
 }

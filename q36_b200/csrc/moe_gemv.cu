@@ -242,6 +242,7 @@ __global__ void k_gather_rows(const uint4 *__restrict__ src, const int *__restri
 
 // split planes -> f32 rows: thread per 32-block (q36_dequant.cuh:106-113 on device)
 __global__ void k_dequant_mxfp4(const uint8_t *__restrict__ W, int M, int K, float *__restrict__ out) {
+    Q36_GDS();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const int nb = K / Q36_QK;
     if (i >= (long)M * nb) return;
@@ -265,7 +266,7 @@ int launch_gateup_gemv(const void *Wg, const void *Wu, int n_group, const int *g
     if (groups <= 0) return Q36_MOE_OK;
     if (FF % 32 || D % 32) return Q36_MOE_EINVAL;
     dim3 grid(FF / 32, groups);
-    k_gateup_gemv<<<grid, 256, 0, st>>>((const uint8_t *)Wg, (const uint8_t *)Wu, n_group, goffs,
+    launch_k(k_gateup_gemv, dim3(grid), dim3(256), 0, st, (const uint8_t *)Wg, (const uint8_t *)Wu, n_group, goffs,
                                         (const uint8_t *)Sg, (const uint8_t *)Su, soffs, Xq, Xs, Hq, Hs, D, FF);
     return check_launch();
 }
@@ -275,14 +276,14 @@ int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *
     if (groups <= 0) return Q36_MOE_OK;
     if (FF != 512 || D % 128) return Q36_MOE_EINVAL;   // lane -> (row, block) map below assumes 16 blocks per row
     dim3 grid(D / 128, groups);
-    k_down_gemv<<<grid, 256, 0, st>>>((const uint8_t *)Wd, n_group, goffs, (const uint8_t *)Sd, soffs, Hq, Hs, Y, D, FF);
+    launch_k(k_down_gemv, dim3(grid), dim3(256), 0, st, (const uint8_t *)Wd, n_group, goffs, (const uint8_t *)Sd, soffs, Hq, Hs, Y, D, FF);
     return check_launch();
 }
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
                    const float *shgate, int shgate_stride, int D, int k, int T, cudaStream_t st) {
     if (T <= 0) return Q36_MOE_OK;
     dim3 grid((D / 4 + 255) / 256, T);
-    k_combine<<<grid, 256, 0, st>>>(out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
+    launch_k(k_combine, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
     return check_launch();
 }
 int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
@@ -290,12 +291,12 @@ int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows,
     if (n_rows <= 0) return Q36_MOE_OK;
     const int row_u4 = row_bytes / 16;
     const long n = (long)n_rows * row_u4;
-    k_gather_rows<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint4 *)src, index, (uint4 *)dst, n_rows, row_u4);
+    launch_k(k_gather_rows, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const uint4 *)src, index, (uint4 *)dst, n_rows, row_u4);
     return check_launch();
 }
 int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st) {
     const long n = (long)M * (K / Q36_QK);
-    k_dequant_mxfp4<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const uint8_t *)W, M, K, out);
+    launch_k(k_dequant_mxfp4, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const uint8_t *)W, M, K, out);
     return check_launch();
 }
 

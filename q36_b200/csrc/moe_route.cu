@@ -3,6 +3,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tc_plan.cuh"
 
 namespace q36 {
 
@@ -150,18 +151,16 @@ __global__ void k_dispatch_place(const int *__restrict__ eid, int n, int n_exper
 // One warp per (row, 32-block), one lane per element, as k_quant_e4m3 does
 // (q36_engine.cu:2412-2428).  SCATTER = false: logical order into Xq[T][K].
 // SCATTER = true: hw order into every row of the sorted space the token feeds.
-template <bool BF16, bool SCATTER>
-__global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ Xq,
-                             uint8_t *__restrict__ Xs, int T, int K, const int *__restrict__ pos,
-                             int k, int shared_row0) {
-    Q36_GDS();
-    const int nb = K / Q36_QK;
-    const long gwarp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (gwarp >= (long)T * nb) return;
-    const int t = (int)(gwarp / nb), b = (int)(gwarp % nb);
+// one (row, 32-block) task of a warp: lane = element
+__device__ __forceinline__ float quant_load(const void *__restrict__ X, bool bf16, int t, int b, int K, int lane) {
     const size_t off = (size_t)t * K + (size_t)b * Q36_QK + lane;
-    const float v = BF16 ? __bfloat162float(((const __nv_bfloat16 *)X)[off]) : ((const float *)X)[off];
+    return bf16 ? __bfloat162float(((const __nv_bfloat16 *)X)[off]) : ((const float *)X)[off];
+}
+template <bool SCATTER>
+__device__ __forceinline__ void quant_task(float v, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int t, int b,
+                                           int K, const int *pos, int k, int shared_row0, int lane) {
+    const int nb = K / Q36_QK;
+    const size_t off = (size_t)t * K + (size_t)b * Q36_QK + lane;
     const float a = warp_max(fabsf(v));
     const int e2 = e2_of_amax(a);
     const uint8_t q = f32_to_e4m3(v * inv_scale_of_e2(e2));
@@ -194,11 +193,131 @@ __global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ X
     }
 }
 
+template <bool BF16, bool SCATTER>
+__global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ Xq,
+                             uint8_t *__restrict__ Xs, int T, int K, const int *__restrict__ pos,
+                             int k, int shared_row0) {
+    Q36_GDS();
+    const int nb = K / Q36_QK;
+    const long gwarp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gwarp >= (long)T * nb) return;
+    const int t = (int)(gwarp / nb), b = (int)(gwarp % nb);
+    quant_task<SCATTER>(quant_load(X, BF16, t, b, K, lane), Xq, Xs, t, b, K, pos, k, shared_row0, lane);
+}
+
+// ------------------------------------------------- fused front end, small T
+// Decode-sized steps spend more time launching the five small kernels above than running them, so for
+// T * k <= FRONT_MAX_ENTRIES one block does router -> dispatch -> (tensor-core work plan) in a single launch.
+// Same results as the separate kernels: the same route_row, the same stable order.
+constexpr int FRONT_MAX_ENTRIES = 1024;
+
+__global__ void __launch_bounds__(1024)
+k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
+              int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
+              int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1,
+              TcPlan *plan, int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16,
+              uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0) {
+    Q36_GDS();
+    __shared__ unsigned short cnt[FRONT_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // 32 KB
+    __shared__ int s_eoffs[DISPATCH_MAX_E + 1];
+    __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+    const int n = T * k;
+    const int used_warps = (n + 31) / 32;          // only the warps that own entries contribute counts
+    for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
+    if (status && tid < 4) status[tid] = 0;
+    for (int t = warp; t < T; t += nwarp) {
+        const float *l = logits + (size_t)t * row_stride;
+        int *ix = idx + (size_t)t * k;
+        float *w = wt + (size_t)t * k;
+        if (n_expert == 256) route_row<8>(l, k, ix, w, scale, 1, lane);
+        else if (n_expert == 128) route_row<4>(l, k, ix, w, scale, 1, lane);
+        else if (n_expert == 64) route_row<2>(l, k, ix, w, scale, 1, lane);
+        else route_row<1>(l, k, ix, w, scale, 1, lane);
+    }
+    __syncthreads();   // idx written by this block is visible to it after the barrier
+    int e = -1;
+    if (tid < n) {
+        e = idx[tid];
+        if (e < se0 || e >= se1 || e >= n_expert) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && r_in_warp == 0) cnt[warp][e] = (unsigned short)__popc(peers);
+    __syncthreads();
+    for (int x = tid; x < n_expert; x += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < used_warps; w++) {
+            const int c = cnt[w][x];
+            cnt[w][x] = (unsigned short)run;
+            run += c;
+        }
+        ecount[x] = run;
+        s_eoffs[x] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {   // exclusive scan of the expert totals: lane owns a contiguous run
+        const int per = (n_expert + 31) / 32;
+        int sum = 0;
+        for (int j = 0; j < per; j++) { const int x = lane * per + j; if (x < n_expert) sum += s_eoffs[x]; }
+        int incl = sum;
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+        int run = incl - sum;
+        for (int j = 0; j < per; j++) {
+            const int x = lane * per + j;
+            if (x < n_expert) { const int c = s_eoffs[x]; s_eoffs[x] = run; run += c; }
+        }
+        if (lane == 31) s_eoffs[n_expert] = run;
+    }
+    __syncthreads();
+    for (int x = tid; x <= n_expert; x += blockDim.x) eoffs[x] = s_eoffs[x];
+    if (tid == 0 && soffs) { soffs[0] = s0; soffs[1] = s1; }
+    if (tid < n) {
+        if (e >= 0) {
+            const int p = s_eoffs[e] + cnt[warp][e] + r_in_warp;
+            elist[p] = tid;
+            pos[tid] = p;
+        } else pos[tid] = -1;
+    }
+    // groups here hold at most T <= 128 rows, one or two token tiles: ranking by size would buy nothing
+    if (plan) tc_plan_block(s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, scratch, false);
+    if (X) {   // decode: quantise and scatter the T rows here as well (pos[] of this block is visible after the barrier)
+        __syncthreads();
+        const int nbk = D / Q36_QK;
+        const int ntask = T * nbk;
+        for (int base = warp; base < ntask; base += 8 * nwarp) {   // eight loads in flight per lane
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int task = base + j * nwarp;
+                v[j] = (task < ntask) ? quant_load(X, x_is_bf16 != 0, task / nbk, task % nbk, D, lane) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int task = base + j * nwarp;
+                if (task < ntask) quant_task<true>(v[j], Xq, Xs, task / nbk, task % nbk, D, pos, k, shared_row0, lane);
+            }
+        }
+    }
+}
+
+int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
+                       int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
+                       void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
+                       int shared_row0, cudaStream_t st) {
+    if (T * k > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E) return Q36_MOE_EINVAL;
+    launch_k(k_front_small, dim3(1), dim3(1024), 0, st, logits, n_expert, k, scale, T, row_stride, se0, se1, idx, wt,
+             ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D,
+             shared_row0);
+    return check_launch();
+}
+
 // -------------------------------------------------------------- launchers
 int launch_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale,
                        int renorm, int T, int row_stride, cudaStream_t st) {
     if (T <= 0) return Q36_MOE_OK;
-    k_router_topk<<<(T + 7) / 8, 256, 0, st>>>(logits, n_expert, k, idx, wt, scale, renorm, T, row_stride);
+    launch_k(k_router_topk, dim3((T + 7) / 8), dim3(256), 0, st, logits, n_expert, k, idx, wt, scale, renorm, T, row_stride);
     return check_launch();
 }
 
@@ -212,9 +331,9 @@ int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *
     const int n_chunk = (n + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
     int *chunk_cnt = (int *)ws;
     int *lrank = chunk_cnt + (size_t)n_chunk * n_expert;
-    if (n > 0) k_dispatch_count<<<n_chunk, DISPATCH_CHUNK, 0, st>>>(eid, n, n_expert, se0, se1, chunk_cnt, lrank);
-    k_dispatch_scan<<<1, 256, 0, st>>>(chunk_cnt, n_chunk, n_expert, ecount, eoffs, soffs, s0, s1);
-    if (n > 0) k_dispatch_place<<<(n + 255) / 256, 256, 0, st>>>(eid, n, n_expert, chunk_cnt, lrank, eoffs, elist, pos);
+    if (n > 0) launch_k(k_dispatch_count, dim3(n_chunk), dim3(DISPATCH_CHUNK), 0, st, eid, n, n_expert, se0, se1, chunk_cnt, lrank);
+    launch_k(k_dispatch_scan, dim3(1), dim3(256), 0, st, chunk_cnt, n_chunk, n_expert, ecount, eoffs, soffs, s0, s1);
+    if (n > 0) launch_k(k_dispatch_place, dim3((n + 255) / 256), dim3(256), 0, st, eid, n, n_expert, chunk_cnt, lrank, eoffs, elist, pos);
     return check_launch();
 }
 
@@ -224,11 +343,11 @@ int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K
     const long warps = (long)T * (K / Q36_QK);
     const unsigned grid = (unsigned)((warps + 7) / 8);
     if (scatter) {
-        if (bf16) k_quant_e4m3<true, true><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, pos, k, shared_row0);
-        else k_quant_e4m3<false, true><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, pos, k, shared_row0);
+        if (bf16) launch_k(k_quant_e4m3<true, true>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
+        else launch_k(k_quant_e4m3<false, true>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
     } else {
-        if (bf16) k_quant_e4m3<true, false><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, nullptr, 0, -1);
-        else k_quant_e4m3<false, false><<<grid, 256, 0, st>>>(X, Xq, Xs, T, K, nullptr, 0, -1);
+        if (bf16) launch_k(k_quant_e4m3<true, false>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, nullptr, 0, -1);
+        else launch_k(k_quant_e4m3<false, false>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, nullptr, 0, -1);
     }
     return check_launch();
 }

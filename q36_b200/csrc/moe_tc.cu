@@ -29,197 +29,59 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tc_plan.cuh"
+#include "tc_ptx.cuh"
 
 namespace q36 {
-
-constexpr int TC_M = 128;        // weight rows per tile (UMMA M)
-constexpr int TC_KSTEP = 128;    // K elements per pipeline stage (= 128 B per row in smem)
-constexpr int TC_THREADS = 320;
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
-
-struct TcTile { int g, mt, row0, nrows; };
-
-// Work plan of one grouped-FFN call, built on the device by k_tc_plan and read by both MMA launches.
-// Groups are ranked by size (largest first); base[w][r] is the first tile of rank r for launch w
-// (0 = gate/up, 1 = down), so a tile index maps to (group, token tile, row tile) by a binary search.
-struct TcPlan {
-    int n_groups, n_tiles[2], pad;
-    int order[DISPATCH_MAX_GROUPS + 1];   // rank -> group
-    int row0[DISPATCH_MAX_GROUPS + 1];    // group -> first row of the sorted space
-    int cnt[DISPATCH_MAX_GROUPS + 1];     // group -> rows
-    int base[2][DISPATCH_MAX_GROUPS + 2];
-};
-
-// ------------------------------------------------------------------ PTX
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t a) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(a), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (and raises *abort_flag) when it gives up or
-// when another role already gave up.
-// `where` identifies the waiter (role * 256 + stage or tile parity) and is what the status word receives.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
-        if (mbar_try(a, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0, where);
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *m, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
-                                       uint32_t sfb, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128B-swizzled operand tile (rows of 128 B, 8-row groups 1024 B
-// apart): start address, LBO 1 (unused for swizzled K-major), SBO 1024 B,
-// descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// Scale-factor image for tcgen05.cp: 32 rows x 16 B, no swizzle, 8-row core
-// matrices 128 B apart.
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-// Block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), both
-// K-major, UE8M0 scales, M = 128, N = n; scale-factor byte ids select which
-// of the four K-blocks of a 32-bit TMEM scale column this MMA uses.
-__device__ __forceinline__ uint32_t idesc_mx(int n, int kb) {
-    return ((uint32_t)kb << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) |
-           ((uint32_t)(TC_M >> 4) << 24) | ((uint32_t)kb << 29);
-}
 
 // ------------------------------------------------------------ configuration
 // NA = 2: gate/up (two A operands, SwiGLU + E4M3 requantisation epilogue), token tile 112
 // NA = 1: down (one A operand, f32 rows out), token tile 128
 // The token tile of gate/up is 112 so that TWO accumulator sets (gate + up each) and the scale
 // columns fit the 512 TMEM columns: the epilogue of one tile overlaps the MMAs of the next.
-template <int NA>
+// SMALL: every group has at most 16 rows (decode).  The B slot shrinks to one 16-row box, which buys two
+// (gate/up) or four (down) more pipeline stages: at decode the kernel is a pure weight stream and the bytes
+// in flight per SM are what bounds it.
+template <int NA, bool SMALL>
 struct TcCfg {
-    static constexpr int N = (NA == 2) ? 112 : 128;          // token rows per tile (max UMMA N)
-    static constexpr int STAGES = (NA == 2) ? 4 : 6;
+    static constexpr int N = (NA == 2) ? TC_N_GATEUP : TC_N_DOWN;   // token rows per tile (max UMMA N)
+    static constexpr int STAGES = SMALL ? ((NA == 2) ? 6 : 10) : ((NA == 2) ? 4 : 6);
     static constexpr int A_BYTES = TC_M * 128;               // 16 KB of shared memory per A operand per stage
     // What the A box signals on the mbarrier: the PACKED bytes read from global memory (64 B per row), not
     // the 128 B per row it occupies after expansion.  Measured on B200: expecting 16 KB leaves the barrier
     // pending for ever, expecting 8 KB completes it.
     static constexpr int A_TX_BYTES = TC_M * 64;
-    static constexpr int B_BYTES = 128 * 128;                // 16 KB slot (N rows used)
+    static constexpr int B_BYTES = SMALL ? 16 * 128 : 128 * 128;   // slot for N rows (2 KB or 16 KB)
     static constexpr int SF_BYTES = 512;
-    static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + (NA + 1) * SF_BYTES;
+    // operand tiles are 128B-swizzled: every stage starts on a 1024-byte boundary
+    static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + ((NA + 1) * SF_BYTES + 1023) / 1024 * 1024;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int ACC_STRIDE = (NA == 2) ? 256 : 128; // TMEM columns between the two accumulator sets
     static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // scale columns: A0 (4), [A1 (4)], B (4)
     static constexpr int TMEM_COLS = 512;
-    static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
+    static constexpr int B_FULL_MIN = SMALL ? (1 << 30) : 49;   // token tiles of at least this many rows use one big box
 };
 
 // ------------------------------------------------------------- tile plan
-// One block.  Ranks the groups by size and lays the prefix sums of their tile counts.
 __global__ void __launch_bounds__(512)
 k_tc_plan(const int *__restrict__ goffs, int n_group, const int *__restrict__ soffs, TcPlan *plan, int mt_gu,
           int mt_dn, int *status) {
     Q36_GDS();
-    __shared__ int cnt[DISPATCH_MAX_GROUPS + 1], order[DISPATCH_MAX_GROUPS + 1], tg[DISPATCH_MAX_GROUPS + 1],
-        td[DISPATCH_MAX_GROUPS + 1];
-    const int tid = threadIdx.x;
-    const int G = n_group + (soffs ? 1 : 0);
-    for (int g = tid; g < G; g += blockDim.x) {
-        const int r0 = (g < n_group) ? goffs[g] : soffs[0];
-        const int r1 = (g < n_group) ? goffs[g + 1] : soffs[1];
-        cnt[g] = max(0, r1 - r0);
-        plan->row0[g] = r0;
-        plan->cnt[g] = cnt[g];
-    }
-    if (tid < 4) status[tid] = 0;
-    __syncthreads();
-    for (int g = tid; g < G; g += blockDim.x) {
-        int r = 0;
-        for (int h = 0; h < G; h++) r += (cnt[h] > cnt[g]) || (cnt[h] == cnt[g] && h < g);
-        order[r] = g;
-    }
-    __syncthreads();
-    for (int r = tid; r < G; r += blockDim.x) {
-        const int n = cnt[order[r]];
-        tg[r] = ((n + TcCfg<2>::N - 1) / TcCfg<2>::N) * mt_gu;
-        td[r] = ((n + TcCfg<1>::N - 1) / TcCfg<1>::N) * mt_dn;
-        plan->order[r] = order[r];
-    }
-    __syncthreads();
-    for (int r = tid; r <= G; r += blockDim.x) {
-        int a = 0, b = 0;
-        for (int h = 0; h < r; h++) { a += tg[h]; b += td[h]; }
-        plan->base[0][r] = a;
-        plan->base[1][r] = b;
-        if (r == G) { plan->n_tiles[0] = a; plan->n_tiles[1] = b; plan->n_groups = G; }
-    }
+    __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
+    if (threadIdx.x < 4) status[threadIdx.x] = 0;
+    tc_plan_block(goffs, n_group, soffs != nullptr, soffs ? soffs[0] : 0, soffs ? soffs[1] : 0, plan, mt_gu, mt_dn, scratch, true);
 }
 
 // ------------------------------------------------------------ main kernel
 struct TcMaps { CUtensorMap a0, a1, s0, s1, b16, bfull; };
 
-template <int NA>
+template <int NA, bool SMALL>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ sfA0, const uint8_t *__restrict__ sfA1,
               uint64_t sfA_stride, const uint8_t *__restrict__ sfS0, const uint8_t *__restrict__ sfS1, int n_routed,
               const uint8_t *__restrict__ sfB, const TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
               uint8_t *__restrict__ Hs, float *__restrict__ Y, int M_total, int K, int *__restrict__ status) {
-    using Cfg = TcCfg<NA>;
+    using Cfg = TcCfg<NA, SMALL>;
     constexpr int W = (NA == 2) ? 0 : 1;
     Q36_GDS();
     extern __shared__ uint8_t smem_raw[];
@@ -466,7 +328,7 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 // code plane of n_group experts: [n_group][M][K] 4-bit elements
-static int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride) {
+int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, (cuuint64_t)n_group};
@@ -479,7 +341,7 @@ static int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_
     return Q36_MOE_OK;
 }
 // activation rows: [R][K] bytes, boxes of box_rows rows x 128 B
-static int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows) {
+int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)R};
@@ -492,7 +354,7 @@ static int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box
     return Q36_MOE_OK;
 }
 
-static int sm_count() {
+int sm_count() {
     static int n = 0;
     if (!n) {
         int dev = 0;
@@ -508,16 +370,16 @@ uint64_t tc_ws_bytes() { return (sizeof(TcPlan) + 255) & ~(uint64_t)255; }
 int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
                    cudaStream_t st) {
     if (n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
-    k_tc_plan<<<1, 512, 0, st>>>(goffs, n_group, soffs, (TcPlan *)plan, FF / TC_M, D / TC_M, status);
+    launch_k(k_tc_plan, dim3(1), dim3(512), 0, st, goffs, n_group, soffs, (TcPlan *)plan, FF / TC_M, D / TC_M, status);
     return check_launch();
 }
 
 // A0/A1: routed experts' planes (A1 unused for NA = 1); S0/S1: the shared expert's planes or NULL.
-template <int NA>
+template <int NA, bool SMALL>
 static int run_grouped(const void *A0, const void *A1, const void *S0, const void *S1, int n_group, int R_max,
                        const uint8_t *Bq, const uint8_t *Bs, uint8_t *Hq, uint8_t *Hs, float *Y, int M, int K,
                        const void *plan, int *status, cudaStream_t st) {
-    using Cfg = TcCfg<NA>;
+    using Cfg = TcCfg<NA, SMALL>;
     if (M % TC_M || K % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK);
     const uint64_t plane = (uint64_t)M * (K / 2);
@@ -532,29 +394,34 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     if ((rc = make_map_codes(&maps.s1, S1, M, K, 1, estride))) return rc;
     if ((rc = make_map_rows(&maps.b16, Bq, R_max, K, 16))) return rc;
     if ((rc = make_map_rows(&maps.bfull, Bq, R_max, K, Cfg::N))) return rc;
-    static bool attr_set[3] = {false, false, false};
-    if (!attr_set[NA]) {
-        if (cudaFuncSetAttribute(k_grouped_mma<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+    static bool attr_set = false;   // one per (NA, SMALL) instantiation
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(k_grouped_mma<NA, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
             return check_launch();
-        attr_set[NA] = true;
+        attr_set = true;
     }
     const int m_tiles = M / TC_M;
     const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
     const int grid = (int)min((long)sm_count(), max_tiles);
-    k_grouped_mma<NA><<<grid, TC_THREADS, Cfg::SMEM_BYTES, st>>>(
+    launch_k(k_grouped_mma<NA, SMALL>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM_BYTES, st, 
         maps, (const uint8_t *)A0 + plane, (const uint8_t *)A1 + plane, estride, (const uint8_t *)S0 + plane,
         (const uint8_t *)S1 + plane, n_group, Bs, (const TcPlan *)plan, Hq, Hs, Y, M, K, status);
     return check_launch();
 }
 
+// max_group_rows: an upper bound on the rows of any one group (<= 16 selects the deep-pipeline variant)
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
-                     const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
-                     int *status, cudaStream_t st) {
-    return run_grouped<2>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
+                     int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF,
+                     const void *plan, int *status, cudaStream_t st) {
+    if (max_group_rows <= 16)
+        return run_grouped<2, true>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
+    return run_grouped<2, false>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
 }
-int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs,
-                   float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
-    return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
+int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq,
+                   const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
+    if (max_group_rows <= 16)
+        return run_grouped<1, true>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
+    return run_grouped<1, false>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
 }
 
 }  // namespace q36

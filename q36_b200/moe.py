@@ -48,7 +48,7 @@ _SIGS = {
     "q36_moe_quant_scatter": (i32, [vp, i32, vp, i32, i32, vp, vp, i32, i32, vp]),
     "q36_moe_ffn_ws_bytes": (u64, [i32, i32, i32, i32]),
     "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32,
-                                        i32, vp, u64, vp]),
+                                        i32, i32, vp, u64, vp]),
     "q36_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "q36_moe_workspace_bytes": (u64, [i32, i32, i32, i32, i32]),
     "q36_moe_ws_status": (i32, [vp, vp]),
@@ -149,7 +149,7 @@ def quant_scatter(X: torch.Tensor, pos: torch.Tensor | None, k: int, shared_row0
 
 def expert_ffn_sorted(Wg, Wu, Wd, n_group: int, goffs: torch.Tensor, Xq: torch.Tensor, Xs: torch.Tensor,
                       D: int, FF: int, path: int, sync_check: bool = True, shared=None, soffs=None, stages: int = 3,
-                      bufs=None, ws=None):
+                      bufs=None, ws=None, max_group_rows: int = 0):
     """Grouped expert FFN over sorted rows.  shared = (Sg, Su, Sd) planes of the extra group whose rows are
     [soffs[0], soffs[1]).  bufs = (Hq, Hs, Y) to reuse; returns (Hq, Hs, Y)."""
     R = Xq.shape[0]
@@ -165,8 +165,8 @@ def expert_ffn_sorted(Wg, Wu, Wd, n_group: int, goffs: torch.Tensor, Xq: torch.T
     Sg, Su, Sd = shared if shared is not None else (None, None, None)
     check(lib.q36_moe_expert_ffn_sorted(Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), n_group, goffs.data_ptr(),
                                         ptr(Sg), ptr(Su), ptr(Sd), ptr(soffs), R, Xq.data_ptr(), Xs.data_ptr(),
-                                        Hq.data_ptr(), Hs.data_ptr(), Y.data_ptr(), D, FF, path, stages, ws.data_ptr(),
-                                        ws.numel(), stream_ptr()), "expert_ffn_sorted")
+                                        Hq.data_ptr(), Hs.data_ptr(), Y.data_ptr(), D, FF, path, stages, max_group_rows,
+                                        ws.data_ptr(), ws.numel(), stream_ptr()), "expert_ffn_sorted")
     if path == PATH_TC and sync_check:
         check(lib.q36_moe_ws_status(ws.data_ptr(), stream_ptr()), "expert_ffn_sorted (device status)")
     return Hq, Hs, Y

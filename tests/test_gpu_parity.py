@@ -211,10 +211,30 @@ def _check_layer(moe, oracle, torch, layer, weights, T, path, rng, zipf=False, s
     return out
 
 
-@pytest.mark.parametrize("T", [1, 2, 4, 8])
-def test_decode_layer_vs_oracle(moe, oracle, torch_cuda, layer, weights, T):
-    """Config 1 of the benchmark: T = 1, 2, 4, 8 tokens, 256 + 1 experts, top-8."""
-    _check_layer(moe, oracle, torch_cuda, layer, weights, T, moe.PATH_GEMV, np.random.default_rng(40 + T))
+@pytest.mark.parametrize("path", ["gemv", "tc"])
+@pytest.mark.parametrize("T", [1, 2, 4, 8, 16])
+def test_decode_layer_vs_oracle(moe, oracle, torch_cuda, layer, weights, T, path):
+    """Config 1 of the benchmark: T = 1, 2, 4, 8 tokens, 256 + 1 experts, top-8 -- on the streaming GEMV and
+    on the fused tcgen05 decode kernel (gate/up + down in one persistent launch)."""
+    p = moe.PATH_GEMV if path == "gemv" else moe.PATH_TC
+    _check_layer(moe, oracle, torch_cuda, layer, weights, T, p, np.random.default_rng(40 + T))
+
+
+def test_decode_paths_agree_and_repeat(moe, oracle, torch_cuda, layer, weights):
+    """The fused decode kernel hands its intermediate from SM to SM through global memory: run it many times
+    on the same input; every run must give the same bits, and the GEMV path must agree closely."""
+    torch = torch_cuda
+    rng = np.random.default_rng(3)
+    T = 8
+    xt = torch.from_numpy(synth.activations(rng, T)).cuda().to(torch.bfloat16)
+    lt = torch.from_numpy(synth.router_logits(rng, T, E)).cuda()
+    ref = layer.forward(xt, lt, path=moe.PATH_TC).clone()
+    for _ in range(20):
+        out = layer.forward(xt, lt, path=moe.PATH_TC)
+        assert torch.equal(out, ref)
+    layer.check_device_status()
+    g = layer.forward(xt, lt, path=moe.PATH_GEMV)
+    assert rel_l2(g.cpu().numpy(), ref.cpu().numpy()) < 2e-3
 
 
 def test_layer_host_buffers_and_f32_input(moe, oracle, torch_cuda, layer, weights):

@@ -270,31 +270,46 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
             b = ones;
             if (i < t.nrows) b = __ldg(reinterpret_cast<const uint4 *>(sfB + (size_t)(t.row0 + i) * nb + 16 * kg));
         };
-        uint32_t it = 0;
-        bool ok = true;
-        int ti = blockIdx.x, kg = 0;
-        uint4 a0, a1, b, na0 = ones, na1 = ones, nb4 = ones;
-        if (ti < n_tiles) fetch(ti, kg, a0, a1, b);
-        while (ti < n_tiles && ok) {
-            int nti = ti, nkg = kg + 1;
-            if (nkg == groups) { nkg = 0; nti = ti + gridDim.x; }
-            if (nti < n_tiles) fetch(nti, nkg, na0, na1, nb4);
-            const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        // The scale bytes are cold 16-byte loads from HBM (2-3 us under load) and every stage waits for them:
+        // the loads run PF items ahead of the fills in a register ring (one item ahead left the loaders, not
+        // the tensor pipe, setting the pace).
+        constexpr int PF = 4;
+        uint4 qa0[PF], qa1[PF], qb[PF];
+        bool qvalid[PF];
+        int pti = blockIdx.x, pkg = 0;
+        auto issue = [&](int k) {
+            qvalid[k] = pti < n_tiles;
+            if (!qvalid[k]) return;
+            fetch(pti, pkg, qa0[k], qa1[k], qb[k]);
+            if (++pkg == groups) { pkg = 0; pti += gridDim.x; }
+        };
 #pragma unroll
-            for (int j = 0; j < 4; j++, it++) {
+        for (int k = 0; k < PF; k++) issue(k);
+        uint32_t it = 0;
+        bool ok = true, running = true;
+        while (running && ok) {
+#pragma unroll
+            for (int k = 0; k < PF; k++) {
+                if (!qvalid[k]) { running = false; break; }
+                const uint32_t wa0[4] = {qa0[k].x, qa0[k].y, qa0[k].z, qa0[k].w}, wa1[4] = {qa1[k].x, qa1[k].y, qa1[k].z, qa1[k].w},
+                               wb[4] = {qb[k].x, qb[k].y, qb[k].z, qb[k].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++, it++) {
+                    if (!ok) break;
+                    const int s = it % Cfg::STAGES;
+                    const uint32_t ph = (it / Cfg::STAGES) & 1;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
+                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
+                    *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
+                    if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
+                    *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full0 + 8 * s);
+                }
                 if (!ok) break;
-                const int s = it % Cfg::STAGES;
-                const uint32_t ph = (it / Cfg::STAGES) & 1;
-                if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
-                uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
-                *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
-                if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
-                *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * s);
+                issue(k);
             }
-            a0 = na0; a1 = na1; b = nb4; ti = nti; kg = nkg;
         }
     }
 

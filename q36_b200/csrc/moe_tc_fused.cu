@@ -18,17 +18,35 @@
 
 namespace q36 {
 
+// One pipeline stage holds ONE 128-row weight tile of ONE matrix for one K step, the 16 token rows and the
+// two scale images: 19 KB, eleven stages.  A gate/up tile walks K as gate(k0), up(k0), gate(k1), ... so the
+// ring is uniform for both tile kinds and about 110 KB of weight bytes per SM are in flight in both phases
+// (the 2 KB token box is fetched for gate and again for up: L2 hits).
 struct FusedCfg {
-    static constexpr int STAGES = 6;
+    static constexpr int STAGES = 9;
     static constexpr int A_BYTES = TC_M * 128;
     static constexpr int A_TX_BYTES = TC_M * 64;     // the A box signals its packed bytes (see moe_tc.cu)
     static constexpr int B_BYTES = 16 * 128;
     static constexpr int SF_BYTES = 512;
-    static constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES + 2048;   // 36 KB, 1024-aligned
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-    static constexpr int ACC_STRIDE = 32;            // TMEM columns per accumulator set: gate [0,16), up [16,32)
-    static constexpr int SF_COL0 = 64;               // A0 (4), A1 (4), B (4)
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;   // 19 KB, 1024-aligned
+    // Scale bytes of a whole tile (all its K steps) are staged by bulk async copies, two tiles deep: the rows
+    // of a tile are contiguous in the row-major scale planes (128 rows x K/32 bytes).  Loads issued by the
+    // loader threads themselves were measured to expose a full HBM latency per 4 K steps (register prefetch
+    // does not help: a warp's loads retire through a handful of shared scoreboards).
+    static constexpr int SFT_A = TC_M * 64;          // up to K = 2048: 64 scale bytes per row
+    static constexpr int SFT_B = 16 * 64;
+    static constexpr int SFT_BYTES = 2 * SFT_A + SFT_B;      // 17 KB: gate (or down), up, tokens
+    static constexpr int SFT_SLOTS = 2;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFT_SLOTS * SFT_BYTES + 1024 + 256;
+    // Measured on B200 (block-scaled kind::mxf8f6f4, M = 128, K = 32): ONE issuing thread gets an MMA through
+    // every ~90 cycles whatever N <= 128 is; TWO issuing warps reach the pipe's own floor of ~40 cycles per
+    // MMA; more issuers add nothing.  So two warps issue, on alternate stages (gate | up, or even | odd K
+    // steps of a down tile), each into its own accumulator columns and its own scale columns.
+    static constexpr int ISSUERS = 2;
+    static constexpr int ACC_STRIDE = 32;            // per accumulator set: issuer 0 at [0,16), issuer 1 at [16,32)
+    static constexpr int SF_COL0 = 64;               // per issuer: A (4), B (4)
     static constexpr int TMEM_COLS = 128;
+    static constexpr int THREADS = 32 * (1 + ISSUERS + 4 + 4);   // producer, issuers, epilogue, scale loaders
     static constexpr int DONE_PER_GROUP_PER_MTILE = 4;   // epilogue warps
 };
 
@@ -36,7 +54,7 @@ struct FusedMaps { CUtensorMap g, u, d, sg, su, sd, x, h; };
 
 struct FTile { int kind, g, mt, row0, nrows; };
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(FusedCfg::THREADS, 1)
 k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restrict__ sfG, const uint8_t *__restrict__ sfU,
                   const uint8_t *__restrict__ sfD, uint64_t sf_stride, const uint8_t *__restrict__ sfSG,
                   const uint8_t *__restrict__ sfSU, const uint8_t *__restrict__ sfSD, int n_routed,
@@ -45,7 +63,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     using Cfg = FusedCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint8_t *sft = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sft + Cfg::SFT_SLOTS * Cfg::SFT_BYTES);
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
     // (16-bit where the value allows it: static + dynamic shared memory sit 1.7 KB under the 227 KB limit)
@@ -55,6 +74,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::STAGES);
     const uint32_t acc_full0 = smem_u32(bars + 2 * Cfg::STAGES), acc_empty0 = smem_u32(bars + 2 * Cfg::STAGES + 2);
+    const uint32_t sft_full0 = smem_u32(bars + 2 * Cfg::STAGES + 4), sft_empty0 = smem_u32(bars + 2 * Cfg::STAGES + 6);
 
     // ---- prologue that needs nothing from earlier kernels: runs while they drain
     if (threadIdx.x == 0) {
@@ -64,7 +84,9 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             mbar_init(empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(sft_full0 + 8 * b, 1);              // producer's expect_tx arrive
+            mbar_init(sft_empty0 + 8 * b, 4);             // one arrive per scale warp
+            mbar_init(acc_full0 + 8 * b, Cfg::ISSUERS);   // one tcgen05.commit per issuing warp
             mbar_init(acc_empty0 + 8 * b, 4);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -119,7 +141,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     if (warp == 0) {
         // ---------------------------------------------------- TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
                 const FTile t = get_tile(ti);
@@ -134,58 +156,73 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                     if (!(ok = wait_group(t.g, 0x600))) break;
                     asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy Hq stores before the TMA reads
                 }
-                const uint32_t tx = na * Cfg::A_TX_BYTES + Cfg::B_BYTES;
-                for (int ks = 0; ks < k_steps; ks++, it++) {
+                {   // the tile's scale bytes: contiguous runs of the row-major planes
+                    const uint32_t slot = tcount & 1;
+                    if (!(ok = mbar_wait(sft_empty0 + 8 * slot, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x800 + slot))) break;
+                    const int nbk = (t.kind ? FF : D) / Q36_QK;
+                    const uint32_t a_bytes = TC_M * nbk, b_bytes = t.nrows * nbk;
+                    const size_t arow = (size_t)ge * sf_stride + (size_t)(t.mt * TC_M) * nbk;
+                    const uint8_t *p0 = t.kind ? (sh ? sfSD : sfD) : (sh ? sfSG : sfG);
+                    const uint32_t dst = smem_u32(sft + slot * Cfg::SFT_BYTES);
+                    mbar_expect_tx(sft_full0 + 8 * slot, a_bytes * na + b_bytes);
+                    bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
+                    if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
+                    bulk_load(dst + 2 * Cfg::SFT_A, (t.kind ? Hs : Xs) + (size_t)t.row0 * nbk, b_bytes, sft_full0 + 8 * slot);
+                    tcount++;
+                }
+                const uint32_t tx = Cfg::A_TX_BYTES + Cfg::B_BYTES;
+                const int steps = k_steps * na;            // gate/up: gate(k0), up(k0), gate(k1), ...
+                for (int j = 0; j < steps; j++, it++) {
+                    const int ks = t.kind ? j : (j >> 1);
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, tx);
-                    tma_load_3d(sb, ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
-                    if (!t.kind) tma_load_3d(sb + Cfg::A_BYTES, ma1, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
-                    tma_load_2d(sb + 2 * Cfg::A_BYTES, mb, ks * TC_KSTEP, t.row0, full0 + 8 * s);
+                    tma_load_3d(sb, (!t.kind && (j & 1)) ? ma1 : ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                    tma_load_2d(sb + Cfg::A_BYTES, mb, ks * TC_KSTEP, t.row0, full0 + 8 * s);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------ MMA issuer
+    } else if (warp <= Cfg::ISSUERS) {
+        // ----------------------------------------------------- MMA issuers
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            const int w = warp - 1;                         // stages with (step & 1) == w are this warp's
+            const uint32_t t_sfa = tmem + Cfg::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
+            uint32_t it0 = 0, tcount = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
                 const FTile t = get_tile(ti);
-                const int k_steps = (t.kind ? FF : D) / TC_KSTEP;
+                const int steps = ((t.kind ? FF : D) / TC_KSTEP) * (t.kind ? 1 : 2);
                 const uint32_t buf = tcount & 1;
-                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE;
+                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE + 16 * w;
                 if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
                 tc_fence_after();
-                for (int ks = 0; ks < k_steps; ks++, it++) {
+                bool first = true;
+                for (int j = w; j < steps; j += Cfg::ISSUERS) {
+                    const uint32_t it = it0 + j;
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
                     tc_fence_after();
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t sf = sb + 2 * Cfg::A_BYTES + Cfg::B_BYTES;
-                    const uint32_t t_sfa0 = tmem + Cfg::SF_COL0, t_sfb = tmem + Cfg::SF_COL0 + 8;
-                    tc_cp_sf(t_sfa0, desc_sf(sf));
-                    if (!t.kind) tc_cp_sf(t_sfa0 + 4, desc_sf(sf + Cfg::SF_BYTES));
-                    tc_cp_sf(t_sfb, desc_sf(sf + 2 * Cfg::SF_BYTES));
+                    const uint32_t sf = sb + Cfg::A_BYTES + Cfg::B_BYTES;
+                    tc_cp_sf(t_sfa, desc_sf(sf));
+                    tc_cp_sf(t_sfb, desc_sf(sf + Cfg::SF_BYTES));
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++) {
-                        const uint32_t acc = (ks | kb) ? 1u : 0u;
-                        const uint32_t id = idesc_mx(16, kb);
-                        const uint64_t bd = desc_sw128(sb + 2 * Cfg::A_BYTES + kb * 32);
                         const uint32_t sfid = (uint32_t)kb << 30;
-                        tc_mma(d_tmem, desc_sw128(sb + kb * 32), bd, id, t_sfa0 | sfid, t_sfb | sfid, acc);
-                        if (!t.kind)
-                            tc_mma(d_tmem + 16, desc_sw128(sb + Cfg::A_BYTES + kb * 32), bd, id, (t_sfa0 + 4) | sfid, t_sfb | sfid, acc);
+                        tc_mma(d_tmem, desc_sw128(sb + kb * 32), desc_sw128(sb + Cfg::A_BYTES + kb * 32), idesc_mx(16, kb),
+                               t_sfa | sfid, t_sfb | sfid, (first && kb == 0) ? 0u : 1u);
                     }
+                    first = false;
                     tc_commit(empty0 + 8 * s);
                 }
+                it0 += steps;
                 if (ok) tc_commit(acc_full0 + 8 * buf);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 1 + Cfg::ISSUERS + 4) {
         // -------------------------------------------------------- epilogue
         const int q = warp & 3;
         uint32_t tcount = 0;
@@ -197,9 +234,19 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;
-            uint32_t acc[32];
-            tc_ld32(tq, acc);            // gate columns [0,16), up columns [16,32) (or the down tile's 16 columns)
-            tc_ld_wait();
+            // columns [0,16): issuer 0 (gate, or the even K steps of a down tile); [16,32): issuer 1 (up / odd)
+            float g[16], u[16];
+            {
+                uint32_t r0[32];
+                tc_ld32(tq, r0);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    g[j] = __uint_as_float(r0[j]);
+                    u[j] = __uint_as_float(r0[16 + j]);
+                    if (t.kind) g[j] += u[j];
+                }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // the registers hold the tile: TMEM is free again
@@ -208,7 +255,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (j < t.nrows) {
-                        const float h = silu_f(__uint_as_float(acc[j])) * __uint_as_float(acc[16 + j]);
+                        const float h = silu_f(g[j]) * u[j];
                         const uint32_t am = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h)));
                         const int e2 = e2_of_amax(__uint_as_float(am));
                         const size_t row = (size_t)(t.row0 + j);
@@ -222,76 +269,52 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++)
-                    if (j < t.nrows) Y[(size_t)(t.row0 + j) * D + mrow] = __uint_as_float(acc[j]);
+                    if (j < t.nrows) Y[(size_t)(t.row0 + j) * D + mrow] = g[j];
             }
         }
     } else {
         // --------------------------------------------------- scale loaders
-        const int i = threadIdx.x - 6 * 32;
+        // Thread i owns row i of the tile: per stage it moves the row's 4 scale bytes of that K step from the
+        // staged plane rows into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
+        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + 4);
         const int w4 = i >> 5, m0 = i & 31;
         const uint32_t my_off = m0 * 16 + w4 * 4;
-        const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-        struct Item { int ti, kg; };
-        // A-scales (weights) can always be fetched ahead; B-scales of a down tile only once its group is done
-        auto fetch_a = [&](const FTile &t, int kg, uint4 &a0, uint4 &a1) {
-            const bool sh = t.g >= n_routed;
-            const int nb = (t.kind ? FF : D) / Q36_QK;
-            const size_t arow = (size_t)(sh ? 0 : t.g) * sf_stride + (size_t)(t.mt * TC_M + i) * nb + 16 * kg;
-            const uint8_t *p0 = t.kind ? (sh ? sfSD : sfD) : (sh ? sfSG : sfG);
-            a0 = __ldg(reinterpret_cast<const uint4 *>(p0 + arow));
-            a1 = ones;
-            if (!t.kind) a1 = __ldg(reinterpret_cast<const uint4 *>((sh ? sfSU : sfU) + arow));
-        };
-        auto fetch_b = [&](const FTile &t, int kg, uint4 &b) {
-            b = ones;
-            if (i < t.nrows) {
-                const int nb = (t.kind ? FF : D) / Q36_QK;
-                const uint8_t *src = (t.kind ? Hs : Xs) + (size_t)(t.row0 + i) * nb + 16 * kg;
-                // Hs was written by other SMs in this same launch: read it at L2, not through the read-only path
-                b = t.kind ? __ldcg(reinterpret_cast<const uint4 *>(src)) : __ldg(reinterpret_cast<const uint4 *>(src));
-            }
-        };
-        uint32_t it = 0;
+        uint32_t it = 0, tcount = 0;
         bool ok = true;
-        int ti = blockIdx.x, kg = 0;
-        uint4 a0 = ones, a1 = ones, b = ones, na0 = ones, na1 = ones, nb4 = ones;
-        bool b_ready = false, nb_ready = false;
-        FTile t = {0, 0, 0, 0, 0}, nt = t;
-        if (ti < n_tiles) {
-            t = get_tile(ti);
-            fetch_a(t, kg, a0, a1);
-            if (!t.kind) { fetch_b(t, kg, b); b_ready = true; }
-        }
-        while (ti < n_tiles && ok) {
-            int nti = ti, nkg = kg + 1;
-            const int groups = ((t.kind ? FF : D) / TC_KSTEP) / 4;
-            if (nkg == groups) { nkg = 0; nti = ti + gridDim.x; }
-            nb_ready = false;
-            if (nti < n_tiles) {
-                nt = (nti == ti) ? t : get_tile(nti);
-                fetch_a(nt, nkg, na0, na1);
-                if (!nt.kind) { fetch_b(nt, nkg, nb4); nb_ready = true; }
-            }
-            if (!b_ready) {   // a down tile: its group's intermediate must be complete before Hs is read
-                if (!(ok = wait_group(t.g, 0x700))) break;
-                fetch_b(t, kg, b);
-            }
-            const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
+            const FTile t = get_tile(ti);
+            const uint32_t slot = tcount & 1;
+            const int nbk = (t.kind ? FF : D) / Q36_QK;
+            const int steps = (nbk / 4) * (t.kind ? 1 : 2);
+            if (!(ok = mbar_wait(sft_full0 + 8 * slot, (tcount >> 1) & 1, &abort_flag, status, 0x700 + slot))) break;
+            const uint8_t *st = sft + slot * Cfg::SFT_BYTES;
+            const uint8_t *ra0 = st + i * nbk, *ra1 = st + Cfg::SFT_A + i * nbk, *rb = st + 2 * Cfg::SFT_A + i * nbk;
+            const bool bvalid = i < t.nrows;
+            for (int j0 = 0; j0 < steps && ok; j0 += 4) {   // four stages per cross-proxy fence
+                const uint32_t it0 = it;
 #pragma unroll
-            for (int j = 0; j < 4; j++, it++) {
+                for (int jj = 0; jj < 4; jj++) {
+                    const int j = j0 + jj;
+                    const int ks = t.kind ? j : (j >> 1);
+                    const bool up = !t.kind && (j & 1);
+                    const uint32_t va = *reinterpret_cast<const uint32_t *>((up ? ra1 : ra0) + 4 * ks);
+                    const uint32_t vb = bvalid ? *reinterpret_cast<const uint32_t *>(rb + 4 * ks) : 0x7f7f7f7fu;
+                    const int s = it % Cfg::STAGES;
+                    const uint32_t ph = (it / Cfg::STAGES) & 1;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
+                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
+                    *reinterpret_cast<uint32_t *>(sf + my_off) = va;
+                    *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = vb;
+                    it++;
+                }
                 if (!ok) break;
-                const int s = it % Cfg::STAGES;
-                const uint32_t ph = (it / Cfg::STAGES) & 1;
-                if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
-                uint8_t *sf = smem + s * Cfg::STAGE_BYTES + 2 * Cfg::A_BYTES + Cfg::B_BYTES;
-                *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
-                if (!t.kind) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
-                *reinterpret_cast<uint32_t *>(sf + 2 * Cfg::SF_BYTES + my_off) = wb[j];
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * s);
+                if (lane == 0)
+                    for (uint32_t x = it0; x < it; x++) mbar_arrive(full0 + 8 * (x % Cfg::STAGES));
             }
-            a0 = na0; a1 = na1; b = nb4; b_ready = nb_ready; t = nt; ti = nti; kg = nkg;
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(sft_empty0 + 8 * slot);   // this warp is done with the staged rows
         }
     }
 
@@ -334,7 +357,7 @@ int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const
     }
     const long max_tiles = (long)(R_max + n_group + 1) * (FF / TC_M + D / TC_M);
     const int grid = (int)min((long)sm_count(), max_tiles);
-    launch_k(k_ffn_fused_small, dim3(grid), dim3(TC_THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
+    launch_k(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
              (const uint8_t *)Wu + plane, (const uint8_t *)Wd + plane, estride, (const uint8_t *)Sg + plane,
              (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status);
     return check_launch();

@@ -46,6 +46,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile 
     atomicCAS(status, 0, where);
     return false;
 }
+// Whole-warp wait with ONE polling lane: 128 threads polling one mbarrier word serialise on it and turn a
+// stage hand-over into microseconds.  All 32 lanes must call; returns the same value in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(a, parity, abort_flag, status, where) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();   // the lanes' later accesses are ordered after lane 0's acquire
+    return ok != 0;
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -57,6 +66,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *m, 
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+// untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

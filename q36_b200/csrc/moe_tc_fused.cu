@@ -142,7 +142,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         // ---------------------------------------------------- TMA producer
         if (lane == 0) {
             uint32_t it = 0, tcount = 0;
-            bool ok = true;
+            bool ok = true, all_gu_done = false;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
                 const FTile t = get_tile(ti);
                 const bool sh = t.g >= n_routed;
@@ -152,8 +152,11 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 const CUtensorMap *ma0 = t.kind ? (sh ? &maps.sd : &maps.d) : (sh ? &maps.sg : &maps.g);
                 const CUtensorMap *ma1 = sh ? &maps.su : &maps.u;
                 const CUtensorMap *mb = t.kind ? &maps.h : &maps.x;
-                if (t.kind) {
+                if (t.kind && !all_gu_done) {
                     if (!(ok = wait_group(t.g, 0x600))) break;
+                    int v;   // after the wait (acquire): if the whole gate/up phase is over, later tiles need no poll
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(&plan->gu_done) : "memory");
+                    all_gu_done = v >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;
                     asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy Hq stores before the TMA reads
                 }
                 {   // the tile's scale bytes: contiguous runs of the row-major planes
@@ -265,7 +268,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 }
                 __threadfence();         // each lane's stores are visible device-wide before the count moves
                 __syncwarp();
-                if (lane == 0) atomicAdd(plan->done + t.g, 1);
+                if (lane == 0) {
+                    atomicAdd(plan->done + t.g, 1);
+                    atomicAdd(&plan->gu_done, 1);      // once every gate/up tile is in, consumers stop polling per group
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++)

@@ -12,7 +12,8 @@ constexpr int TC_N_DOWN = 128;     // token rows per down tile
 // Groups are ranked by size (largest first); base[w][r] is the first tile of rank r for launch w
 // (0 = gate/up, 1 = down), so a tile index maps to (group, token tile, row tile) by a binary search.
 struct TcPlan {
-    int n_groups, n_tiles[2], pad;
+    int n_groups, n_tiles[2];
+    int gu_done;                          // gate/up tiles whose epilogue has finished (fused decode kernel only)
     int order[DISPATCH_MAX_GROUPS + 1];   // rank -> group
     int row0[DISPATCH_MAX_GROUPS + 1];    // group -> first row of the sorted space
     int cnt[DISPATCH_MAX_GROUPS + 1];     // group -> rows
@@ -72,6 +73,7 @@ __device__ __forceinline__ void tc_plan_block(const int *goffs, int n_group, boo
             if (r < G) { plan->base[0][r] = ra; plan->base[1][r] = rb; ra += tg[r]; rb += td[r]; }
         }
         if (tid == 31) {
+            plan->gu_done = 0;
             plan->base[0][G] = ia; plan->base[1][G] = ib;
             plan->n_tiles[0] = ia; plan->n_tiles[1] = ib; plan->n_groups = G;
         }

@@ -39,27 +39,37 @@ namespace q36 {
 // NA = 1: down (one A operand, f32 rows out), token tile 128
 // The token tile of gate/up is 112 so that TWO accumulator sets (gate + up each) and the scale
 // columns fit the 512 TMEM columns: the epilogue of one tile overlaps the MMAs of the next.
-// SMALL: every group has at most 16 rows (decode).  The B slot shrinks to one 16-row box, which buys two
-// (gate/up) or four (down) more pipeline stages: at decode the kernel is a pure weight stream and the bytes
-// in flight per SM are what bounds it.
-template <int NA, bool SMALL>
+//
+// Measured on B200 and built in:
+//  * one thread gets a block-scaled MMA (M = 128, K = 32) through every ~90 cycles for any N <= 128 (N = 128
+//    would need 64); two issuing warps reach the pipe rate.  Gate/up has two issuers, one per matrix.
+//  * scale bytes fetched by the loader threads themselves (ld.global, even prefetched in registers) exposed a
+//    full HBM latency every four K steps and set the pace of the whole kernel.  They now arrive by TMA: a
+//    ring of items (four K steps: 16 scale bytes per row, boxes of 16 B x 128 rows), issued by the producer
+//    with the operand tiles; the loader warps only reshuffle shared memory.
+template <int NA>
 struct TcCfg {
     static constexpr int N = (NA == 2) ? TC_N_GATEUP : TC_N_DOWN;   // token rows per tile (max UMMA N)
-    static constexpr int STAGES = SMALL ? ((NA == 2) ? 6 : 10) : ((NA == 2) ? 4 : 6);
+    static constexpr int ISSUERS = NA;
+    static constexpr int STAGES = (NA == 2) ? 4 : 6;
     static constexpr int A_BYTES = TC_M * 128;               // 16 KB of shared memory per A operand per stage
     // What the A box signals on the mbarrier: the PACKED bytes read from global memory (64 B per row), not
     // the 128 B per row it occupies after expansion.  Measured on B200: expecting 16 KB leaves the barrier
     // pending for ever, expecting 8 KB completes it.
     static constexpr int A_TX_BYTES = TC_M * 64;
-    static constexpr int B_BYTES = SMALL ? 16 * 128 : 128 * 128;   // slot for N rows (2 KB or 16 KB)
-    static constexpr int SF_BYTES = 512;
+    static constexpr int B_BYTES = N * 128;                  // 14 KB or 16 KB
+    static constexpr int SF_BYTES = 512;                     // one 32 x 16 B scale image
     // operand tiles are 128B-swizzled: every stage starts on a 1024-byte boundary
     static constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + ((NA + 1) * SF_BYTES + 1023) / 1024 * 1024;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SFR_SLOTS = 4;                      // ring of scale items
+    static constexpr int SFR_PART = 128 * 16;                // 128 rows x 16 B
+    static constexpr int SFR_BYTES = (NA + 1) * SFR_PART;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFR_SLOTS * SFR_BYTES + 1024 /* alignment */ + 512 /* barriers */;
     static constexpr int ACC_STRIDE = (NA == 2) ? 256 : 128; // TMEM columns between the two accumulator sets
-    static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // scale columns: A0 (4), [A1 (4)], B (4)
+    static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // per issuer: A (4), B (4)
     static constexpr int TMEM_COLS = 512;
-    static constexpr int B_FULL_MIN = SMALL ? (1 << 30) : 49;   // token tiles of at least this many rows use one big box
+    static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
+    static constexpr int THREADS = 32 * (1 + ISSUERS + 4 + 4);
 };
 
 // ------------------------------------------------------------- tile plan
@@ -73,54 +83,60 @@ k_tc_plan(const int *__restrict__ goffs, int n_group, const int *__restrict__ so
 }
 
 // ------------------------------------------------------------ main kernel
-struct TcMaps { CUtensorMap a0, a1, s0, s1, b16, bfull; };
+struct TcMaps { CUtensorMap a0, a1, s0, s1, b16, bfull, fa0, fa1, fs0, fs1, fb; };
 
-template <int NA, bool SMALL>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ sfA0, const uint8_t *__restrict__ sfA1,
-              uint64_t sfA_stride, const uint8_t *__restrict__ sfS0, const uint8_t *__restrict__ sfS1, int n_routed,
-              const uint8_t *__restrict__ sfB, const TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
-              uint8_t *__restrict__ Hs, float *__restrict__ Y, int M_total, int K, int *__restrict__ status) {
-    using Cfg = TcCfg<NA, SMALL>;
+template <int NA>
+__global__ void __launch_bounds__(TcCfg<NA>::THREADS, 1)
+k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *__restrict__ plan,
+              uint8_t *__restrict__ Hq, uint8_t *__restrict__ Hs, float *__restrict__ Y, int M_total, int K,
+              int *__restrict__ status) {
+    using Cfg = TcCfg<NA>;
     constexpr int W = (NA == 2) ? 0 : 1;
-    Q36_GDS();
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-    // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint8_t *sfr = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sfr + Cfg::SFR_SLOTS * Cfg::SFR_BYTES);
+    // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], sfr_full[SLOTS], sfr_empty[SLOTS]
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
-    __shared__ int s_order[DISPATCH_MAX_GROUPS + 1], s_row0[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1],
-        s_base[DISPATCH_MAX_GROUPS + 2];
+    __shared__ int s_row0[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1], s_base[DISPATCH_MAX_GROUPS + 2];
+    __shared__ unsigned short s_order[DISPATCH_MAX_GROUPS + 1];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::STAGES);
-    const uint32_t acc_full0 = smem_u32(bars + 2 * Cfg::STAGES), acc_empty0 = smem_u32(bars + 2 * Cfg::STAGES + 2);
-    const int n_tiles = plan->n_tiles[W];
-    const int G = plan->n_groups;
-    const int k_steps = K / TC_KSTEP;
-    const int nb = K / Q36_QK;
-    const int m_tiles = M_total / TC_M;
+    const uint32_t acc_full0 = smem_u32(bars + 2 * Cfg::STAGES), acc_empty0 = acc_full0 + 16;
+    const uint32_t sfr_full0 = acc_empty0 + 16, sfr_empty0 = sfr_full0 + 8 * Cfg::SFR_SLOTS;
 
-    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
-        s_base[i] = plan->base[W][i];
-        if (i < G) { s_order[i] = plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = plan->cnt[i]; }
-    }
+    // ---- prologue that needs nothing from earlier kernels
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < Cfg::STAGES; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4);   // producer's expect_tx arrive + one arrive per scale warp
-            mbar_init(empty0 + 8 * s, 1);      // tcgen05.commit
+            mbar_init(full0 + 8 * s, 1 + 4);               // producer's expect_tx arrive + one arrive per scale warp
+            mbar_init(empty0 + 8 * s, Cfg::ISSUERS);       // one tcgen05.commit per issuing warp
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(acc_full0 + 8 * b, 1);   // tcgen05.commit
-            mbar_init(acc_empty0 + 8 * b, 4);  // one arrive per epilogue warp
+            mbar_init(acc_full0 + 8 * b, Cfg::ISSUERS);
+            mbar_init(acc_empty0 + 8 * b, 4);              // one arrive per epilogue warp
+        }
+        for (int b = 0; b < Cfg::SFR_SLOTS; b++) {
+            mbar_init(sfr_full0 + 8 * b, 1);
+            mbar_init(sfr_empty0 + 8 * b, 4);              // one arrive per scale warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    Q36_GDS();   // from here on: global memory written by earlier kernels
+
+    const int n_tiles = plan->n_tiles[W];
+    const int G = plan->n_groups;
+    const int k_steps = K / TC_KSTEP;
+    const int m_tiles = M_total / TC_M;
+    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
+        s_base[i] = plan->base[W][i];
+        if (i < G) { s_order[i] = (unsigned short)plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = plan->cnt[i]; }
     }
     tc_fence_before();
     __syncthreads();
@@ -142,17 +158,28 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
     if (warp == 0) {
         // ---------------------------------------------------- TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, item = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
                 const TcTile t = get_tile(ti);
                 const bool sh = t.g >= n_routed;
                 const CUtensorMap *ma0 = sh ? &maps.s0 : &maps.a0, *ma1 = sh ? &maps.s1 : &maps.a1;
+                const CUtensorMap *fa0 = sh ? &maps.fs0 : &maps.fa0, *fa1 = sh ? &maps.fs1 : &maps.fa1;
                 const int ge = sh ? 0 : t.g;
                 const bool full_box = t.nrows >= Cfg::B_FULL_MIN;
                 const int slabs = (t.nrows + 15) / 16;
                 const uint32_t tx = NA * Cfg::A_TX_BYTES + (full_box ? Cfg::N * 128 : slabs * 2048);
                 for (int ks = 0; ks < k_steps; ks++, it++) {
+                    if ((ks & 3) == 0) {   // the scale bytes of the next four K steps
+                        const uint32_t sl = item % Cfg::SFR_SLOTS;
+                        if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / Cfg::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl))) break;
+                        const uint32_t dst = smem_u32(sfr + sl * Cfg::SFR_BYTES);
+                        mbar_expect_tx(sfr_full0 + 8 * sl, NA * Cfg::SFR_PART + Cfg::N * 16);
+                        tma_load_3d(dst, fa0, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                        if (NA == 2) tma_load_3d(dst + Cfg::SFR_PART, fa1, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                        tma_load_2d(dst + NA * Cfg::SFR_PART, &maps.fb, 4 * ks, t.row0, sfr_full0 + 8 * sl);
+                        item++;
+                    }
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
@@ -169,16 +196,20 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------ MMA issuer
+    } else if (warp <= Cfg::ISSUERS) {
+        // ----------------------------------------------------- MMA issuers
+        // NA = 2: issuer 0 drives the gate matrix, issuer 1 the up matrix of the SAME stage; each copies its own
+        // weight-scale image and its own copy of the token-scale image into its own TMEM columns.
         if (lane == 0) {
+            const int w = warp - 1;
+            const uint32_t t_sfa = tmem + Cfg::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
                 const TcTile t = get_tile(ti);
                 const int n_mma = (t.nrows >= Cfg::B_FULL_MIN) ? Cfg::N : max(16, (t.nrows + 15) & ~15);
                 const uint32_t buf = tcount & 1;
-                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE;
+                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE + w * Cfg::N;
                 // this accumulator set must have been drained by the epilogue two tiles ago
                 if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
                 tc_fence_after();
@@ -189,26 +220,20 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
                     tc_fence_after();
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     const uint32_t sf = sb + NA * Cfg::A_BYTES + Cfg::B_BYTES;
-                    const uint32_t t_sfa0 = tmem + Cfg::SF_COL0, t_sfb = tmem + Cfg::SF_COL0 + 4 * NA;
-                    tc_cp_sf(t_sfa0, desc_sf(sf));
-                    if (NA == 2) tc_cp_sf(t_sfa0 + 4, desc_sf(sf + Cfg::SF_BYTES));
+                    tc_cp_sf(t_sfa, desc_sf(sf + w * Cfg::SF_BYTES));
                     tc_cp_sf(t_sfb, desc_sf(sf + NA * Cfg::SF_BYTES));
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++) {
-                        const uint32_t acc = (ks | kb) ? 1u : 0u;
-                        const uint32_t id = idesc_mx(n_mma, kb);
-                        const uint64_t bd = desc_sw128(sb + NA * Cfg::A_BYTES + kb * 32);
                         const uint32_t sfid = (uint32_t)kb << 30;
-                        tc_mma(d_tmem, desc_sw128(sb + kb * 32), bd, id, t_sfa0 | sfid, t_sfb | sfid, acc);
-                        if (NA == 2)
-                            tc_mma(d_tmem + Cfg::N, desc_sw128(sb + Cfg::A_BYTES + kb * 32), bd, id, (t_sfa0 + 4) | sfid, t_sfb | sfid, acc);
+                        tc_mma(d_tmem, desc_sw128(sb + w * Cfg::A_BYTES + kb * 32), desc_sw128(sb + NA * Cfg::A_BYTES + kb * 32),
+                               idesc_mx(n_mma, kb), t_sfa | sfid, t_sfb | sfid, (ks | kb) ? 1u : 0u);
                     }
-                    tc_commit(empty0 + 8 * s);   // stage reusable once these MMAs have read it
+                    tc_commit(empty0 + 8 * s);   // stage reusable once every issuer's MMAs have read it
                 }
-                if (ok) tc_commit(acc_full0 + 8 * buf);     // accumulators complete
+                if (ok) tc_commit(acc_full0 + 8 * buf);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 1 + Cfg::ISSUERS + 4) {
         // -------------------------------------------------------- epilogue
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
         uint32_t tcount = 0;
@@ -253,49 +278,28 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
         }
     } else {
         // --------------------------------------------------- scale loaders
-        // Work items are (tile, group of 4 K-steps): one 16-byte load per operand row covers four stages.
-        // The loads of the NEXT item are issued before the current item waits for its stages.
-        const int i = threadIdx.x - 6 * 32;      // 0..127: row of the tile
+        // Thread i owns row i of the tile: per stage it moves the row's 4 scale bytes of that K step from the
+        // staged item into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
+        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + 4);
         const int w4 = i >> 5, m0 = i & 31;
-        const uint32_t my_off = m0 * 16 + w4 * 4; // byte offset of this row's word in the 32x16 B image
-        const int groups = k_steps / 4;
-        const uint4 ones = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-        auto fetch = [&](int ti, int kg, uint4 &a0, uint4 &a1, uint4 &b) {
+        const uint32_t my_off = m0 * 16 + w4 * 4;
+        uint32_t it = 0, item = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
             const TcTile t = get_tile(ti);
-            const bool sh = t.g >= n_routed;
-            const size_t arow = (size_t)(sh ? 0 : t.g) * sfA_stride + (size_t)(t.mt * TC_M + i) * nb + 16 * kg;
-            a0 = __ldg(reinterpret_cast<const uint4 *>((sh ? sfS0 : sfA0) + arow));
-            a1 = ones;
-            if (NA == 2) a1 = __ldg(reinterpret_cast<const uint4 *>((sh ? sfS1 : sfA1) + arow));
-            b = ones;
-            if (i < t.nrows) b = __ldg(reinterpret_cast<const uint4 *>(sfB + (size_t)(t.row0 + i) * nb + 16 * kg));
-        };
-        // The scale bytes are cold 16-byte loads from HBM (2-3 us under load) and every stage waits for them:
-        // the loads run PF items ahead of the fills in a register ring (one item ahead left the loaders, not
-        // the tensor pipe, setting the pace).
-        constexpr int PF = 4;
-        uint4 qa0[PF], qa1[PF], qb[PF];
-        bool qvalid[PF];
-        int pti = blockIdx.x, pkg = 0;
-        auto issue = [&](int k) {
-            qvalid[k] = pti < n_tiles;
-            if (!qvalid[k]) return;
-            fetch(pti, pkg, qa0[k], qa1[k], qb[k]);
-            if (++pkg == groups) { pkg = 0; pti += gridDim.x; }
-        };
+            const bool bvalid = i < t.nrows;
+            for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
+                const uint32_t sl = item % Cfg::SFR_SLOTS;
+                if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl))) break;
+                const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + i * 16;
+                const uint4 a0 = *reinterpret_cast<const uint4 *>(src);
+                const uint4 a1 = (NA == 2) ? *reinterpret_cast<const uint4 *>(src + Cfg::SFR_PART) : make_uint4(0, 0, 0, 0);
+                uint4 b = *reinterpret_cast<const uint4 *>(src + NA * Cfg::SFR_PART);
+                if (!bvalid) b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+                const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w}, wb[4] = {b.x, b.y, b.z, b.w};
+                const uint32_t it0 = it;
 #pragma unroll
-        for (int k = 0; k < PF; k++) issue(k);
-        uint32_t it = 0;
-        bool ok = true, running = true;
-        while (running && ok) {
-#pragma unroll
-            for (int k = 0; k < PF; k++) {
-                if (!qvalid[k]) { running = false; break; }
-                const uint32_t wa0[4] = {qa0[k].x, qa0[k].y, qa0[k].z, qa0[k].w}, wa1[4] = {qa1[k].x, qa1[k].y, qa1[k].z, qa1[k].w},
-                               wb[4] = {qb[k].x, qb[k].y, qb[k].z, qb[k].w};
-#pragma unroll
-                for (int j = 0; j < 4; j++, it++) {
-                    if (!ok) break;
+                for (int j = 0; j < 4; j++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
@@ -303,12 +307,18 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, const uint8_t *__restrict__ s
                     *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
                     if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
                     *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(full0 + 8 * s);
+                    it++;
+                    if (Cfg::STAGES < 6 || j == 3) {   // few stages: hand each over at once; else one fence per item
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full0 + 8 * s);
+                    }
                 }
                 if (!ok) break;
-                issue(k);
+                if (Cfg::STAGES >= 6 && lane == 0)
+                    for (uint32_t x = it0; x + 1 < it; x++) mbar_arrive(full0 + 8 * (x % Cfg::STAGES));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
             }
         }
     }
@@ -389,15 +399,31 @@ int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int F
     return check_launch();
 }
 
+// scale plane of n_group experts: [n_group][rows][nb] bytes (n_group = 0: a plain [rows][nb] matrix),
+// boxes of 16 B (four K steps) x box_rows rows
+static int make_map_scales(CUtensorMap *m, const void *base, int rows, int nb, int n_group, uint64_t stride3, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return Q36_MOE_ECUDA;
+    cuuint64_t dims[3] = {(cuuint64_t)nb, (cuuint64_t)rows, (cuuint64_t)(n_group > 0 ? n_group : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)nb, (cuuint64_t)stride3};
+    cuuint32_t box[3] = {16, (cuuint32_t)box_rows, 1}, el[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, n_group > 0 ? 3 : 2, const_cast<void *>(base), dims, strides, box, el,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+
 // A0/A1: routed experts' planes (A1 unused for NA = 1); S0/S1: the shared expert's planes or NULL.
-template <int NA, bool SMALL>
+template <int NA>
 static int run_grouped(const void *A0, const void *A1, const void *S0, const void *S1, int n_group, int R_max,
                        const uint8_t *Bq, const uint8_t *Bs, uint8_t *Hq, uint8_t *Hs, float *Y, int M, int K,
                        const void *plan, int *status, cudaStream_t st) {
-    using Cfg = TcCfg<NA, SMALL>;
+    using Cfg = TcCfg<NA>;
     if (M % TC_M || K % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK);
     const uint64_t plane = (uint64_t)M * (K / 2);
+    const int nb = K / Q36_QK;
     if (NA == 1) A1 = A0;
     if (!S0) { S0 = A0; S1 = A1; }
     if (NA == 1) S1 = S0;
@@ -409,34 +435,35 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     if ((rc = make_map_codes(&maps.s1, S1, M, K, 1, estride))) return rc;
     if ((rc = make_map_rows(&maps.b16, Bq, R_max, K, 16))) return rc;
     if ((rc = make_map_rows(&maps.bfull, Bq, R_max, K, Cfg::N))) return rc;
-    static bool attr_set = false;   // one per (NA, SMALL) instantiation
+    if ((rc = make_map_scales(&maps.fa0, (const uint8_t *)A0 + plane, M, nb, n_group, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fa1, (const uint8_t *)A1 + plane, M, nb, n_group, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fs0, (const uint8_t *)S0 + plane, M, nb, 1, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fs1, (const uint8_t *)S1 + plane, M, nb, 1, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fb, Bs, R_max, nb, 0, 0, Cfg::N))) return rc;
+    static bool attr_set = false;   // one per instantiation
     if (!attr_set) {
-        if (cudaFuncSetAttribute(k_grouped_mma<NA, SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_grouped_mma<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
             return check_launch();
         attr_set = true;
     }
     const int m_tiles = M / TC_M;
     const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
     const int grid = (int)min((long)sm_count(), max_tiles);
-    launch_k(k_grouped_mma<NA, SMALL>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM_BYTES, st, 
-        maps, (const uint8_t *)A0 + plane, (const uint8_t *)A1 + plane, estride, (const uint8_t *)S0 + plane,
-        (const uint8_t *)S1 + plane, n_group, Bs, (const TcPlan *)plan, Hq, Hs, Y, M, K, status);
+    launch_k(k_grouped_mma<NA>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Hq, Hs,
+             Y, M, K, status);
     return check_launch();
 }
 
-// max_group_rows: an upper bound on the rows of any one group (<= 16 selects the deep-pipeline variant)
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
                      int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF,
                      const void *plan, int *status, cudaStream_t st) {
-    if (max_group_rows <= 16)
-        return run_grouped<2, true>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
-    return run_grouped<2, false>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
+    (void)max_group_rows;
+    return run_grouped<2>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
 }
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq,
                    const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
-    if (max_group_rows <= 16)
-        return run_grouped<1, true>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
-    return run_grouped<1, false>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
+    (void)max_group_rows;
+    return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
 }
 
 }  // namespace q36

@@ -90,6 +90,33 @@ __host__ __device__ __forceinline__ int hw_pos(int j) { return (j < 16) ? (2 * j
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }   // q36_ops.cuh:58
 __device__ __forceinline__ float sigm_f(float x) { return 1.f / (1.f + __expf(-x)); } // q36_ops.cuh:59
 
+// SwiGLU + E4M3 requantisation of NC token columns held by a warp whose 32 lanes are the 32 ff rows of one scale
+// block: h = silu(g) * u, block amax by one redux per column, shared exponent, code stored at the lane's hw
+// position of row (row0 + c).  Written without per-column branches so that the NC dependent chains (exp,
+// divide, redux, convert, store: several hundred cycles each) overlap; only the stores are predicated.
+template <int NC>
+__device__ __forceinline__ void swiglu_quant_store(const float (&g)[NC], const float (&u)[NC], int n_valid, size_t row0,
+                                                   uint8_t *__restrict__ Hq, uint8_t *__restrict__ Hs, int FF, int blk,
+                                                   int lane) {
+    float h[NC];
+    uint32_t am[NC];
+#pragma unroll
+    for (int c = 0; c < NC; c++) h[c] = __fdividef(g[c], 1.f + __expf(-g[c])) * u[c];
+#pragma unroll
+    for (int c = 0; c < NC; c++) am[c] = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h[c])));
+    const int p = hw_pos(lane);
+    const int nbh = FF / Q36_QK;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int e2 = e2_of_amax(__uint_as_float(am[c]));
+        const uint8_t q = f32_to_e4m3(h[c] * inv_scale_of_e2(e2));
+        if (c < n_valid) {
+            Hq[(row0 + c) * FF + blk * Q36_QK + p] = q;
+            if (lane == 0) Hs[(row0 + c) * nbh + blk] = (uint8_t)(127 + e2);
+        }
+    }
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -253,16 +253,13 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                     tc_ld32(tq + Cfg::N + c0, u);
                     tc_ld_wait();
                     const int blk = mrow / Q36_QK;           // this warp's 32 rows are one scale block
-                    const int nbh = M_total / Q36_QK;
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (c0 + j < t.nrows) {              // warp-uniform
-                            const float h = silu_f(__uint_as_float(g[j])) * __uint_as_float(u[j]);
-                            const uint32_t am = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h)));
-                            const int e2 = e2_of_amax(__uint_as_float(am));
-                            const size_t row = (size_t)(t.row0 + c0 + j);
-                            Hq[row * M_total + blk * Q36_QK + hw_pos(lane)] = f32_to_e4m3(h * inv_scale_of_e2(e2));
-                            if (lane == 0) Hs[row * nbh + blk] = (uint8_t)(127 + e2);
+                    for (int j0 = 0; j0 < 32; j0 += 8) {
+                        if (c0 + j0 < t.nrows) {             // warp-uniform; eight columns per batch for ILP
+                            float gg[8], uu[8];
+#pragma unroll
+                            for (int c = 0; c < 8; c++) { gg[c] = __uint_as_float(g[j0 + c]); uu[c] = __uint_as_float(u[j0 + c]); }
+                            swiglu_quant_store<8>(gg, uu, t.nrows - c0 - j0, (size_t)(t.row0 + c0 + j0), Hq, Hs, M_total, blk, lane);
                         }
                     }
                 } else {

@@ -254,17 +254,13 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // the registers hold the tile: TMEM is free again
             if (!t.kind) {
-                const int blk = mrow / Q36_QK, nbh = FF / Q36_QK;
+                const int blk = mrow / Q36_QK;
+                {
+                    float g0[8], u0[8], g1[8], u1[8];
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (j < t.nrows) {
-                        const float h = silu_f(g[j]) * u[j];
-                        const uint32_t am = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h)));
-                        const int e2 = e2_of_amax(__uint_as_float(am));
-                        const size_t row = (size_t)(t.row0 + j);
-                        Hq[row * FF + blk * Q36_QK + hw_pos(lane)] = f32_to_e4m3(h * inv_scale_of_e2(e2));
-                        if (lane == 0) Hs[row * nbh + blk] = (uint8_t)(127 + e2);
-                    }
+                    for (int c = 0; c < 8; c++) { g0[c] = g[c]; u0[c] = u[c]; g1[c] = g[8 + c]; u1[c] = u[8 + c]; }
+                    swiglu_quant_store<8>(g0, u0, t.nrows, (size_t)t.row0, Hq, Hs, FF, blk, lane);
+                    if (t.nrows > 8) swiglu_quant_store<8>(g1, u1, t.nrows - 8, (size_t)t.row0 + 8, Hq, Hs, FF, blk, lane);
                 }
                 __threadfence();         // each lane's stores are visible device-wide before the count moves
                 __syncwarp();

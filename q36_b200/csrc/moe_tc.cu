@@ -69,7 +69,8 @@ struct TcCfg {
     static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // per issuer: A (4), B (4)
     static constexpr int TMEM_COLS = 512;
     static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
-    static constexpr int THREADS = 32 * (1 + ISSUERS + 4 + 4);
+    static constexpr int EPI_WARPS = 8;                      // two per TMEM lane quarter, alternating 32-column chunks
+    static constexpr int THREADS = 32 * (1 + ISSUERS + EPI_WARPS + 4);
 };
 
 // ------------------------------------------------------------- tile plan
@@ -116,7 +117,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full0 + 8 * b, Cfg::ISSUERS);
-            mbar_init(acc_empty0 + 8 * b, 4);              // one arrive per epilogue warp
+            mbar_init(acc_empty0 + 8 * b, Cfg::EPI_WARPS); // one arrive per epilogue warp
         }
         for (int b = 0; b < Cfg::SFR_SLOTS; b++) {
             mbar_init(sfr_full0 + 8 * b, 1);
@@ -233,9 +234,10 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                 if (ok) tc_commit(acc_full0 + 8 * buf);
             }
         }
-    } else if (warp < 1 + Cfg::ISSUERS + 4) {
+    } else if (warp < 1 + Cfg::ISSUERS + Cfg::EPI_WARPS) {
         // -------------------------------------------------------- epilogue
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
+        const int half = (warp - 1 - Cfg::ISSUERS) >> 2;   // which of the quarter's two warps: even or odd 32-column chunks
         uint32_t tcount = 0;
         bool ok = true;
         for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
@@ -245,7 +247,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
             if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;   // weight row (output feature) of this thread
-            for (int c0 = 0; c0 < t.nrows; c0 += 32) {
+            for (int c0 = 32 * half; c0 < t.nrows; c0 += 64) {
                 uint32_t g[32];
                 tc_ld32(tq + c0, g);
                 if (NA == 2) {
@@ -254,12 +256,12 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                     tc_ld_wait();
                     const int blk = mrow / Q36_QK;           // this warp's 32 rows are one scale block
 #pragma unroll
-                    for (int j0 = 0; j0 < 32; j0 += 8) {
-                        if (c0 + j0 < t.nrows) {             // warp-uniform; eight columns per batch for ILP
-                            float gg[8], uu[8];
+                    for (int j0 = 0; j0 < 32; j0 += 16) {
+                        if (c0 + j0 < t.nrows) {             // warp-uniform; sixteen columns per batch for ILP
+                            float gg[16], uu[16];
 #pragma unroll
-                            for (int c = 0; c < 8; c++) { gg[c] = __uint_as_float(g[j0 + c]); uu[c] = __uint_as_float(u[j0 + c]); }
-                            swiglu_quant_store<8>(gg, uu, t.nrows - c0 - j0, (size_t)(t.row0 + c0 + j0), Hq, Hs, M_total, blk, lane);
+                            for (int c = 0; c < 16; c++) { gg[c] = __uint_as_float(g[j0 + c]); uu[c] = __uint_as_float(u[j0 + c]); }
+                            swiglu_quant_store<16>(gg, uu, t.nrows - c0 - j0, (size_t)(t.row0 + c0 + j0), Hq, Hs, M_total, blk, lane);
                         }
                     }
                 } else {
@@ -277,7 +279,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         // --------------------------------------------------- scale loaders
         // Thread i owns row i of the tile: per stage it moves the row's 4 scale bytes of that K step from the
         // staged item into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
-        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + 4);
+        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + Cfg::EPI_WARPS);
         const int w4 = i >> 5, m0 = i & 31;
         const uint32_t my_off = m0 * 16 + w4 * 4;
         uint32_t it = 0, item = 0;

@@ -203,7 +203,7 @@ def run_ours(args):
     dL = [x.to(dev) for x in hL]
     dO = [torch.empty((T, D), dtype=torch.float32, device=dev) for _ in range(NL)]
     ws = layers[0].workspace(T)                   # one scratch, layers run back to back on one stream
-    stack = ep.EPStack(layers, world, rank, T) if world > 1 else None
+    stack = ep.NativeEP(layers, world, rank, T) if world > 1 else None
 
     def step_device():
         if stack is not None:
@@ -229,7 +229,9 @@ def run_ours(args):
     graph = None
     step_device()
     torch.cuda.synchronize()
-    if world == 1:
+    if world > 1:
+        dist.barrier()
+    if world == 1:     # (the expert-parallel step issues NCCL send/recv from native code and is not captured)
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
             step_device()

@@ -216,6 +216,25 @@ int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const voi
 int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
                         void *stream);
 
+/* Native expert-parallel layer step (the role of q36_multi_prefill, q36_engine.cu:4261-4306, with the
+ * reference's gather + sum + broadcast through device 0 replaced by two all-to-alls of routed rows).
+ * One process per GPU; rank r owns experts [r*n_expert/world, (r+1)*n_expert/world) and passes ITS shard's
+ * planes as Wg/Wu/Wd; the shared expert (Sg/Su/Sd, may be NULL) is replicated and runs on the rank's own
+ * tokens.  NCCL is looked up at run time (libnccl.so.2); without it these calls return Q36_MOE_EINVAL.
+ *   q36_moe_ep_unique_id  rank 0 fills 128 bytes that the caller distributes to every rank
+ *   q36_moe_ep_init       collective; returns an opaque communicator
+ *   q36_moe_ep_layer      launch-only: X [T][D], logits [T][stride] of this rank's T tokens -> out [T][D];
+ *                         the exchange uses a fixed capacity of T*k rows per peer, so no count reaches the host
+ *   ws: q36_moe_ep_workspace_bytes(...) bytes; its first 16 bytes are the status words of q36_moe_ws_status. */
+int q36_moe_ep_unique_id(void *out128);
+int q36_moe_ep_init(const void *id128, int rank, int world, void **comm_out);
+int q36_moe_ep_destroy(void *comm);
+uint64_t q36_moe_ep_workspace_bytes(int T, int world, int n_expert, int k, int D, int FF);
+int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd, const void *Sg,
+                     const void *Su, const void *Sd, int n_expert, int k, int D, int FF, const void *X,
+                     int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
+                     float route_scale, float *out, int T, void *ws, uint64_t ws_bytes, void *stream);
+
 /* ---- tensor-core self-check (the role of test_mma_bs.cu:45-175) ----------
  * Runs 128 x N x K block-scaled tcgen05 tiles on caller data and returns the
  * f32 accumulators, so that the operand, scale-factor and descriptor mapping

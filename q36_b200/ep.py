@@ -83,8 +83,20 @@ class DeviceOps:
         return self.m.combine(Y, ypos, wt, SH, shgate, stride, D, k, T)
 
 
+_SOFFS_CACHE: dict = {}
+
+
+def _soffs(R: int, T: int, device) -> torch.Tensor:
+    """Row range of the shared expert's group, built once per shape (a host-to-device copy is not capturable)."""
+    key = (R, T, str(device))
+    if key not in _SOFFS_CACHE:
+        _SOFFS_CACHE[key] = torch.tensor([R, R + T], dtype=torch.int32, device=device)
+    return _SOFFS_CACHE[key]
+
+
 def ep_layer(ops, layer, X, logits, world: int, rank: int, E: int, k: int, path: int, group=None):
-    """One expert-parallel layer step for this rank's T tokens.  Returns out [T,D] f32."""
+    """One expert-parallel layer step for this rank's T tokens.  Returns out [T,D] f32.
+    Launch-only (no host synchronisation), so a whole stack of these can be captured in one CUDA graph."""
     T, D = X.shape
     C = T * k
     per = E // world
@@ -104,7 +116,7 @@ def ep_layer(ops, layer, X, logits, world: int, rank: int, E: int, k: int, path:
     R = world * C
     rows_q = torch.cat([ops.gather_rows(recv_q, _pad_index(llist, R)), Xq], 0)     # sorted rows, then own tokens
     rows_s = torch.cat([ops.gather_rows(recv_s, _pad_index(llist, R)), Xs], 0)
-    soffs = torch.tensor([R, R + T], dtype=torch.int32, device=X.device)
+    soffs = _soffs(R, T, X.device)
     Y = ops.ffn(layer, loffs[se0:], rows_q, rows_s, soffs, path)                  # [R+T, D] f32
     back = ops.gather_rows(Y, lpos)                                               # result row of every received slot
     recv_y = torch.empty_like(back)
@@ -123,6 +135,54 @@ def _pad_index(llist: torch.Tensor, R: int) -> torch.Tensor:
     return out
 
 
+class NativeEP:
+    """The C entry point q36_moe_ep_layer: the whole step (kernels and NCCL send/recv) is issued from native
+    code on the current stream; torch.distributed only carries the 128-byte NCCL id at set-up."""
+    launches_per_layer = 14     # front, quantise, pack, eids, dispatch x3, unpack, plan, gate/up, down, gather, combine (+2 exchanges)
+
+    def __init__(self, layers, world: int, rank: int, T: int):
+        import ctypes as C
+        from . import moe
+        self.moe, self.layers, self.world, self.rank, self.T = moe, layers, world, rank, T
+        dev = layers[0].device
+        idt = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            moe.check(moe.lib.q36_moe_ep_unique_id(buf), "ep_unique_id")
+            idt = torch.tensor(list(buf), dtype=torch.uint8)
+        idt = idt.to(dev)
+        dist.broadcast(idt, src=0)
+        idb = bytes(idt.cpu().tolist())
+        comm = C.c_void_p()
+        moe.check(moe.lib.q36_moe_ep_init(idb, rank, world, C.byref(comm)), "ep_init")
+        self.comm = comm
+        ly = layers[0]
+        n = int(moe.lib.q36_moe_ep_workspace_bytes(T, world, ly.E, ly.k, ly.D, ly.FF))
+        self.ws = torch.empty(n, dtype=torch.uint8, device=dev)
+
+    def layer(self, ly, X, logits, out):
+        m = self.moe
+        stride = logits.shape[1]
+        m.check(m.lib.q36_moe_ep_layer(self.comm, ly.Wg.data_ptr(), ly.Wu.data_ptr(), ly.Wd.data_ptr(), m.ptr(ly.Sg),
+                                       m.ptr(ly.Su), m.ptr(ly.Sd), ly.E, ly.k, ly.D, ly.FF, X.data_ptr(),
+                                       int(X.dtype == torch.bfloat16), logits.data_ptr(), stride,
+                                       ly.E if stride > ly.E else -1, 1.0, out.data_ptr(), X.shape[0], self.ws.data_ptr(),
+                                       self.ws.numel(), m.stream_ptr()), "ep_layer")
+        return out
+
+    def step(self, Xs, Ls, outs):
+        for l, ly in enumerate(self.layers):
+            self.layer(ly, Xs[l], Ls[l], outs[l])
+
+    def check_device_status(self):
+        self.moe.check(self.moe.lib.q36_moe_ws_status(self.ws.data_ptr(), self.moe.stream_ptr()), "device status")
+
+    def close(self):
+        if self.comm:
+            self.moe.lib.q36_moe_ep_destroy(self.comm)
+            self.comm = None
+
+
 class EPStack:
     """A stack of layers stepped expert-parallel; `step` runs every layer on this rank's tokens."""
     launches_per_layer = 17     # kernels of this library per layer step (dispatch x2, quant, gathers x5, FFN x2, combine)
@@ -131,7 +191,7 @@ class EPStack:
         from . import moe
         self.ops = DeviceOps(moe)
         self.layers, self.world, self.rank, self.T, self.group = layers, world, rank, T, group
-        self.path = moe.PATH_GEMV if path is None else path
+        self.path = moe.PATH_TC if path is None else path
 
     def step(self, Xs, Ls, outs):
         for l, layer in enumerate(self.layers):

@@ -39,6 +39,15 @@ def _worker(rank, world, port, q):
         full.check_device_status()
         err = float((out - ref).norm() / ref.norm())
         worst = max(worst, err)
+    # the native entry point (q36_moe_ep_layer): kernels and NCCL send/recv issued from C
+    nat = ep.NativeEP([shard], world, rank, T)
+    for _ in range(3):
+        out = nat.layer(shard, X, L, torch.empty((T, synth.D_MODEL), dtype=torch.float32, device=X.device))
+    torch.cuda.synchronize()
+    nat.check_device_status()
+    ref = full.forward(X, L, path=moe.PATH_TC)
+    worst = max(worst, float((out - ref).norm() / ref.norm()))
+    nat.close()
     q.put((rank, worst))
     dist.barrier()
     dist.destroy_process_group()

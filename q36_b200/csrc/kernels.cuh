@@ -53,9 +53,14 @@ int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int m
 // host helpers of moe_tc.cu shared with moe_tc_fused.cu
 int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride);
 int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows);
+// the same planes seen as [.., K / 128 steps, rows, 128 elements] so that ONE copy fetches `ksteps` consecutive
+// K steps as consecutive 128-byte-swizzled tiles (coordinates: 0, row, K step [, expert])
+int make_map_codes_ksteps(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride, int ksteps);
+int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box_rows, int ksteps);
 int sm_count();
 
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
+int ffn_fused_small_max_rows(int D, int FF);   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
                            uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st);

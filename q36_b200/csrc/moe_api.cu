@@ -253,7 +253,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     void *plan = p + 256;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
     if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, st))) return rc;
-    if (stages == 3 && max_group_rows > 0 && max_group_rows <= 16)
+    if (stages == 3 && max_group_rows > 0 && max_group_rows <= 16 && R_max <= ffn_fused_small_max_rows(D, FF))
         return launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, n_group,
                                       R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, st);
     const int mgr = max_group_rows > 0 ? max_group_rows : R_max;

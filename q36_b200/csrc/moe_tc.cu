@@ -364,6 +364,33 @@ int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, 
     if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
     return Q36_MOE_OK;
 }
+// A thread needs ~140 cycles to issue any asynchronous copy, whatever its size, so the decode kernel fetches
+// several K steps per copy: the K axis is split into (step, 128 elements) and the step index becomes a box
+// dimension AFTER the rows, which lays the steps down as consecutive [rows][128 B] swizzled tiles.
+int make_map_codes_ksteps(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride, int ksteps) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return Q36_MOE_ECUDA;
+    cuuint64_t dims[4] = {128, (cuuint64_t)M, (cuuint64_t)(K / 128), (cuuint64_t)n_group};
+    cuuint64_t strides[3] = {(cuuint64_t)(K / 2), 64, (cuuint64_t)expert_stride};
+    cuuint32_t box[4] = {128, TC_M, (cuuint32_t)ksteps, 1}, el[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, const_cast<void *>(base), dims, strides, box, el,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box_rows, int ksteps) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return Q36_MOE_ECUDA;
+    cuuint64_t dims[3] = {128, (cuuint64_t)R, (cuuint64_t)(K / 128)};
+    cuuint64_t strides[2] = {(cuuint64_t)K, 128};
+    cuuint32_t box[3] = {128, (cuuint32_t)box_rows, (cuuint32_t)ksteps}, el[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, el,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
 // activation rows: [R][K] bytes, boxes of box_rows rows x 128 B
 int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();

@@ -18,17 +18,26 @@
 
 namespace q36 {
 
-// One pipeline stage holds ONE 128-row weight tile of ONE matrix for one K step, the 16 token rows and the
-// two scale images: 19 KB, eleven stages.  A gate/up tile walks K as gate(k0), up(k0), gate(k1), ... so the
-// ring is uniform for both tile kinds and about 110 KB of weight bytes per SM are in flight in both phases
-// (the 2 KB token box is fetched for gate and again for up: L2 hits).
+// What sets the layout (all measured on B200, see ub_tma_rate.cu and ub_mma_issue.cu):
+//  * a thread needs ~140 cycles to issue ANY asynchronous copy, so a stage is TWO K steps fetched by two copies
+//    (one 4-bit weight box of 2 x [128 rows][128 elements], one box of 2 x [16 token rows][128 B]);
+//  * a thread gets one block-scaled MMA through per ~90-110 cycles, the pipe takes one per ~40, so FOUR warps
+//    issue, each into its own accumulator columns: warps 0,1 the two K steps of the even stages, warps 2,3 of
+//    the odd ones.  A gate/up tile alternates gate and up stages, hence gate = acc0 + acc1, up = acc2 + acc3; a
+//    down tile (2 stages) is the sum of all four;
+//  * every role looks its tile up in a table built once per CTA (a binary search per tile per role cost ~900
+//    cycles, more than a down tile's share of the HBM stream);
+//  * the scale bytes have their own producer thread, so the two serial issue chains run side by side.
 struct FusedCfg {
-    static constexpr int STAGES = 9;
-    static constexpr int A_BYTES = TC_M * 128;
+    static constexpr int STAGES = 4;
+    static constexpr int KS = 2;                     // K steps per stage
+    static constexpr int A_BYTES = TC_M * 128;       // one K step of one matrix, 4-bit codes in 8-bit containers
     static constexpr int A_TX_BYTES = TC_M * 64;     // the A box signals its packed bytes (see moe_tc.cu)
     static constexpr int B_BYTES = 16 * 128;
     static constexpr int SF_BYTES = 512;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;   // 19 KB, 1024-aligned
+    static constexpr int OFF_B = KS * A_BYTES, OFF_SF = OFF_B + KS * B_BYTES;
+    static constexpr int STAGE_BYTES = OFF_SF + KS * 2 * SF_BYTES;          // 38 KB, 1024-aligned
+    static constexpr int STAGE_TX = KS * (A_TX_BYTES + B_BYTES);
     // Scale bytes of a whole tile (all its K steps) are staged by bulk async copies, two tiles deep: the rows
     // of a tile are contiguous in the row-major scale planes (128 rows x K/32 bytes).  Loads issued by the
     // loader threads themselves were measured to expose a full HBM latency per 4 K steps (register prefetch
@@ -38,17 +47,17 @@ struct FusedCfg {
     static constexpr int SFT_BYTES = 2 * SFT_A + SFT_B;      // 17 KB: gate (or down), up, tokens
     static constexpr int SFT_SLOTS = 2;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFT_SLOTS * SFT_BYTES + 1024 + 256;
-    // Measured on B200 (block-scaled kind::mxf8f6f4, M = 128, K = 32): ONE issuing thread gets an MMA through
-    // every ~90 cycles whatever N <= 128 is; TWO issuing warps reach the pipe's own floor of ~40 cycles per
-    // MMA; more issuers add nothing.  So two warps issue, on alternate stages (gate | up, or even | odd K
-    // steps of a down tile), each into its own accumulator columns and its own scale columns.
-    static constexpr int ISSUERS = 2;
-    static constexpr int ACC_STRIDE = 32;            // per accumulator set: issuer 0 at [0,16), issuer 1 at [16,32)
-    static constexpr int SF_COL0 = 64;               // per issuer: A (4), B (4)
-    static constexpr int TMEM_COLS = 128;
-    static constexpr int THREADS = 32 * (1 + ISSUERS + 4 + 4);   // producer, issuers, epilogue, scale loaders
+    static constexpr int ISSUERS = 4;
+    static constexpr int ACC_STRIDE = 64;            // per accumulator set: issuer w at [16 w, 16 w + 16)
+    static constexpr int SF_COL0 = 128;              // per issuer: A (4), B (4)
+    static constexpr int TMEM_COLS = 256;
+    static constexpr int W_ISSUE0 = 2, W_EPI0 = W_ISSUE0 + ISSUERS, W_LOAD0 = W_EPI0 + 4;
+    static constexpr int THREADS = 32 * (W_LOAD0 + 4);   // weight producer, scale producer, issuers, epilogue, scale loaders
     static constexpr int DONE_PER_GROUP_PER_MTILE = 4;   // epilogue warps
+    static constexpr int MAX_GROUPS = DISPATCH_MAX_GROUPS + 1;   // the plan lists every group, empty ones included
+    static constexpr int MAX_TILES = 32;                 // per CTA
 };
+static_assert(FusedCfg::STAGE_BYTES % 1024 == 0, "stage alignment");
 
 struct FusedMaps { CUtensorMap g, u, d, sg, su, sd, x, h; };
 
@@ -67,9 +76,9 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     uint64_t *bars = reinterpret_cast<uint64_t *>(sft + Cfg::SFT_SLOTS * Cfg::SFT_BYTES);
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
-    // (16-bit where the value allows it: static + dynamic shared memory sit 1.7 KB under the 227 KB limit)
-    __shared__ int s_row0[DISPATCH_MAX_GROUPS + 1], s_base0[DISPATCH_MAX_GROUPS + 2], s_base1[DISPATCH_MAX_GROUPS + 2];
-    __shared__ unsigned short s_order[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1];
+    __shared__ int s_row0[Cfg::MAX_GROUPS + 1], s_base0[Cfg::MAX_GROUPS + 2], s_base1[Cfg::MAX_GROUPS + 2];
+    __shared__ unsigned short s_order[Cfg::MAX_GROUPS + 1], s_cnt[Cfg::MAX_GROUPS + 1];
+    __shared__ int4 s_tiles[Cfg::MAX_TILES];       // x = group | kind << 16, y = row tile, z = first row, w = rows
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::STAGES);
@@ -80,8 +89,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < Cfg::STAGES; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4);
-            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, 1 + 4);              // the producer's expect_tx arrive + one per scale warp
+            mbar_init(empty0 + 8 * s, 2);                 // one tcgen05.commit per issuing warp of the stage
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(sft_full0 + 8 * b, 1);              // producer's expect_tx arrive
@@ -91,7 +100,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == Cfg::W_ISSUE0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -100,7 +109,13 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     const int G = plan->n_groups;
     const int n0 = plan->n_tiles[0], n_tiles = n0 + plan->n_tiles[1];
     const int mt_gu = FF / TC_M;
-    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
+    int my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const bool fits = G <= Cfg::MAX_GROUPS && my_tiles <= Cfg::MAX_TILES;
+    if (!fits) {                                   // (uniform over the CTA) nothing is computed, the status says so
+        my_tiles = 0;
+        if (threadIdx.x == 0) atomicCAS(status, 0, 0x900);
+    }
+    for (int i = threadIdx.x; i <= G && fits; i += blockDim.x) {
         s_base0[i] = plan->base[0][i];
         s_base1[i] = plan->base[1][i];
         if (i < G) { s_order[i] = (unsigned short)plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = (unsigned short)plan->cnt[i]; }
@@ -109,8 +124,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-
-    auto get_tile = [&](int ti) {
+    if ((int)threadIdx.x < my_tiles) {             // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
+        const int ti = blockIdx.x + threadIdx.x * gridDim.x;
         const int kind = ti >= n0;
         const int *base = kind ? s_base1 : s_base0;
         const int t = kind ? ti - n0 : ti;
@@ -120,7 +135,12 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             if (base[mid] <= t) lo = mid; else hi = mid - 1;
         }
         const int g = s_order[lo];
-        return FTile{kind, g, t - base[lo], s_row0[g], s_cnt[g]};   // one token tile per group: mt = local index
+        s_tiles[threadIdx.x] = make_int4(g | (kind << 16), t - base[lo], s_row0[g], s_cnt[g]);   // one token tile per group
+    }
+    __syncthreads();
+    auto get_tile = [&](int j) {
+        const int4 v = s_tiles[j];
+        return FTile{v.x >> 16, v.x & 0xffff, v.y, v.z, v.w};
     };
     // gate/up of group g is complete when every epilogue warp of each of its row tiles has published
     const int done_target = mt_gu * Cfg::DONE_PER_GROUP_PER_MTILE;
@@ -137,117 +157,129 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         atomicCAS(status, 0, where);
         return false;
     };
+    // A down tile reads Hq/Hs written through the generic proxy, possibly by other SMs: wait for the group's
+    // count, then order those writes before this thread's asynchronous reads.
+    auto wait_inputs = [&](const FTile &t, bool &all_gu_done, int where) -> bool {
+        if (!t.kind || all_gu_done) return true;
+        if (!wait_group(t.g, where)) return false;
+        int v;   // after the wait (acquire): if the whole gate/up phase is over, later tiles need no poll
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(&plan->gu_done) : "memory");
+        all_gu_done = v >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;
+        asm volatile("fence.proxy.async;" ::: "memory");
+        return true;
+    };
 
     if (warp == 0) {
-        // ---------------------------------------------------- TMA producer
+        // ------------------------------------------- TMA producer: weights and token rows
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            uint32_t it = 0;
             bool ok = true, all_gu_done = false;
-            for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
-                const FTile t = get_tile(ti);
+            for (int j = 0; j < my_tiles && ok; j++) {
+                const FTile t = get_tile(j);
                 const bool sh = t.g >= n_routed;
                 const int ge = sh ? 0 : t.g;
-                const int na = t.kind ? 1 : 2;
-                const int k_steps = (t.kind ? FF : D) / TC_KSTEP;
                 const CUtensorMap *ma0 = t.kind ? (sh ? &maps.sd : &maps.d) : (sh ? &maps.sg : &maps.g);
                 const CUtensorMap *ma1 = sh ? &maps.su : &maps.u;
                 const CUtensorMap *mb = t.kind ? &maps.h : &maps.x;
-                if (t.kind && !all_gu_done) {
-                    if (!(ok = wait_group(t.g, 0x600))) break;
-                    int v;   // after the wait (acquire): if the whole gate/up phase is over, later tiles need no poll
-                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(&plan->gu_done) : "memory");
-                    all_gu_done = v >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;
-                    asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy Hq stores before the TMA reads
-                }
-                {   // the tile's scale bytes: contiguous runs of the row-major planes
-                    const uint32_t slot = tcount & 1;
-                    if (!(ok = mbar_wait(sft_empty0 + 8 * slot, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x800 + slot))) break;
-                    const int nbk = (t.kind ? FF : D) / Q36_QK;
-                    const uint32_t a_bytes = TC_M * nbk, b_bytes = t.nrows * nbk;
-                    const size_t arow = (size_t)ge * sf_stride + (size_t)(t.mt * TC_M) * nbk;
-                    const uint8_t *p0 = t.kind ? (sh ? sfSD : sfD) : (sh ? sfSG : sfG);
-                    const uint32_t dst = smem_u32(sft + slot * Cfg::SFT_BYTES);
-                    mbar_expect_tx(sft_full0 + 8 * slot, a_bytes * na + b_bytes);
-                    bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
-                    if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
-                    bulk_load(dst + 2 * Cfg::SFT_A, (t.kind ? Hs : Xs) + (size_t)t.row0 * nbk, b_bytes, sft_full0 + 8 * slot);
-                    tcount++;
-                }
-                const uint32_t tx = Cfg::A_TX_BYTES + Cfg::B_BYTES;
-                const int steps = k_steps * na;            // gate/up: gate(k0), up(k0), gate(k1), ...
-                for (int j = 0; j < steps; j++, it++) {
-                    const int ks = t.kind ? j : (j >> 1);
+                if (!(ok = wait_inputs(t, all_gu_done, 0x600))) break;
+                const int nst = t.kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));   // gate, up, gate, ...
+                for (int q = 0; q < nst; q++, it++) {
+                    const int kpair = t.kind ? q : (q >> 1);
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    mbar_expect_tx(full0 + 8 * s, tx);
-                    tma_load_3d(sb, (!t.kind && (j & 1)) ? ma1 : ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
-                    tma_load_2d(sb + Cfg::A_BYTES, mb, ks * TC_KSTEP, t.row0, full0 + 8 * s);
+                    mbar_expect_tx(full0 + 8 * s, Cfg::STAGE_TX);
+                    tma_load_4d(sb, (!t.kind && (q & 1)) ? ma1 : ma0, 0, t.mt * TC_M, kpair * Cfg::KS, ge, full0 + 8 * s);
+                    tma_load_3d(sb + Cfg::OFF_B, mb, 0, t.row0, kpair * Cfg::KS, full0 + 8 * s);
                 }
             }
         }
-    } else if (warp <= Cfg::ISSUERS) {
+    } else if (warp == 1) {
+        // --------------------------- scale producer: a tile's scale bytes, contiguous runs of the row-major planes
+        if (lane == 0) {
+            bool ok = true, all_gu_done = false;
+            for (int j = 0; j < my_tiles && ok; j++) {
+                const FTile t = get_tile(j);
+                const bool sh = t.g >= n_routed;
+                const int ge = sh ? 0 : t.g;
+                const uint32_t slot = j & 1;
+                if (!(ok = wait_inputs(t, all_gu_done, 0x680))) break;
+                if (!(ok = mbar_wait(sft_empty0 + 8 * slot, ((j >> 1) & 1) ^ 1, &abort_flag, status, 0x800 + slot))) break;
+                const int nbk = (t.kind ? FF : D) / Q36_QK;
+                const uint32_t a_bytes = TC_M * nbk, b_bytes = t.nrows * nbk;
+                const size_t arow = (size_t)ge * sf_stride + (size_t)(t.mt * TC_M) * nbk;
+                const uint8_t *p0 = t.kind ? (sh ? sfSD : sfD) : (sh ? sfSG : sfG);
+                const uint32_t dst = smem_u32(sft + slot * Cfg::SFT_BYTES);
+                mbar_expect_tx(sft_full0 + 8 * slot, a_bytes * (t.kind ? 1 : 2) + b_bytes);
+                bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
+                if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
+                bulk_load(dst + 2 * Cfg::SFT_A, (t.kind ? Hs : Xs) + (size_t)t.row0 * nbk, b_bytes, sft_full0 + 8 * slot);
+            }
+        }
+    } else if (warp < Cfg::W_EPI0) {
         // ----------------------------------------------------- MMA issuers
         if (lane == 0) {
-            const int w = warp - 1;                         // stages with (step & 1) == w are this warp's
+            const int w = warp - Cfg::W_ISSUE0;
+            const int par = w >> 1, h = w & 1;             // stages with (stage & 1) == par, K step h of the stage
             const uint32_t t_sfa = tmem + Cfg::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
-            uint32_t it0 = 0, tcount = 0;
+            uint32_t it0 = 0;
             bool ok = true;
-            for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-                const FTile t = get_tile(ti);
-                const int steps = ((t.kind ? FF : D) / TC_KSTEP) * (t.kind ? 1 : 2);
-                const uint32_t buf = tcount & 1;
+            for (int j = 0; j < my_tiles && ok; j++) {
+                const int kind = s_tiles[j].x >> 16;
+                const int nst = kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));
+                const uint32_t buf = j & 1;
                 const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE + 16 * w;
-                if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
+                if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
                 tc_fence_after();
                 bool first = true;
-                for (int j = w; j < steps; j += Cfg::ISSUERS) {
-                    const uint32_t it = it0 + j;
+                for (int q = par; q < nst; q += 2) {
+                    const uint32_t it = it0 + q;
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
                     tc_fence_after();
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t sf = sb + Cfg::A_BYTES + Cfg::B_BYTES;
+                    const uint32_t sa = sb + h * Cfg::A_BYTES, sbb = sb + Cfg::OFF_B + h * Cfg::B_BYTES;
+                    const uint32_t sf = sb + Cfg::OFF_SF + h * 2 * Cfg::SF_BYTES;
                     tc_cp_sf(t_sfa, desc_sf(sf));
                     tc_cp_sf(t_sfb, desc_sf(sf + Cfg::SF_BYTES));
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++) {
                         const uint32_t sfid = (uint32_t)kb << 30;
-                        tc_mma(d_tmem, desc_sw128(sb + kb * 32), desc_sw128(sb + Cfg::A_BYTES + kb * 32), idesc_mx(16, kb),
+                        tc_mma(d_tmem, desc_sw128(sa + kb * 32), desc_sw128(sbb + kb * 32), idesc_mx(16, kb),
                                t_sfa | sfid, t_sfb | sfid, (first && kb == 0) ? 0u : 1u);
                     }
                     first = false;
                     tc_commit(empty0 + 8 * s);
                 }
-                it0 += steps;
+                it0 += nst;
                 if (ok) tc_commit(acc_full0 + 8 * buf);
             }
         }
-    } else if (warp < 1 + Cfg::ISSUERS + 4) {
+    } else if (warp < Cfg::W_LOAD0) {
         // -------------------------------------------------------- epilogue
-        const int q = warp & 3;
-        uint32_t tcount = 0;
+        const int q = warp & 3;                            // the TMEM lane quadrant this warp may read
         bool ok = true;
-        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-            const FTile t = get_tile(ti);
-            const uint32_t buf = tcount & 1;
+        for (int j = 0; j < my_tiles && ok; j++) {
+            const FTile t = get_tile(j);
+            const uint32_t buf = j & 1;
             const uint32_t tq = tmem + buf * Cfg::ACC_STRIDE + ((uint32_t)(q * 32) << 16);
-            if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
+            if (!(ok = mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;
-            // columns [0,16): issuer 0 (gate, or the even K steps of a down tile); [16,32): issuer 1 (up / odd)
+            // four partial sums of 16 token columns each (see FusedCfg)
             float g[16], u[16];
             {
-                uint32_t r0[32];
+                uint32_t r0[32], r1[32];
                 tc_ld32(tq, r0);
+                tc_ld32(tq + 32, r1);
                 tc_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    g[j] = __uint_as_float(r0[j]);
-                    u[j] = __uint_as_float(r0[16 + j]);
-                    if (t.kind) g[j] += u[j];
+                for (int c = 0; c < 16; c++) {
+                    g[c] = __uint_as_float(r0[c]) + __uint_as_float(r0[16 + c]);
+                    u[c] = __uint_as_float(r1[c]) + __uint_as_float(r1[16 + c]);
+                    if (t.kind) g[c] += u[c];
                 }
             }
             tc_fence_before();
@@ -270,43 +302,45 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; j++)
-                    if (j < t.nrows) Y[(size_t)(t.row0 + j) * D + mrow] = g[j];
+                for (int c = 0; c < 16; c++)
+                    if (c < t.nrows) Y[(size_t)(t.row0 + c) * D + mrow] = g[c];
             }
         }
     } else {
         // --------------------------------------------------- scale loaders
-        // Thread i owns row i of the tile: per stage it moves the row's 4 scale bytes of that K step from the
-        // staged plane rows into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
-        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + 4);
+        // Thread i owns row i of the tile: per K step it moves the row's 4 scale bytes from the staged plane
+        // rows into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
+        const int i = threadIdx.x - 32 * Cfg::W_LOAD0;
         const int w4 = i >> 5, m0 = i & 31;
         const uint32_t my_off = m0 * 16 + w4 * 4;
-        uint32_t it = 0, tcount = 0;
+        uint32_t it = 0;
         bool ok = true;
-        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-            const FTile t = get_tile(ti);
-            const uint32_t slot = tcount & 1;
+        for (int j = 0; j < my_tiles && ok; j++) {
+            const FTile t = get_tile(j);
+            const uint32_t slot = j & 1;
             const int nbk = (t.kind ? FF : D) / Q36_QK;
-            const int steps = (nbk / 4) * (t.kind ? 1 : 2);
-            if (!(ok = mbar_wait(sft_full0 + 8 * slot, (tcount >> 1) & 1, &abort_flag, status, 0x700 + slot))) break;
+            const int nst = t.kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));
+            if (!(ok = mbar_wait(sft_full0 + 8 * slot, (j >> 1) & 1, &abort_flag, status, 0x700 + slot))) break;
             const uint8_t *st = sft + slot * Cfg::SFT_BYTES;
             const uint8_t *ra0 = st + i * nbk, *ra1 = st + Cfg::SFT_A + i * nbk, *rb = st + 2 * Cfg::SFT_A + i * nbk;
             const bool bvalid = i < t.nrows;
-            for (int j0 = 0; j0 < steps && ok; j0 += 4) {   // four stages per cross-proxy fence
+            for (int q0 = 0; q0 < nst && ok; q0 += 2) {   // two stages (four K steps) per cross-proxy fence
                 const uint32_t it0 = it;
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
-                    const int j = j0 + jj;
-                    const int ks = t.kind ? j : (j >> 1);
-                    const bool up = !t.kind && (j & 1);
-                    const uint32_t va = *reinterpret_cast<const uint32_t *>((up ? ra1 : ra0) + 4 * ks);
-                    const uint32_t vb = bvalid ? *reinterpret_cast<const uint32_t *>(rb + 4 * ks) : 0x7f7f7f7fu;
+                for (int qq = 0; qq < 2; qq++) {
+                    const int q = q0 + qq;
+                    const int kpair = t.kind ? q : (q >> 1);
+                    const uint8_t *ra = (!t.kind && (q & 1)) ? ra1 : ra0;
+                    const uint2 va = *reinterpret_cast<const uint2 *>(ra + 8 * kpair);       // 2 K steps x 4 scale bytes
+                    const uint2 vb = bvalid ? *reinterpret_cast<const uint2 *>(rb + 8 * kpair) : make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
-                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES + Cfg::B_BYTES;
-                    *reinterpret_cast<uint32_t *>(sf + my_off) = va;
-                    *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = vb;
+                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + Cfg::OFF_SF;
+                    *reinterpret_cast<uint32_t *>(sf + my_off) = va.x;
+                    *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = vb.x;
+                    *reinterpret_cast<uint32_t *>(sf + 2 * Cfg::SF_BYTES + my_off) = va.y;
+                    *reinterpret_cast<uint32_t *>(sf + 3 * Cfg::SF_BYTES + my_off) = vb.y;
                     it++;
                 }
                 if (!ok) break;
@@ -327,30 +361,33 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         for (int i = 0; i < 200; i++) __nanosleep(1000);
         if (threadIdx.x == 0) atomicCAS(status, 0, 1);
     }
-    if (warp == 1) {
+    if (warp == Cfg::W_ISSUE0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
+// every non-empty group has at least one row and one token tile, so the row count bounds the tiles of a CTA
+int ffn_fused_small_max_rows(int D, int FF) { return FusedCfg::MAX_TILES * sm_count() / (FF / TC_M + D / TC_M); }
+
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
                            uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st) {
     using Cfg = FusedCfg;
-    if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || n_group + 1 > Cfg::MAX_GROUPS || R_max > ffn_fused_small_max_rows(D, FF)) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)FF * (D / 2) + (uint64_t)FF * (D / Q36_QK);   // same for [FF][D] and [D][FF]
     const uint64_t plane = (uint64_t)FF * (D / 2);
     if (!Sg) { Sg = Wg; Su = Wu; Sd = Wd; }
     FusedMaps maps;
     int rc;
-    if ((rc = make_map_codes(&maps.g, Wg, FF, D, n_group, estride))) return rc;
-    if ((rc = make_map_codes(&maps.u, Wu, FF, D, n_group, estride))) return rc;
-    if ((rc = make_map_codes(&maps.d, Wd, D, FF, n_group, estride))) return rc;
-    if ((rc = make_map_codes(&maps.sg, Sg, FF, D, 1, estride))) return rc;
-    if ((rc = make_map_codes(&maps.su, Su, FF, D, 1, estride))) return rc;
-    if ((rc = make_map_codes(&maps.sd, Sd, D, FF, 1, estride))) return rc;
-    if ((rc = make_map_rows(&maps.x, Xq, R_max, D, 16))) return rc;
-    if ((rc = make_map_rows(&maps.h, Hq, R_max, FF, 16))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.g, Wg, FF, D, n_group, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.u, Wu, FF, D, n_group, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.d, Wd, D, FF, n_group, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.sg, Sg, FF, D, 1, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.su, Su, FF, D, 1, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.sd, Sd, D, FF, 1, estride, Cfg::KS))) return rc;
+    if ((rc = make_map_rows_ksteps(&maps.x, Xq, R_max, D, 16, Cfg::KS))) return rc;
+    if ((rc = make_map_rows_ksteps(&maps.h, Hq, R_max, FF, 16, Cfg::KS))) return rc;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_ffn_fused_small, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)

@@ -55,6 +55,12 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t a, uint32_t parity, vola
     __syncwarp();   // the lanes' later accesses are ordered after lane 0's acquire
     return ok != 0;
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"

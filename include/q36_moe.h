@@ -161,7 +161,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
 /* k_moe_combine / k_moe_combine_pf (q36_engine.cu:785-791, 3393-3401):
  *   out[t][i] = sum_{s<k} wt[t][s] * Y_rows[pos[t*k+s]][i]          (pos >= 0)
  *             + (SH_rows ? sigmoid(shgate[t*shgate_stride]) * SH_rows[t][i] : 0)
- * in slot order; shgate == NULL means gate 1.  */
+ * in slot order; shgate == NULL means gate 1.  1 <= k <= 8. */
 int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float *wt,
                     const float *SH_rows, const float *shgate, int shgate_stride, int D, int k,
                     int T, void *stream);

@@ -92,8 +92,16 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     int rc;
     const bool use_tc = pick_path(path, T) == Q36_MOE_PATH_TC;
     const bool fused_front = n <= 1024;
-    const bool fused_quant = fused_front && T <= 2;     // beyond a couple of rows the scatter serialises inside one block: measured slower than a launch
-    if (fused_front) {
+    static const bool no_cluster = getenv("Q36_NOCLUSTER") != nullptr;
+    // decode on the tensor-core path with every expert resident: one cluster launch does all of the front end
+    const bool cluster_front = use_tc && T <= 16 && n <= 128 && se0 == 0 && se1 == E && D * T <= 16 * 2048 && !no_cluster;
+    const bool fused_quant = cluster_front || (fused_front && T <= 2);     // beyond a couple of rows the scatter serialises inside one block: measured slower than a launch
+    if (cluster_front) {
+        if ((rc = launch_front_decode(logits, E, k, route_scale, T, logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
+                                      w.pos, w.soffs, n, shared ? n + T : n, w.plan, D, FF, w.status, X, x_is_bf16, w.Xq,
+                                      w.Xs, shared ? n : -1, st)))
+            return rc;
+    } else if (fused_front) {
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, se0, se1, w.idx, w.wt, w.ecount, w.eoffs,
                                      w.elist, w.pos, w.soffs, n, shared ? n + T : n, use_tc ? w.plan : nullptr, D, FF,
                                      w.status, fused_quant ? X : nullptr, x_is_bf16, w.Xq, w.Xs, shared ? n : -1, st)))

@@ -211,20 +211,34 @@ k_combine(float *__restrict__ out, const float *__restrict__ Y, const int *__res
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= D) return;
+    // All row positions, then all rows, are fetched before the first add: a loop that loads pos -> row -> adds
+    // pays two dependent memory latencies per slot, which at decode sizes is the whole kernel.  The sum itself
+    // keeps the slot order.
+    constexpr int KMAX = 8;
+    int p[KMAX];
+    float w[KMAX];
+    float4 y[KMAX];
+#pragma unroll
+    for (int s = 0; s < KMAX; s++) {
+        p[s] = (s < k) ? pos[(size_t)t * k + s] : -1;
+        w[s] = (s < k) ? wt[(size_t)t * k + s] : 0.f;
+    }
+    const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
+    float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (SH) ysh = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
+#pragma unroll
+    for (int s = 0; s < KMAX; s++)
+        y[s] = (p[s] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[s] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < k; s++) {
-        const int p = pos[(size_t)t * k + s];
-        if (p < 0) continue;
-        const float w = wt[(size_t)t * k + s];
-        const float4 y = *reinterpret_cast<const float4 *>(Y + (size_t)p * D + i);
-        acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
-        acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
+#pragma unroll
+    for (int s = 0; s < KMAX; s++) {
+        if (p[s] < 0) continue;
+        acc.x = fmaf(w[s], y[s].x, acc.x); acc.y = fmaf(w[s], y[s].y, acc.y);
+        acc.z = fmaf(w[s], y[s].z, acc.z); acc.w = fmaf(w[s], y[s].w, acc.w);
     }
     if (SH) {
-        const float gs = shgate ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
-        const float4 y = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
-        acc.x = fmaf(gs, y.x, acc.x); acc.y = fmaf(gs, y.y, acc.y);
-        acc.z = fmaf(gs, y.z, acc.z); acc.w = fmaf(gs, y.w, acc.w);
+        acc.x = fmaf(gs, ysh.x, acc.x); acc.y = fmaf(gs, ysh.y, acc.y);
+        acc.z = fmaf(gs, ysh.z, acc.z); acc.w = fmaf(gs, ysh.w, acc.w);
     }
     *reinterpret_cast<float4 *>(out + (size_t)t * D + i) = acc;
 }
@@ -282,6 +296,7 @@ int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
                    const float *shgate, int shgate_stride, int D, int k, int T, cudaStream_t st) {
     if (T <= 0) return Q36_MOE_OK;
+    if (k <= 0 || k > 8) return Q36_MOE_EINVAL;   // the kernel keeps one row per slot in registers
     dim3 grid((D / 4 + 255) / 256, T);
     launch_k(k_combine, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
     return check_launch();

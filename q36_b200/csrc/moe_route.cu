@@ -1,4 +1,5 @@
 // Routing, deterministic dispatch and the activation quantiser.
+#include <cooperative_groups.h>
 #include <stdio.h>
 
 #include "common.cuh"
@@ -193,6 +194,38 @@ __device__ __forceinline__ void quant_task(float v, uint8_t *__restrict__ Xq, ui
     }
 }
 
+
+// The two halves of quant_task<true>, for a kernel that quantises before it knows where the rows go.
+// quant_pack: lane l ends up with word (l & 7) of the block's 32 codes in hw order, and the block exponent.
+__device__ __forceinline__ void quant_pack(float v, int lane, uint32_t &word, int &e2) {
+    const float a = warp_max(fabsf(v));
+    e2 = e2_of_amax(a);
+    const uint8_t q = f32_to_e4m3(v * inv_scale_of_e2(e2));
+    const int src = (lane & 1) ? (16 + (lane >> 1)) : (lane >> 1);
+    const uint32_t qp = __shfl_sync(0xffffffffu, (uint32_t)q, src);
+    uint32_t w = qp;
+    w |= __shfl_down_sync(0xffffffffu, qp, 1) << 8;
+    w |= __shfl_down_sync(0xffffffffu, qp, 2) << 16;
+    w |= __shfl_down_sync(0xffffffffu, qp, 3) << 24;
+    word = __shfl_sync(0xffffffffu, w, (lane & 7) * 4);
+}
+// quant_put: the block goes to every row of the sorted space token t feeds (its k slots, then its shared row)
+__device__ __forceinline__ void quant_put(uint32_t word, int e2, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int t,
+                                          int b, int K, const int *pos, int k, int shared_row0, int lane) {
+    const int nb = K / Q36_QK;
+    const int n_dst = k + (shared_row0 >= 0 ? 1 : 0);
+    for (int d0 = 0; d0 < n_dst; d0 += 4) {
+        const int d = d0 + (lane >> 3);
+        if (d < n_dst) {
+            const int row = (d < k) ? __ldcg(pos + (size_t)t * k + d) : (shared_row0 + t);
+            if (row >= 0) {
+                ((uint32_t *)(Xq + (size_t)row * K + (size_t)b * Q36_QK))[lane & 7] = word;
+                if ((lane & 7) == 0) Xs[(size_t)row * nb + b] = (uint8_t)(127 + e2);
+            }
+        }
+    }
+}
+
 template <bool BF16, bool SCATTER>
 __global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ Xq,
                              uint8_t *__restrict__ Xs, int T, int K, const int *__restrict__ pos,
@@ -310,6 +343,168 @@ int launch_front_small(const float *logits, int n_expert, int k, float scale, in
     launch_k(k_front_small, dim3(1), dim3(1024), 0, st, logits, n_expert, k, scale, T, row_stride, se0, se1, idx, wt,
              ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D,
              shared_row0);
+    return check_launch();
+}
+
+
+// ----------------------------------------------- decode front end: one cluster
+// At most 16 tokens (T * k <= 128 entries), all experts resident.  One thread-block cluster, one launch:
+//   CTA 0        router -> stable dispatch -> work plan of the fused tensor-core kernel
+//   CTAs 1..7    quantise the token rows (needs no routing result), wait at the cluster barrier for CTA 0's
+//                row positions, then write every block to the k + 1 rows it feeds.
+// Same results as k_front_small + k_quant_e4m3<., true>: the same route_row, the same ascending-entry order
+// inside an expert's bucket, the same quantiser.
+constexpr int FD_CLUSTER = 8;
+constexpr int FD_THREADS = 1024;
+constexpr int FD_MAX_ENTRIES = 128;
+constexpr int FD_MAX_TASKS = 8;                                   // (row, block) tasks per quantising warp
+constexpr int FD_QWARPS = (FD_CLUSTER - 1) * (FD_THREADS / 32);
+
+__global__ void __launch_bounds__(FD_THREADS)
+k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scale, int T, int row_stride,
+               int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
+               int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan,
+               int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16, uint8_t *__restrict__ Xq,
+               uint8_t *__restrict__ Xs, int D, int shared_row0) {
+    Q36_GDS();
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n = T * k;
+    if (cluster.block_rank() != 0) {
+        // ---- quantise now, place after the barrier
+        const int nbk = D / Q36_QK, ntask = T * nbk;
+        const int qw = ((int)cluster.block_rank() - 1) * (FD_THREADS / 32) + warp;
+        uint32_t word[FD_MAX_TASKS];
+        int e2[FD_MAX_TASKS];
+        float v[FD_MAX_TASKS];
+#pragma unroll
+        for (int j = 0; j < FD_MAX_TASKS; j++) {
+            const int task = qw + j * FD_QWARPS;
+            v[j] = (task < ntask) ? quant_load(X, x_is_bf16 != 0, task / nbk, task % nbk, D, lane) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < FD_MAX_TASKS; j++) quant_pack(v[j], lane, word[j], e2[j]);
+        cluster.sync();
+#pragma unroll
+        for (int j = 0; j < FD_MAX_TASKS; j++) {
+            const int task = qw + j * FD_QWARPS;
+            if (task < ntask) quant_put(word[j], e2[j], Xq, Xs, task / nbk, task % nbk, D, pos, k, shared_row0, lane);
+        }
+        return;
+    }
+    // ---- CTA 0: route, sort, plan
+    __shared__ unsigned short cnt[FD_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // per (entry warp, expert): count, then base
+    __shared__ int s_idx[FD_MAX_ENTRIES];
+    __shared__ float s_wt[FD_MAX_ENTRIES];
+    __shared__ int s_eoffs[DISPATCH_MAX_E + 1];
+    __shared__ int s_wsum[FD_THREADS / 32];
+    const int used_warps = (n + 31) / 32;
+    if (warp < T) {
+        const float *l = logits + (size_t)warp * row_stride;
+        if (n_expert == 256) route_row<8>(l, k, s_idx + warp * k, s_wt + warp * k, scale, 1, lane);
+        else if (n_expert == 128) route_row<4>(l, k, s_idx + warp * k, s_wt + warp * k, scale, 1, lane);
+        else if (n_expert == 64) route_row<2>(l, k, s_idx + warp * k, s_wt + warp * k, scale, 1, lane);
+        else route_row<1>(l, k, s_idx + warp * k, s_wt + warp * k, scale, 1, lane);
+    } else {
+        for (int i = tid - 32 * T; i < used_warps * DISPATCH_MAX_E; i += FD_THREADS - 32 * T) (&cnt[0][0])[i] = 0;
+        if (status && lane < 4 && warp == T) status[lane] = 0;
+    }
+    __syncthreads();
+    int e = -1;
+    if (tid < n) {
+        e = s_idx[tid];
+        idx[tid] = e;
+        wt[tid] = s_wt[tid];
+        if (e >= n_expert) e = -1;
+    }
+    int r_in_warp = 0;
+    if (warp < used_warps) {
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        r_in_warp = __popc(peers & ((1u << lane) - 1u));
+        if (e >= 0 && r_in_warp == 0) cnt[warp][e] = (unsigned short)__popc(peers);
+    }
+    __syncthreads();
+    // per expert: rows, and (one scan for both) rows before it | non-empty experts before it << 16
+    int tot = 0;
+    if (tid < n_expert) {
+        for (int w = 0; w < used_warps; w++) {
+            const int c = cnt[w][tid];
+            cnt[w][tid] = (unsigned short)tot;
+            tot += c;
+        }
+    }
+    const int val = tot | ((tot > 0) << 16);
+    int incl = val;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    if (lane == 31) s_wsum[warp] = incl;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; w++) before += s_wsum[w];
+    const int excl = before + incl - val;
+    if (tid < n_expert) {
+        const int row0 = excl & 0xffff, ne = excl >> 16;
+        s_eoffs[tid] = row0;
+        ecount[tid] = tot;
+        eoffs[tid] = row0;
+        if (plan) {
+            plan->row0[tid] = row0; plan->cnt[tid] = tot; plan->done[tid] = 0; plan->order[tid] = tid;
+            plan->base[0][tid] = ne * mt_gu; plan->base[1][tid] = ne * mt_dn;
+        }
+        if (tid == n_expert - 1) {
+            const int total = (excl + val) & 0xffff, ne_all = (excl + val) >> 16;
+            eoffs[n_expert] = total;
+            if (soffs) { soffs[0] = s0; soffs[1] = s1; }
+            if (plan) {
+                const bool extra = s1 > s0;
+                int G = n_expert;
+                int ta = ne_all * mt_gu, tb = ne_all * mt_dn;
+                if (extra) {   // the shared expert's rows are one more group: T <= 16 rows, one token tile
+                    plan->row0[G] = s0; plan->cnt[G] = s1 - s0; plan->done[G] = 0; plan->order[G] = G;
+                    plan->base[0][G] = ta; plan->base[1][G] = tb;
+                    ta += mt_gu; tb += mt_dn;
+                    G++;
+                }
+                plan->base[0][G] = ta; plan->base[1][G] = tb;
+                plan->n_tiles[0] = ta; plan->n_tiles[1] = tb; plan->n_groups = G; plan->gu_done = 0;
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < n) {
+        if (e >= 0) {
+            const int p = s_eoffs[e] + cnt[warp][e] + r_in_warp;
+            elist[p] = tid;
+            pos[tid] = p;
+        } else pos[tid] = -1;
+    }
+    cluster.sync();   // (release/acquire at cluster scope: pos[] is visible to the quantising CTAs)
+}
+
+// 0 when this front end applies, else the caller takes the general kernels
+int launch_front_decode(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int *idx, float *wt,
+                        int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
+                        int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0,
+                        cudaStream_t st) {
+    if (T > 16 || T * k > FD_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || n_expert > FD_THREADS || D % Q36_QK ||
+        T * (D / Q36_QK) > FD_QWARPS * FD_MAX_TASKS || s1 - s0 > 16)
+        return Q36_MOE_EINVAL;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(FD_CLUSTER);
+    cfg.blockDim = dim3(FD_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = FD_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, k_front_decode, logits, n_expert, k, scale, T, row_stride, idx, wt, ecount, eoffs, elist, pos,
+                       soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D, shared_row0);
     return check_launch();
 }
 

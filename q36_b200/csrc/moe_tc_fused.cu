@@ -27,7 +27,19 @@ namespace q36 {
 //    down tile (2 stages) is the sum of all four;
 //  * every role looks its tile up in a table built once per CTA (a binary search per tile per role cost ~900
 //    cycles, more than a down tile's share of the HBM stream);
-//  * the scale bytes have their own producer thread, so the two serial issue chains run side by side.
+//  * three producer threads, because every asynchronous copy costs its issuing thread ~140 cycles: weights
+//    (they depend on nothing, so this thread runs as far ahead as the ring allows), a tile's scale bytes (two
+//    tiles ahead), and the token rows of each stage;
+//  * gate/up tiles are dealt round-robin (tile b, b + grid, ...).  A gate/up tile is 2 D / FF (= 8) down tiles
+//    of work and 260 of them do not divide by 148, so the CTAs that got one gate/up tile fewer first take a
+//    few extra down tiles (the lowest ranks: their inputs are there first) -- only as many as they can finish
+//    before the others join, since a group's rows arrive ~7000 cycles after its last gate/up MMA (epilogue,
+//    release fence, the polls); the rest is dealt round-robin;
+//  * a watcher thread walks the CTA's tile list ahead of everybody and, for a down tile, waits until the
+//    gate/up tiles of its group -- possibly on other SMs -- have published Hq/Hs; the other roles poll a
+//    count in shared memory, so that the L2 round trips of the check sit on nobody's issue path;
+//  * publishing costs a device-scope release fence, measured at ~2500 cycles under the weight stream: a
+//    publisher thread pays it, not the epilogue warps (they only signal through shared memory).
 struct FusedCfg {
     static constexpr int STAGES = 4;
     static constexpr int KS = 2;                     // K steps per stage
@@ -37,7 +49,7 @@ struct FusedCfg {
     static constexpr int SF_BYTES = 512;
     static constexpr int OFF_B = KS * A_BYTES, OFF_SF = OFF_B + KS * B_BYTES;
     static constexpr int STAGE_BYTES = OFF_SF + KS * 2 * SF_BYTES;          // 38 KB, 1024-aligned
-    static constexpr int STAGE_TX = KS * (A_TX_BYTES + B_BYTES);
+    static constexpr int STAGE_TX_A = KS * A_TX_BYTES, STAGE_TX_B = KS * B_BYTES;
     // Scale bytes of a whole tile (all its K steps) are staged by bulk async copies, two tiles deep: the rows
     // of a tile are contiguous in the row-major scale planes (128 rows x K/32 bytes).  Loads issued by the
     // loader threads themselves were measured to expose a full HBM latency per 4 K steps (register prefetch
@@ -51,11 +63,13 @@ struct FusedCfg {
     static constexpr int ACC_STRIDE = 64;            // per accumulator set: issuer w at [16 w, 16 w + 16)
     static constexpr int SF_COL0 = 128;              // per issuer: A (4), B (4)
     static constexpr int TMEM_COLS = 256;
-    static constexpr int W_ISSUE0 = 2, W_EPI0 = W_ISSUE0 + ISSUERS, W_LOAD0 = W_EPI0 + 4;
-    static constexpr int THREADS = 32 * (W_LOAD0 + 4);   // weight producer, scale producer, issuers, epilogue, scale loaders
+    static constexpr int W_ISSUE0 = 3, W_EPI0 = W_ISSUE0 + ISSUERS, W_LOAD0 = W_EPI0 + 4, W_SCHED = W_LOAD0 + 4, W_PUB = W_SCHED + 1;
+    // warps: weight producer, scale producer, token-row producer, issuers, epilogue, scale loaders, watcher, publisher
+    static constexpr int THREADS = 32 * (W_PUB + 1);
     static constexpr int DONE_PER_GROUP_PER_MTILE = 4;   // epilogue warps
     static constexpr int MAX_GROUPS = DISPATCH_MAX_GROUPS + 1;   // the plan lists every group, empty ones included
-    static constexpr int MAX_TILES = 32;                 // per CTA
+    static constexpr int MAX_TILES = 40;                 // per CTA
+    static constexpr int EXTRA_DOWN = 3;                 // extra down tiles of a CTA that is one gate/up tile short
 };
 static_assert(FusedCfg::STAGE_BYTES % 1024 == 0, "stage alignment");
 
@@ -76,6 +90,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     uint64_t *bars = reinterpret_cast<uint64_t *>(sft + Cfg::SFT_SLOTS * Cfg::SFT_BYTES);
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_flag;
+    __shared__ int s_ready;                        // tile records [0, s_ready) are valid and their inputs are there
+    __shared__ int s_pub;                          // gate/up epilogue warps finished (all tiles of this CTA)
     __shared__ int s_row0[Cfg::MAX_GROUPS + 1], s_base0[Cfg::MAX_GROUPS + 2], s_base1[Cfg::MAX_GROUPS + 2];
     __shared__ unsigned short s_order[Cfg::MAX_GROUPS + 1], s_cnt[Cfg::MAX_GROUPS + 1];
     __shared__ int4 s_tiles[Cfg::MAX_TILES];       // x = group | kind << 16, y = row tile, z = first row, w = rows
@@ -88,8 +104,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     // ---- prologue that needs nothing from earlier kernels: runs while they drain
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        s_ready = 0;
+        s_pub = 0;
         for (int s = 0; s < Cfg::STAGES; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4);              // the producer's expect_tx arrive + one per scale warp
+            mbar_init(full0 + 8 * s, 2 + 4);              // the two producers' expect_tx arrives + one per scale warp
             mbar_init(empty0 + 8 * s, 2);                 // one tcgen05.commit per issuing warp of the stage
         }
         for (int b = 0; b < 2; b++) {
@@ -109,9 +127,20 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     const int G = plan->n_groups;
     const int n0 = plan->n_tiles[0], n_tiles = n0 + plan->n_tiles[1];
     const int mt_gu = FF / TC_M;
-    int my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int n1 = n_tiles - n0, grid = gridDim.x, b = blockIdx.x;
+    // this CTA's list: its gate/up tiles, its extra down tiles if it is one gate/up tile short, its share of the rest
+    const int n_long = n0 % grid;                              // CTAs [0, n_long) have one gate/up tile more
+    const int n_short = n_long ? grid - n_long : 0;
+    // (a CTA without any gate/up tile has nothing to read before the first round is published: no extras then)
+    const int extra_total = n0 >= grid ? min(n1, n_short * Cfg::EXTRA_DOWN) : 0;
+    const int my_gu = b < n0 ? (n0 - b + grid - 1) / grid : 0;
+    const int sb = b - n_long;                                 // index among the short CTAs
+    const int my_extra = (n_short && sb >= 0 && sb < extra_total) ? (extra_total - sb + n_short - 1) / n_short : 0;
+    const int n_rest = n1 - extra_total;
+    const int my_rest = b < n_rest ? (n_rest - b + grid - 1) / grid : 0;
+    int my_tiles = my_gu + my_extra + my_rest;
     const bool fits = G <= Cfg::MAX_GROUPS && my_tiles <= Cfg::MAX_TILES;
-    if (!fits) {                                   // (uniform over the CTA) nothing is computed, the status says so
+    if (!fits) {                                               // (uniform over the CTA) nothing is computed, the status says so
         my_tiles = 0;
         if (threadIdx.x == 0) atomicCAS(status, 0, 0x900);
     }
@@ -124,23 +153,38 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
-    if ((int)threadIdx.x < my_tiles) {             // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
-        const int ti = blockIdx.x + threadIdx.x * gridDim.x;
-        const int kind = ti >= n0;
+    if ((int)threadIdx.x < my_tiles) {
+        const int i = threadIdx.x;
+        const int kind = i >= my_gu;
+        const int t = !kind ? b + i * grid
+                            : (i < my_gu + my_extra ? sb + (i - my_gu) * n_short : extra_total + b + (i - my_gu - my_extra) * grid);
         const int *base = kind ? s_base1 : s_base0;
-        const int t = kind ? ti - n0 : ti;
         int lo = 0, hi = G - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
             if (base[mid] <= t) lo = mid; else hi = mid - 1;
         }
         const int g = s_order[lo];
-        s_tiles[threadIdx.x] = make_int4(g | (kind << 16), t - base[lo], s_row0[g], s_cnt[g]);   // one token tile per group
+        s_tiles[i] = make_int4(g | (kind << 16), t - base[lo], s_row0[g], s_cnt[g]);   // one token tile per group
     }
     __syncthreads();
     auto get_tile = [&](int j) {
         const int4 v = s_tiles[j];
         return FTile{v.x >> 16, v.x & 0xffff, v.y, v.z, v.w};
+    };
+    // Every role walks j = 0, 1, ...: true once the watcher has seen tile j's inputs, false when the CTA has no
+    // tile j.  Only the roles that READ a down tile's token rows have to wait; the others just walk the list.
+    auto tile_wait = [&](int j, int where) -> bool {
+        if (j >= my_tiles) return false;
+        for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+            int v;
+            asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(&s_ready)) : "memory");
+            if (v > j) return true;
+            if ((i & 255u) == 255u && abort_flag) return false;
+        }
+        abort_flag = 1;
+        atomicCAS(status, 0, where);
+        return false;
     };
     // gate/up of group g is complete when every epilogue warp of each of its row tiles has published
     const int done_target = mt_gu * Cfg::DONE_PER_GROUP_PER_MTILE;
@@ -157,31 +201,17 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         atomicCAS(status, 0, where);
         return false;
     };
-    // A down tile reads Hq/Hs written through the generic proxy, possibly by other SMs: wait for the group's
-    // count, then order those writes before this thread's asynchronous reads.
-    auto wait_inputs = [&](const FTile &t, bool &all_gu_done, int where) -> bool {
-        if (!t.kind || all_gu_done) return true;
-        if (!wait_group(t.g, where)) return false;
-        int v;   // after the wait (acquire): if the whole gate/up phase is over, later tiles need no poll
-        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(&plan->gu_done) : "memory");
-        all_gu_done = v >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;
-        asm volatile("fence.proxy.async.global;" ::: "memory");   // (the all-spaces form costs ~1000 cycles here, this one ~20)
-        return true;
-    };
-
     if (warp == 0) {
-        // ------------------------------------------- TMA producer: weights and token rows
+        // ------------------------------------------- TMA producer: weights (they depend on nothing)
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true, all_gu_done = false;
+            bool ok = true;
             for (int j = 0; j < my_tiles && ok; j++) {
                 const FTile t = get_tile(j);
                 const bool sh = t.g >= n_routed;
                 const int ge = sh ? 0 : t.g;
                 const CUtensorMap *ma0 = t.kind ? (sh ? &maps.sd : &maps.d) : (sh ? &maps.sg : &maps.g);
                 const CUtensorMap *ma1 = sh ? &maps.su : &maps.u;
-                const CUtensorMap *mb = t.kind ? &maps.h : &maps.x;
-                if (!(ok = wait_inputs(t, all_gu_done, 0x600))) break;
                 const int nst = t.kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));   // gate, up, gate, ...
                 for (int q = 0; q < nst; q++, it++) {
                     const int kpair = t.kind ? q : (q >> 1);
@@ -189,22 +219,23 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    mbar_expect_tx(full0 + 8 * s, Cfg::STAGE_TX);
+                    mbar_expect_tx(full0 + 8 * s, Cfg::STAGE_TX_A);
                     tma_load_4d(sb, (!t.kind && (q & 1)) ? ma1 : ma0, 0, t.mt * TC_M, kpair * Cfg::KS, ge, full0 + 8 * s);
-                    tma_load_3d(sb + Cfg::OFF_B, mb, 0, t.row0, kpair * Cfg::KS, full0 + 8 * s);
                 }
             }
         }
     } else if (warp == 1) {
-        // --------------------------- scale producer: a tile's scale bytes, contiguous runs of the row-major planes
+        // ----- scale producer: a tile's scale bytes, contiguous runs of the row-major planes, two tiles deep
         if (lane == 0) {
-            bool ok = true, all_gu_done = false;
-            for (int j = 0; j < my_tiles && ok; j++) {
+            bool ok = true;
+            for (int j = 0; ok && tile_wait(j, 0x680); j++) {
                 const FTile t = get_tile(j);
+                // (the watcher's acquire ordered the other CTAs' generic-proxy stores of Hq/Hs; this orders them
+                // before this thread's asynchronous reads.  The all-spaces form of the fence costs ~1000 cycles.)
+                if (t.kind) asm volatile("fence.proxy.async.global;" ::: "memory");
                 const bool sh = t.g >= n_routed;
                 const int ge = sh ? 0 : t.g;
                 const uint32_t slot = j & 1;
-                if (!(ok = wait_inputs(t, all_gu_done, 0x680))) break;
                 if (!(ok = mbar_wait(sft_empty0 + 8 * slot, ((j >> 1) & 1) ^ 1, &abort_flag, status, 0x800 + slot))) break;
                 const int nbk = (t.kind ? FF : D) / Q36_QK;
                 const uint32_t a_bytes = TC_M * nbk, b_bytes = t.nrows * nbk;
@@ -215,6 +246,26 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
                 if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
                 bulk_load(dst + 2 * Cfg::SFT_A, (t.kind ? Hs : Xs) + (size_t)t.row0 * nbk, b_bytes, sft_full0 + 8 * slot);
+            }
+        }
+    } else if (warp == 2) {
+        // ----- token-row producer: per stage the 16 token rows of its two K steps
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int j = 0; ok && tile_wait(j, 0x690); j++) {
+                const FTile t = get_tile(j);
+                if (t.kind) asm volatile("fence.proxy.async.global;" ::: "memory");   // as in the scale producer
+                const CUtensorMap *mb = t.kind ? &maps.h : &maps.x;
+                const int nst = t.kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));
+                for (int q = 0; q < nst; q++, it++) {
+                    const int kpair = t.kind ? q : (q >> 1);
+                    const int s = it % Cfg::STAGES;
+                    const uint32_t ph = (it / Cfg::STAGES) & 1;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x180 + s))) break;
+                    mbar_expect_tx(full0 + 8 * s, Cfg::STAGE_TX_B);
+                    tma_load_3d(smem_u32(smem + s * Cfg::STAGE_BYTES) + Cfg::OFF_B, mb, 0, t.row0, kpair * Cfg::KS, full0 + 8 * s);
+                }
             }
         }
     } else if (warp < Cfg::W_EPI0) {
@@ -294,16 +345,56 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                     swiglu_quant_store<8>(g0, u0, t.nrows, (size_t)t.row0, Hq, Hs, FF, blk, lane);
                     if (t.nrows > 8) swiglu_quant_store<8>(g1, u1, t.nrows - 8, (size_t)t.row0 + 8, Hq, Hs, FF, blk, lane);
                 }
-                __threadfence();         // each lane's stores are visible device-wide before the count moves
+                // hand the tile to the publisher: the lanes' stores are ordered before lane 0 by the warp barrier,
+                // lane 0's CTA-scope release orders them before the publisher's device-scope one
                 __syncwarp();
-                if (lane == 0) {
-                    atomicAdd(plan->done + t.g, 1);
-                    atomicAdd(&plan->gu_done, 1);      // once every gate/up tile is in, consumers stop polling per group
-                }
+                if (lane == 0) asm volatile("red.release.cta.shared.add.s32 [%0], 1;" ::"r"(smem_u32(&s_pub)) : "memory");
             } else {
 #pragma unroll
                 for (int c = 0; c < 16; c++)
                     if (c < t.nrows) Y[(size_t)(t.row0 + c) * D + mrow] = g[c];
+            }
+        }
+    } else if (warp == Cfg::W_SCHED) {
+        // --------------------------------------------------------- watcher
+        if (lane == 0) {
+            bool all_gu_done = false;
+            for (int j = 0; j < my_tiles; j++) {
+                const int4 v = s_tiles[j];
+                if ((v.x >> 16) && !all_gu_done) {
+                    // the group's own count first (one L2 round trip when it is there, as it mostly is); the
+                    // global count only when a wait was needed, to stop polling once the whole phase is over
+                    int a;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(a) : "l"(plan->done + (v.x & 0xffff)) : "memory");
+                    if (a < done_target) {
+                        if (!wait_group(v.x & 0xffff, 0x600)) break;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(a) : "l"(&plan->gu_done) : "memory");
+                        all_gu_done = a >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;
+                    }
+                }
+                asm volatile("st.release.cta.shared.s32 [%0], %1;" ::"r"(smem_u32(&s_ready)), "r"(all_gu_done ? my_tiles : j + 1) : "memory");
+                if (all_gu_done) break;
+            }
+        }
+    } else if (warp == Cfg::W_PUB) {
+        // ------------------------------------------------------- publisher
+        // gate/up tiles come first in the CTA's list, in order: tile i is done when the four epilogue warps have
+        // signalled 4 (i + 1) times in all
+        if (lane == 0) {
+            for (int gi = 0; gi < my_gu && gi < my_tiles; gi++) {
+                bool ok = false;
+                for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+                    int v;
+                    asm volatile("ld.acquire.cta.shared.s32 %0, [%1];" : "=r"(v) : "r"(smem_u32(&s_pub)) : "memory");
+                    if (v >= 4 * (gi + 1)) { ok = true; break; }
+                    if ((i & 255u) == 255u && abort_flag) break;
+                    __nanosleep(32);
+                }
+                if (!ok) { if (!abort_flag) { abort_flag = 1; atomicCAS(status, 0, 0x6a0); } break; }
+                const int g = s_tiles[gi].x & 0xffff;
+                asm volatile("fence.acq_rel.gpu;" ::: "memory");
+                atomicAdd(plan->done + g, Cfg::DONE_PER_GROUP_PER_MTILE);
+                atomicAdd(&plan->gu_done, Cfg::DONE_PER_GROUP_PER_MTILE);   // once every gate/up tile is in, nobody polls per group
             }
         }
     } else {
@@ -368,7 +459,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
 }
 
 // every non-empty group has at least one row and one token tile, so the row count bounds the tiles of a CTA
-int ffn_fused_small_max_rows(int D, int FF) { return FusedCfg::MAX_TILES * sm_count() / (FF / TC_M + D / TC_M); }
+int ffn_fused_small_max_rows(int D, int FF) {
+    // per CTA: its round-robin shares of both tile kinds (rounded up) plus the extra down tiles of a short CTA
+    return (FusedCfg::MAX_TILES - 2 - (2 * D) / FF) * sm_count() / (FF / TC_M + D / TC_M);
+}
 
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,

@@ -146,7 +146,9 @@ uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
 /* Sg/Su/Sd (or NULL): one extra group, the shared expert, with its own planes
  * and the row range [soffs[0], soffs[1]) (device ints).  stages: bit 0 runs
  * gate/up + SwiGLU, bit 1 runs down; 3 = both (the intermediate Hq/Hs is the
- * hand-over, so the halves can be launched and timed separately).
+ * hand-over, so the halves can be launched and timed separately); 4 alone
+ * does only the set-up both halves share on the tensor-core path (status
+ * words, work plan), so that a benchmark can take it out of a timing.
  * max_group_rows: an upper bound on the rows of any single group when the
  * caller knows one (decode: the number of tokens), else 0.  With the
  * tensor-core path, stages == 3 and a bound <= 16, gate/up and down run as

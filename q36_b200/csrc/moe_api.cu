@@ -242,7 +242,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
                               uint64_t ws_bytes, void *stream) {
     if (!Wg || !Wu || !Wd || !goffs || !Xq_rows || !Xs_rows || !Hq_rows || !Hs_rows || !Y_rows) return Q36_MOE_EINVAL;
     if (n_group <= 0 || n_group > DISPATCH_MAX_GROUPS || D % 128 || FF % 128 || R_max <= 0) return Q36_MOE_EINVAL;
-    if (!(stages & 3) || (path != Q36_MOE_PATH_GEMV && path != Q36_MOE_PATH_TC)) return Q36_MOE_EINVAL;
+    if (!(stages & 7) || (path != Q36_MOE_PATH_GEMV && path != Q36_MOE_PATH_TC)) return Q36_MOE_EINVAL;
     const bool shared = Sg && Su && Sd && soffs;
     cudaStream_t st = (cudaStream_t)stream;
     int rc;

@@ -118,6 +118,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x >= 32 && threadIdx.x < 40)     // the eight descriptors, fetched while the previous kernel drains
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.g + (threadIdx.x - 32)) : "memory");
     if (warp == Cfg::W_ISSUE0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");

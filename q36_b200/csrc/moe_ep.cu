@@ -252,10 +252,19 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     // 5. grouped expert FFN on the local shard (+ shared expert on the own tokens)
     const int *goffs = w.loffs + se0;
     if ((rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
-    if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s, w.Hq,
-                               w.Hs, D, FF, w.plan, w.status, st)))
-        return rc;
-    if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st))) return rc;
+    // an expert receives at most one row per token of every rank: with at most 16 of them the decode kernel
+    // (gate/up and down in one persistent launch) applies
+    if (world * T <= 16 && R + T <= ffn_fused_small_max_rows(D, FF)) {
+        if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, per,
+                                         R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, st)))
+            return rc;
+    } else {
+        if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
+                                   w.Hq, w.Hs, D, FF, w.plan, w.status, st)))
+            return rc;
+        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+            return rc;
+    }
     // 6. result rows back to their home ranks, then the weighted combine
     if ((rc = launch_gather_rows(w.Y, w.lpos, w.back, S, D * 4, st))) return rc;
     if ((rc = all_to_all(api, c, w.back, w.recv_y, (size_t)C * D * 4, st))) return rc;

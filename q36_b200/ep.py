@@ -138,12 +138,15 @@ def _pad_index(llist: torch.Tensor, R: int) -> torch.Tensor:
 class NativeEP:
     """The C entry point q36_moe_ep_layer: the whole step (kernels and NCCL send/recv) is issued from native
     code on the current stream; torch.distributed only carries the 128-byte NCCL id at set-up."""
-    launches_per_layer = 14     # front, quantise, pack, eids, dispatch x3, unpack, plan, gate/up, down, gather, combine (+2 exchanges)
+    # front, quantise, pack, eids, dispatch x3, unpack, plan, gate/up, down, gather, combine (+2 exchanges);
+    # gate/up and down are one launch when no expert can receive more than 16 rows (world * T <= 16)
+    launches_per_layer = 14
 
     def __init__(self, layers, world: int, rank: int, T: int):
         import ctypes as C
         from . import moe
         self.moe, self.layers, self.world, self.rank, self.T = moe, layers, world, rank, T
+        self.launches_per_layer = 13 if world * T <= 16 else 14
         dev = layers[0].device
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:

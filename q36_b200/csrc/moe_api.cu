@@ -94,7 +94,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     const bool fused_front = n <= 1024;
     static const bool no_cluster = getenv("Q36_NOCLUSTER") != nullptr;
     // decode on the tensor-core path with every expert resident: one cluster launch does all of the front end
-    const bool cluster_front = use_tc && T <= 16 && n <= 128 && se0 == 0 && se1 == E && D * T <= 16 * 2048 && !no_cluster;
+    const bool cluster_front = use_tc && T <= 16 && n <= 128 && se0 == 0 && se1 == E && D % 1024 == 0 && D * T <= 32 * 1024 && !no_cluster;
     const bool fused_quant = cluster_front || (fused_front && T <= 2);     // beyond a couple of rows the scatter serialises inside one block: measured slower than a launch
     if (cluster_front) {
         if ((rc = launch_front_decode(logits, E, k, route_scale, T, logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist,

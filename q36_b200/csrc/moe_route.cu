@@ -33,14 +33,14 @@ __device__ __forceinline__ void route_row(const float *__restrict__ l, int k, in
 #pragma unroll
         for (int j = 0; j < PER_LANE; j++)
             if (v[j] > bm) { bm = v[j]; bj = j; }
-        float wv = bm;
-        int wi = lane + bj * 32;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
-            if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
-        }
+        // warp arg-max in two reductions: the largest value as an order-preserving integer key, then the lowest
+        // expert id among the lanes that hold it (the shuffle tree this replaces was 10 dependent shuffles)
+        const uint32_t bits = __float_as_uint(bm + 0.f);                         // (-0 -> +0: equal floats, equal keys)
+        const uint32_t key = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+        const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
+        const int wi = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (uint32_t)(lane + bj * 32) : 0xffffffffu);
+        const uint32_t vb = (kmax & 0x80000000u) ? (kmax & 0x7fffffffu) : ~kmax;
+        const float wv = __uint_as_float(vb);
         const float w = expf(wv - m) / s;
         if (lane == r) { w_keep = w; idx[r] = wi; }
         wsum += w;
@@ -195,35 +195,80 @@ __device__ __forceinline__ void quant_task(float v, uint8_t *__restrict__ Xq, ui
 }
 
 
-// The two halves of quant_task<true>, for a kernel that quantises before it knows where the rows go.
-// quant_pack: lane l ends up with word (l & 7) of the block's 32 codes in hw order, and the block exponent.
-__device__ __forceinline__ void quant_pack(float v, int lane, uint32_t &word, int &e2) {
-    const float a = warp_max(fabsf(v));
-    e2 = e2_of_amax(a);
-    const uint8_t q = f32_to_e4m3(v * inv_scale_of_e2(e2));
-    const int src = (lane & 1) ? (16 + (lane >> 1)) : (lane >> 1);
-    const uint32_t qp = __shfl_sync(0xffffffffu, (uint32_t)q, src);
-    uint32_t w = qp;
-    w |= __shfl_down_sync(0xffffffffu, qp, 1) << 8;
-    w |= __shfl_down_sync(0xffffffffu, qp, 2) << 16;
-    w |= __shfl_down_sync(0xffffffffu, qp, 3) << 24;
-    word = __shfl_sync(0xffffffffu, w, (lane & 7) * 4);
-}
-// quant_put: the block goes to every row of the sorted space token t feeds (its k slots, then its shared row)
-__device__ __forceinline__ void quant_put(uint32_t word, int e2, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int t,
-                                          int b, int K, const int *pos, int k, int shared_row0, int lane) {
-    const int nb = K / Q36_QK;
-    const int n_dst = k + (shared_row0 >= 0 ? 1 : 0);
-    for (int d0 = 0; d0 < n_dst; d0 += 4) {
-        const int d = d0 + (lane >> 3);
-        if (d < n_dst) {
-            const int row = (d < k) ? __ldcg(pos + (size_t)t * k + d) : (shared_row0 + t);
-            if (row >= 0) {
-                ((uint32_t *)(Xq + (size_t)row * K + (size_t)b * Q36_QK))[lane & 7] = word;
-                if ((lane & 7) == 0) Xs[(size_t)row * nb + b] = (uint8_t)(127 + e2);
+// ------------------------------------------- quantiser, one lane per 32-block
+// The same arithmetic as quant_task, laid out for rows that are scattered to several destinations: a lane
+// owns a whole 32-block (64 B of bf16 or 128 B of f32 in, its amax needs no shuffle), a warp 32 consecutive
+// blocks of one token row, so every destination row receives 1 KB of codes and 32 scale bytes per warp in
+// full sectors.  (One warp per block writes 32 B and one scale byte per destination: at 4096 tokens the
+// single-byte stores alone are 2.4 M partial-sector writes.)
+struct QBlock { uint4 lo, hi; int e2; };   // the block's 32 codes in hw order (element j at 2j, j+16 at 2j+1)
+
+template <bool BF16>
+__device__ __forceinline__ QBlock quant_block_lane(const void *__restrict__ X, size_t off) {
+    float v[32];
+    if (BF16) {
+        const uint4 *p = reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)X + off);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint4 u = p[i];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+                v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
             }
         }
+    } else {
+        const float4 *p = reinterpret_cast<const float4 *>((const float *)X + off);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float4 u = p[i];
+            v[4 * i] = u.x; v[4 * i + 1] = u.y; v[4 * i + 2] = u.z; v[4 * i + 3] = u.w;
+        }
     }
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i++) a = fmaxf(a, fabsf(v[i]));
+    QBlock r;
+    r.e2 = e2_of_amax(a);
+    const float inv = inv_scale_of_e2(r.e2);
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {   // bytes 4i..4i+3 = elements 2i, 2i+16, 2i+1, 2i+17
+        w[i] = (uint32_t)f32_to_e4m3(v[2 * i] * inv) | ((uint32_t)f32_to_e4m3(v[2 * i + 16] * inv) << 8) |
+               ((uint32_t)f32_to_e4m3(v[2 * i + 1] * inv) << 16) | ((uint32_t)f32_to_e4m3(v[2 * i + 17] * inv) << 24);
+    }
+    r.lo = make_uint4(w[0], w[1], w[2], w[3]);
+    r.hi = make_uint4(w[4], w[5], w[6], w[7]);
+    return r;
+}
+__device__ __forceinline__ void quant_block_put(const QBlock &q, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int row,
+                                                int blk, int K) {
+    uint4 *d = reinterpret_cast<uint4 *>(Xq + (size_t)row * K + (size_t)blk * Q36_QK);
+    d[0] = q.lo;
+    d[1] = q.hi;
+    Xs[(size_t)row * (K / Q36_QK) + blk] = (uint8_t)(127 + q.e2);
+}
+
+// warp = (token, run of 32 blocks); K must be a multiple of 1024
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+k_quant_rows(const void *__restrict__ X, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int T, int K,
+             const int *__restrict__ pos, int k, int shared_row0) {
+    Q36_GDS();
+    const int runs = K / (32 * Q36_QK);
+    const long gwarp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gwarp >= (long)T * runs) return;
+    const int t = (int)(gwarp / runs), blk = (int)(gwarp % runs) * 32 + lane;
+    int rows[9];
+#pragma unroll
+    for (int d = 0; d < 8; d++) rows[d] = (d < k) ? pos[(size_t)t * k + d] : -1;   // (issued before the row is read)
+    rows[8] = shared_row0 >= 0 ? shared_row0 + t : -1;
+    const QBlock q = quant_block_lane<BF16>(X, (size_t)t * K + (size_t)blk * Q36_QK);
+#pragma unroll
+    for (int d = 0; d < 9; d++)
+        if (rows[d] >= 0) quant_block_put(q, Xq, Xs, rows[d], blk, K);
 }
 
 template <bool BF16, bool SCATTER>
@@ -350,15 +395,14 @@ int launch_front_small(const float *logits, int n_expert, int k, float scale, in
 // ----------------------------------------------- decode front end: one cluster
 // At most 16 tokens (T * k <= 128 entries), all experts resident.  One thread-block cluster, one launch:
 //   CTA 0        router -> stable dispatch -> work plan of the fused tensor-core kernel
-//   CTAs 1..7    quantise the token rows (needs no routing result), wait at the cluster barrier for CTA 0's
-//                row positions, then write every block to the k + 1 rows it feeds.
+//   CTA 1        quantises the token rows (needs no routing result), waits at the cluster barrier for CTA 0's
+//                row positions, then writes every block to the k + 1 rows it feeds.
 // Same results as k_front_small + k_quant_e4m3<., true>: the same route_row, the same ascending-entry order
 // inside an expert's bucket, the same quantiser.
-constexpr int FD_CLUSTER = 8;
+constexpr int FD_CLUSTER = 2;
 constexpr int FD_THREADS = 1024;
 constexpr int FD_MAX_ENTRIES = 128;
-constexpr int FD_MAX_TASKS = 8;                                   // (row, block) tasks per quantising warp
-constexpr int FD_QWARPS = (FD_CLUSTER - 1) * (FD_THREADS / 32);
+constexpr int FD_QWARPS = FD_THREADS / 32;                        // one (token, run of 32 blocks) per warp of CTA 1
 
 __global__ void __launch_bounds__(FD_THREADS)
 k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scale, int T, int row_stride,
@@ -371,25 +415,22 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n = T * k;
+    __shared__ int s_pos[FD_MAX_ENTRIES];          // row of every entry; CTA 0 writes it into every CTA of the cluster
     if (cluster.block_rank() != 0) {
-        // ---- quantise now, place after the barrier
-        const int nbk = D / Q36_QK, ntask = T * nbk;
-        const int qw = ((int)cluster.block_rank() - 1) * (FD_THREADS / 32) + warp;
-        uint32_t word[FD_MAX_TASKS];
-        int e2[FD_MAX_TASKS];
-        float v[FD_MAX_TASKS];
-#pragma unroll
-        for (int j = 0; j < FD_MAX_TASKS; j++) {
-            const int task = qw + j * FD_QWARPS;
-            v[j] = (task < ntask) ? quant_load(X, x_is_bf16 != 0, task / nbk, task % nbk, D, lane) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < FD_MAX_TASKS; j++) quant_pack(v[j], lane, word[j], e2[j]);
+        // ---- quantise now (warp = token x run of 32 blocks, lane = block), place after the barrier
+        const int runs = D / (32 * Q36_QK);
+        const int t = warp / runs, blk = (warp % runs) * 32 + lane;
+        const bool mine = warp < T * runs;
+        QBlock q;
+        if (mine) q = x_is_bf16 ? quant_block_lane<true>(X, (size_t)t * D + (size_t)blk * Q36_QK)
+                                : quant_block_lane<false>(X, (size_t)t * D + (size_t)blk * Q36_QK);
         cluster.sync();
-#pragma unroll
-        for (int j = 0; j < FD_MAX_TASKS; j++) {
-            const int task = qw + j * FD_QWARPS;
-            if (task < ntask) quant_put(word[j], e2[j], Xq, Xs, task / nbk, task % nbk, D, pos, k, shared_row0, lane);
+        if (mine) {
+            for (int d = 0; d < k; d++) {
+                const int row = s_pos[t * k + d];
+                if (row >= 0) quant_block_put(q, Xq, Xs, row, blk, D);
+            }
+            if (shared_row0 >= 0) quant_block_put(q, Xq, Xs, shared_row0 + t, blk, D);
         }
         return;
     }
@@ -473,13 +514,15 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
     }
     __syncthreads();
     if (tid < n) {
+        int p = -1;
         if (e >= 0) {
-            const int p = s_eoffs[e] + cnt[warp][e] + r_in_warp;
+            p = s_eoffs[e] + cnt[warp][e] + r_in_warp;
             elist[p] = tid;
-            pos[tid] = p;
-        } else pos[tid] = -1;
+        }
+        pos[tid] = p;
+        for (int r = 1; r < FD_CLUSTER; r++) *cluster.map_shared_rank(&s_pos[tid], r) = p;   // no L2 round trip for the scatter
     }
-    cluster.sync();   // (release/acquire at cluster scope: pos[] is visible to the quantising CTAs)
+    cluster.sync();   // (release/acquire at cluster scope: the remote stores above are visible to their CTAs)
 }
 
 // 0 when this front end applies, else the caller takes the general kernels
@@ -487,8 +530,8 @@ int launch_front_decode(const float *logits, int n_expert, int k, float scale, i
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
                         int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0,
                         cudaStream_t st) {
-    if (T > 16 || T * k > FD_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || n_expert > FD_THREADS || D % Q36_QK ||
-        T * (D / Q36_QK) > FD_QWARPS * FD_MAX_TASKS || s1 - s0 > 16)
+    if (T > 16 || T * k > FD_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || n_expert > FD_THREADS || D % (32 * Q36_QK) ||
+        T * (D / (32 * Q36_QK)) > FD_QWARPS || s1 - s0 > 16)
         return Q36_MOE_EINVAL;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(FD_CLUSTER);
@@ -537,7 +580,12 @@ int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K
     if (T <= 0) return Q36_MOE_OK;
     const long warps = (long)T * (K / Q36_QK);
     const unsigned grid = (unsigned)((warps + 7) / 8);
-    if (scatter) {
+    if (scatter && K % (32 * Q36_QK) == 0 && k <= 8) {
+        const long w2 = (long)T * (K / (32 * Q36_QK));
+        const unsigned g2 = (unsigned)((w2 + 7) / 8);
+        if (bf16) launch_k(k_quant_rows<true>, dim3(g2), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
+        else launch_k(k_quant_rows<false>, dim3(g2), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
+    } else if (scatter) {
         if (bf16) launch_k(k_quant_e4m3<true, true>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
         else launch_k(k_quant_e4m3<false, true>, dim3(grid), dim3(256), 0, st, X, Xq, Xs, T, K, pos, k, shared_row0);
     } else {

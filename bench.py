@@ -388,7 +388,7 @@ def roofline_decode(moe, layers, dX, dL, T, path, hbm_peak, peak_kind, dev):
         ach = nbytes / (a_ms * 1e-3) / 1e9
         # dram__bytes_read + dram__bytes_write of one launch of this kernel on this layer shape at T = 8, from the
         # ncu capture summarised in profiles/k_ffn_fused_small_decode_T8.md (scaled by the rows when T differs)
-        traffic = 104.6e6 * (nbytes / 98.46e6)
+        traffic = 103.4e6 * (nbytes / 98.46e6)
         extra["setup_us_per_launch"] = t_setup * 1e3
         roof = {"bound": "hbm", "kernel": "k_ffn_fused_small (gate/up + SwiGLU + down in one launch)",
                 "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": traffic,

@@ -24,8 +24,11 @@ int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K
 // returns EINVAL without launching when the sizes are outside what it holds
 int launch_front_decode(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int *idx, float *wt,
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                        int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0,
+                        int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0, int put_k,
                         cudaStream_t st);
+int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
+                               int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
+                               int *status, cudaStream_t st);
 int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
                        int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,

@@ -99,7 +99,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     if (cluster_front) {
         if ((rc = launch_front_decode(logits, E, k, route_scale, T, logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
                                       w.pos, w.soffs, n, shared ? n + T : n, w.plan, D, FF, w.status, X, x_is_bf16, w.Xq,
-                                      w.Xs, shared ? n : -1, st)))
+                                      w.Xs, shared ? n : -1, k, st)))
             return rc;
     } else if (fused_front) {
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, se0, se1, w.idx, w.wt, w.ecount, w.eoffs,

@@ -226,8 +226,14 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     const int nbs = D / Q36_QK, rowb = D + nbs + EP_PAD;
     const bool shared = Sg && Su && Sd;
     int rc;
-    // 1. route + dispatch over ALL experts (their order is the destination-rank order)
-    if (n <= 1024) {
+    // 1. route + dispatch over ALL experts (their order is the destination-rank order), and
+    // 2. quantise the rank's tokens once, in token order (hw order inside the blocks): one cluster launch at decode sizes
+    const bool cluster_front = T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
+    if (cluster_front) {
+        if ((rc = launch_front_decode(logits, E, k, route_scale, T, logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist, w.pos,
+                                      nullptr, 0, 0, nullptr, D, FF, w.status, X, x_is_bf16, w.Xq, w.Xs, 0, 0, st)))
+            return rc;
+    } else if (n <= 1024) {
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, 0, E, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
                                      w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, nullptr, 0, nullptr, nullptr, -1, st)))
             return rc;
@@ -235,23 +241,29 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
         if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
         if ((rc = launch_dispatch(w.idx, n, E, 0, E, w.ecount, w.eoffs, w.elist, w.pos, w.disp, nullptr, 0, 0, st))) return rc;
     }
-    // 2. quantise the rank's tokens once, in token order (hw order inside the blocks)
-    if ((rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, nullptr, 0, 0, true, st))) return rc;
+    if (!cluster_front && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, nullptr, 0, 0, true, st))) return rc;
     // 3. pack per destination rank and exchange
     launch_k(k_ep_pack, dim3(S), dim3(128), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
              (const int *)w.eoffs, (const int *)w.elist, (const int *)w.pos, world, E, k, T, C, D, w.send, w.ypos);
     if ((rc = check_launch())) return rc;
     if ((rc = all_to_all(api, c, w.send, w.recv, (size_t)C * rowb, st))) return rc;
     // 4. local plan over the received slots; empty slots (-1) and nothing else drop out
-    launch_k(k_ep_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)w.recv, S, rowb, D + nbs, w.reid);
-    if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st)))
-        return rc;
+    const bool small_plan = S <= 1024;   // one block sorts the slots and writes the work plan
+    if (small_plan) {
+        if ((rc = launch_dispatch_plan_small(w.recv + (D + nbs), rowb, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs,
+                                             R, shared ? R + T : R, w.plan, D, FF, w.status, st)))
+            return rc;
+    } else {
+        launch_k(k_ep_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)w.recv, S, rowb, D + nbs, w.reid);
+        if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st)))
+            return rc;
+    }
     launch_k(k_ep_unpack, dim3(R + T), dim3(128), 0, st, (const uint8_t *)w.recv, (const int *)w.llist,
              (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s);
     if ((rc = check_launch())) return rc;
     // 5. grouped expert FFN on the local shard (+ shared expert on the own tokens)
     const int *goffs = w.loffs + se0;
-    if ((rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
+    if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
     // an expert receives at most one row per token of every rank: with at most 16 of them the decode kernel
     // (gate/up and down in one persistent launch) applies
     if (world * T <= 16 && R + T <= ffn_fused_small_max_rows(D, FF)) {

@@ -295,17 +295,19 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
               int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
               int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1,
               TcPlan *plan, int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16,
-              uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0) {
+              uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0,
+              const uint8_t *__restrict__ ent, int ent_stride, int n_ent) {
+    // ent != nullptr: no routing, the n_ent entries' expert ids are the ints at ent + i * ent_stride (T, k unused)
     Q36_GDS();
     __shared__ unsigned short cnt[FRONT_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // 32 KB
     __shared__ int s_eoffs[DISPATCH_MAX_E + 1];
     __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
-    const int n = T * k;
+    const int n = ent ? n_ent : T * k;
     const int used_warps = (n + 31) / 32;          // only the warps that own entries contribute counts
     for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
     if (status && tid < 4) status[tid] = 0;
-    for (int t = warp; t < T; t += nwarp) {
+    for (int t = warp; t < T && !ent; t += nwarp) {
         const float *l = logits + (size_t)t * row_stride;
         int *ix = idx + (size_t)t * k;
         float *w = wt + (size_t)t * k;
@@ -317,7 +319,7 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
     __syncthreads();   // idx written by this block is visible to it after the barrier
     int e = -1;
     if (tid < n) {
-        e = idx[tid];
+        e = ent ? *reinterpret_cast<const int *>(ent + (size_t)tid * ent_stride) : idx[tid];
         if (e < se0 || e >= se1 || e >= n_expert) e = -1;
     }
     const unsigned peers = __match_any_sync(0xffffffffu, e);
@@ -380,6 +382,17 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
     }
 }
 
+// dispatch (+ work plan) of entries whose expert ids sit in a strided buffer: k_front_small without the router
+int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
+                               int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
+                               int *status, cudaStream_t st) {
+    if (n_ent > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || !ent) return Q36_MOE_EINVAL;
+    launch_k(k_front_small, dim3(1), dim3(1024), 0, st, (const float *)nullptr, n_expert, 1, 1.f, 0, 0, se0, se1, (int *)nullptr,
+             (float *)nullptr, ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status,
+             (const void *)nullptr, 0, (uint8_t *)nullptr, (uint8_t *)nullptr, D, -1, (const uint8_t *)ent, ent_stride, n_ent);
+    return check_launch();
+}
+
 int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
                        int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
@@ -387,7 +400,7 @@ int launch_front_small(const float *logits, int n_expert, int k, float scale, in
     if (T * k > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E) return Q36_MOE_EINVAL;
     launch_k(k_front_small, dim3(1), dim3(1024), 0, st, logits, n_expert, k, scale, T, row_stride, se0, se1, idx, wt,
              ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D,
-             shared_row0);
+             shared_row0, (const uint8_t *)nullptr, 0, 0);
     return check_launch();
 }
 
@@ -409,7 +422,9 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
                int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
                int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan,
                int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16, uint8_t *__restrict__ Xq,
-               uint8_t *__restrict__ Xs, int D, int shared_row0) {
+               uint8_t *__restrict__ Xs, int D, int shared_row0, int put_k) {
+    // put_k: k for the sorted row space of a single-GPU layer; 0 when only the token-order rows (shared_row0 + t)
+    // are wanted, as in the expert-parallel step
     Q36_GDS();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -426,7 +441,7 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
                                 : quant_block_lane<false>(X, (size_t)t * D + (size_t)blk * Q36_QK);
         cluster.sync();
         if (mine) {
-            for (int d = 0; d < k; d++) {
+            for (int d = 0; d < put_k; d++) {
                 const int row = s_pos[t * k + d];
                 if (row >= 0) quant_block_put(q, Xq, Xs, row, blk, D);
             }
@@ -528,7 +543,7 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
 // 0 when this front end applies, else the caller takes the general kernels
 int launch_front_decode(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int *idx, float *wt,
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                        int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0,
+                        int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0, int put_k,
                         cudaStream_t st) {
     if (T > 16 || T * k > FD_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || n_expert > FD_THREADS || D % (32 * Q36_QK) ||
         T * (D / (32 * Q36_QK)) > FD_QWARPS || s1 - s0 > 16)
@@ -547,7 +562,7 @@ int launch_front_decode(const float *logits, int n_expert, int k, float scale, i
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&cfg, k_front_decode, logits, n_expert, k, scale, T, row_stride, idx, wt, ecount, eoffs, elist, pos,
-                       soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D, shared_row0);
+                       soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D, shared_row0, put_k);
     return check_launch();
 }
 

@@ -146,7 +146,10 @@ class NativeEP:
         import ctypes as C
         from . import moe
         self.moe, self.layers, self.world, self.rank, self.T = moe, layers, world, rank, T
-        self.launches_per_layer = 13 if world * T <= 16 else 14
+        # decode sizes: front cluster (route, dispatch, quantise), pack, sort + plan of the received slots, unpack,
+        # FFN (one launch when no expert can receive more than 16 rows, else two), gather, combine
+        small = T <= 16 and world * T * layers[0].k <= 1024
+        self.launches_per_layer = (7 if world * T <= 16 else 8) if small else 14
         dev = layers[0].device
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:

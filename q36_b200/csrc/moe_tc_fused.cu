@@ -340,7 +340,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // the registers hold the tile: TMEM is free again
             if (!t.kind) {
                 const int blk = mrow / Q36_QK;
-                {
+                if (t.nrows <= 2) {   // the usual routed group at decode: a short batch publishes sooner
+                    const float g0[2] = {g[0], g[1]}, u0[2] = {u[0], u[1]};
+                    swiglu_quant_store<2>(g0, u0, t.nrows, (size_t)t.row0, Hq, Hs, FF, blk, lane);
+                } else {
                     float g0[8], u0[8], g1[8], u1[8];
 #pragma unroll
                     for (int c = 0; c < 8; c++) { g0[c] = g[c]; u0[c] = u[c]; g1[c] = g[8 + c]; u1[c] = u[8 + c]; }

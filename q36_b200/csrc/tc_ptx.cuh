@@ -46,22 +46,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile 
     atomicCAS(status, 0, where);
     return false;
 }
-// Whole-warp wait with ONE polling lane: 128 threads polling one mbarrier word serialise on it and turn a
-// stage hand-over into microseconds.  All 32 lanes must call; returns the same value in every lane.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(a, parity, abort_flag, status, where) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    __syncwarp();   // the lanes' later accesses are ordered after lane 0's acquire
-    return ok != 0;
-}
-// non-blocking: has the phase with this parity completed?
-__device__ __forceinline__ bool mbar_test(uint32_t a, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, int w, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

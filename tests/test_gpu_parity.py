@@ -297,6 +297,31 @@ def test_ffn_tc_vs_oracle(moe, oracle, torch_cuda, layer, weights, T):
     _check_ffn(moe, oracle, torch_cuda, layer, weights, T, moe.PATH_TC, np.random.default_rng(60 + T))
 
 
+@pytest.mark.parametrize("T", [3, 16])
+def test_ffn_one_launch_matches_two_and_setup_only(moe, oracle, torch_cuda, layer, weights, T):
+    """With a bound of at most 16 rows per group the tensor-core call is ONE persistent launch (gate/up and down);
+    it must give what the two grouped-GEMM launches give, shared expert's group included.  The f32 sums differ in
+    their order (four partial accumulators against one), so a code of the quantised intermediate may sit on the
+    other side of a rounding boundary now and then.  stages = 4 alone builds the plan and touches no output."""
+    torch = torch_cuda
+    X, L, xt, lt, idx, wt, eo, el, pos, Xq, Xs = _sorted_inputs(moe, oracle, torch, T, np.random.default_rng(70 + T))
+    n, R = T * K8, T * (K8 + 1)
+    soffs = torch.tensor([n, n + T], dtype=torch.int32, device="cuda")
+    shared = (layer.Sg, layer.Su, layer.Sd)
+    two = moe.expert_ffn_sorted(layer.Wg, layer.Wu, layer.Wd, E, eo, Xq, Xs, D, FF, moe.PATH_TC, shared=shared, soffs=soffs)
+    one = moe.expert_ffn_sorted(layer.Wg, layer.Wu, layer.Wd, E, eo, Xq, Xs, D, FF, moe.PATH_TC, shared=shared, soffs=soffs,
+                                max_group_rows=T)
+    hq1, hq2 = one[0].cpu().numpy(), two[0].cpu().numpy()
+    assert (hq1 != hq2).sum() <= max(2, hq1.size // 2000)
+    assert (one[1].cpu().numpy() != two[1].cpu().numpy()).sum() <= 2          # Hs
+    assert rel_l2(one[2].cpu().numpy(), two[2].cpu().numpy()) < 1e-3
+    bufs = tuple(torch.full_like(b, 7) for b in one)
+    moe.expert_ffn_sorted(layer.Wg, layer.Wu, layer.Wd, E, eo, Xq, Xs, D, FF, moe.PATH_TC, shared=shared, soffs=soffs,
+                          stages=4, bufs=bufs, max_group_rows=T)
+    for b in bufs:
+        assert bool((b == 7).all())
+
+
 def test_tc_and_gemv_paths_agree(moe, oracle, torch_cuda, layer, weights):
     torch = torch_cuda
     rng = np.random.default_rng(8)

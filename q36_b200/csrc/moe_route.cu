@@ -242,12 +242,28 @@ __device__ __forceinline__ QBlock quant_block_lane(const void *__restrict__ X, s
     r.hi = make_uint4(w[4], w[5], w[6], w[7]);
     return r;
 }
-__device__ __forceinline__ void quant_block_put(const QBlock &q, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int row,
-                                                int blk, int K) {
-    uint4 *d = reinterpret_cast<uint4 *>(Xq + (size_t)row * K + (size_t)blk * Q36_QK);
-    d[0] = q.lo;
-    d[1] = q.hi;
-    Xs[(size_t)row * (K / Q36_QK) + blk] = (uint8_t)(127 + q.e2);
+// Lane pairs swap halves so that each of the two store instructions of a warp covers 512 contiguous bytes (whole
+// sectors); a lane storing its own two halves would leave every sector half-written twice.  All 32 lanes call.
+struct QStore { uint4 first, second; };   // what this lane stores at byte 64 * (lane / 2) + 16 * (lane & 1) and + 32
+__device__ __forceinline__ QStore quant_block_pair(const QBlock &q, int lane) {
+    const bool odd = lane & 1;
+    // even lane keeps lo, gives hi; odd lane keeps hi, gives lo
+    const uint4 give = odd ? q.lo : q.hi;
+    uint4 got;
+    got.x = __shfl_xor_sync(0xffffffffu, give.x, 1); got.y = __shfl_xor_sync(0xffffffffu, give.y, 1);
+    got.z = __shfl_xor_sync(0xffffffffu, give.z, 1); got.w = __shfl_xor_sync(0xffffffffu, give.w, 1);
+    QStore r;
+    r.first = odd ? got : q.lo;     // block 2i:   [lo_2i | hi_2i]     <- lanes 2i, 2i+1
+    r.second = odd ? q.hi : got;    // block 2i+1: [lo_2i+1 | hi_2i+1] <- lanes 2i, 2i+1
+    return r;
+}
+// blk0 = first block of the warp's run of 32
+__device__ __forceinline__ void quant_block_put(const QStore &qs, int e2, uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs,
+                                                int row, int blk0, int lane, int K) {
+    uint8_t *base = Xq + (size_t)row * K + (size_t)blk0 * Q36_QK + 64 * (lane >> 1) + 16 * (lane & 1);
+    *reinterpret_cast<uint4 *>(base) = qs.first;
+    *reinterpret_cast<uint4 *>(base + 32) = qs.second;
+    Xs[(size_t)row * (K / Q36_QK) + blk0 + lane] = (uint8_t)(127 + e2);
 }
 
 // warp = (token, run of 32 blocks); K must be a multiple of 1024
@@ -266,9 +282,10 @@ k_quant_rows(const void *__restrict__ X, uint8_t *__restrict__ Xq, uint8_t *__re
     for (int d = 0; d < 8; d++) rows[d] = (d < k) ? pos[(size_t)t * k + d] : -1;   // (issued before the row is read)
     rows[8] = shared_row0 >= 0 ? shared_row0 + t : -1;
     const QBlock q = quant_block_lane<BF16>(X, (size_t)t * K + (size_t)blk * Q36_QK);
+    const QStore qs = quant_block_pair(q, lane);
 #pragma unroll
     for (int d = 0; d < 9; d++)
-        if (rows[d] >= 0) quant_block_put(q, Xq, Xs, rows[d], blk, K);
+        if (rows[d] >= 0) quant_block_put(qs, q.e2, Xq, Xs, rows[d], blk - lane, lane, K);
 }
 
 template <bool BF16, bool SCATTER>
@@ -408,14 +425,14 @@ int launch_front_small(const float *logits, int n_expert, int k, float scale, in
 // ----------------------------------------------- decode front end: one cluster
 // At most 16 tokens (T * k <= 128 entries), all experts resident.  One thread-block cluster, one launch:
 //   CTA 0        router -> stable dispatch -> work plan of the fused tensor-core kernel
-//   CTA 1        quantises the token rows (needs no routing result), waits at the cluster barrier for CTA 0's
-//                row positions, then writes every block to the k + 1 rows it feeds.
+//   CTAs 1..7    quantise the token rows (needs no routing result), wait at the cluster barrier for CTA 0's
+//                row positions, then write every block to the k + 1 rows it feeds.
 // Same results as k_front_small + k_quant_e4m3<., true>: the same route_row, the same ascending-entry order
 // inside an expert's bucket, the same quantiser.
-constexpr int FD_CLUSTER = 2;
+constexpr int FD_CLUSTER = 8;
 constexpr int FD_THREADS = 1024;
 constexpr int FD_MAX_ENTRIES = 128;
-constexpr int FD_QWARPS = FD_THREADS / 32;                        // one (token, run of 32 blocks) per warp of CTA 1
+constexpr int FD_QWARPS = (FD_CLUSTER - 1) * (FD_THREADS / 32);   // one (token, run of 32 blocks) per quantising warp
 
 __global__ void __launch_bounds__(FD_THREADS)
 k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scale, int T, int row_stride,
@@ -433,19 +450,25 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
     __shared__ int s_pos[FD_MAX_ENTRIES];          // row of every entry; CTA 0 writes it into every CTA of the cluster
     if (cluster.block_rank() != 0) {
         // ---- quantise now (warp = token x run of 32 blocks, lane = block), place after the barrier
+        // (units are dealt across the CTAs first: one SM's store path would take microseconds for all rows)
         const int runs = D / (32 * Q36_QK);
-        const int t = warp / runs, blk = (warp % runs) * 32 + lane;
-        const bool mine = warp < T * runs;
+        const int unit = ((int)cluster.block_rank() - 1) + (FD_CLUSTER - 1) * warp;
+        const int t = unit / runs, blk0 = (unit % runs) * 32;
+        const bool mine = unit < T * runs;
         QBlock q;
-        if (mine) q = x_is_bf16 ? quant_block_lane<true>(X, (size_t)t * D + (size_t)blk * Q36_QK)
-                                : quant_block_lane<false>(X, (size_t)t * D + (size_t)blk * Q36_QK);
+        QStore qs;
+        if (mine) {
+            q = x_is_bf16 ? quant_block_lane<true>(X, (size_t)t * D + (size_t)(blk0 + lane) * Q36_QK)
+                          : quant_block_lane<false>(X, (size_t)t * D + (size_t)(blk0 + lane) * Q36_QK);
+            qs = quant_block_pair(q, lane);
+        }
         cluster.sync();
         if (mine) {
             for (int d = 0; d < put_k; d++) {
                 const int row = s_pos[t * k + d];
-                if (row >= 0) quant_block_put(q, Xq, Xs, row, blk, D);
+                if (row >= 0) quant_block_put(qs, q.e2, Xq, Xs, row, blk0, lane, D);
             }
-            if (shared_row0 >= 0) quant_block_put(q, Xq, Xs, shared_row0 + t, blk, D);
+            if (shared_row0 >= 0) quant_block_put(qs, q.e2, Xq, Xs, shared_row0 + t, blk0, lane, D);
         }
         return;
     }

@@ -145,6 +145,16 @@ def cpu_layer_rate(tokens: int, budget_s: float):
                             "C dequantiser over gate/up/down + fp32 matmul, OpenMP over rows"}, per_eval
 
 
+def workload_config(NL, T, world, experts_per_rank, launch):
+    """The `config` object of both arms' JSON lines."""
+    return {"workload": f"decode stack: {NL} distinct MoE layers (256+1 MXFP4 experts, D=2048, FF=512, top-8), "
+                        f"{T} tokens per rank per step ({world * T} global)",
+            "tokens_per_rank": T, "layers": NL, "experts_per_rank": experts_per_rank,
+            "parallelism": f"ep{world}" if world > 1 else "single",
+            "l2": f"inputs larger than L2: each step streams {NL} layers of distinct expert weights",
+            "launch": launch}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -165,8 +175,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * T * args.layers / v, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"decode, {args.layers} MoE layers, {T} tokens per step, CPU (bounded sample per step; "
-                               "ms_per_step extrapolates the sample to a whole step)"},
+        # the same workload as the GPU arm's line (a bounded sample of it per step: see cpu_baseline.sample;
+        # ms_per_step extrapolates the sample to a whole step)
+        "config": workload_config(args.layers, args.tokens, args.gpus, E // max(1, args.gpus), "host cores, OpenMP"),
         "cpu_baseline": base, "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": wall}))
 
@@ -300,12 +311,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "mxfp4 x e4m3 -> f32", "data": "synthetic",
-        "config": {"workload": f"decode stack: {NL} distinct MoE layers (256+1 MXFP4 experts, D=2048, FF=512, top-8), "
-                               f"{T} tokens per rank per step ({world * T} global)",
-                   "tokens_per_rank": T, "layers": NL, "experts_per_rank": se1 - se0,
-                   "parallelism": f"ep{world}" if world > 1 else "single",
-                   "l2": f"inputs larger than L2: each step streams {NL} layers of distinct expert weights",
-                   "launch": "CUDA graph of one step" if graph is not None else "stream launches"},
+        "config": workload_config(NL, T, world, se1 - se0, "CUDA graph of one step" if graph is not None else "stream launches"),
         "e2e": e2e, "gpu_launches": launches_per_layer * NL * args.steps, "clocks": clk.summary(),
         "roofline": roof, "peaks": peak_kind,
     }

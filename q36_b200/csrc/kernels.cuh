@@ -42,7 +42,7 @@ int launch_gateup_gemv(const void *Wg, const void *Wu, int n_group, const int *g
 int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *Sd, const int *soffs,
                      const uint8_t *Hq, const uint8_t *Hs, float *Y, int D, int FF, cudaStream_t st);
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
-                   const float *shgate, int shgate_stride, int D, int k, int T, cudaStream_t st);
+                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st);
 int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
                        cudaStream_t st);
 int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st);

@@ -116,6 +116,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
     const int ng = se1 - se0;
     const int *goffs = w.eoffs + se0;
+    bool decode_kernel = false;     // the FFN is the one persistent decode launch
     if (!use_tc) {
         if ((rc = launch_gateup_gemv(Wg, Wu, ng, goffs, shared ? Sg : nullptr, shared ? Su : nullptr, w.soffs, w.Xq,
                                      w.Xs, w.Hq, w.Hs, D, FF, st)))
@@ -126,7 +127,8 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st)))
             return rc;
         static const bool no_fuse = getenv("Q36_NOFUSE") != nullptr;
-        if (T <= 16 && !no_fuse) {
+        decode_kernel = T <= 16 && !no_fuse;
+        if (decode_kernel) {
             // decode: gate/up and down in one persistent launch
             if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
                                              ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, st)))
@@ -140,8 +142,10 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         }
     }
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
+    // (behind the decode kernel the combine may read the routing results before its grid dependency resolves:
+    // that kernel lets its successor start only after it has seen the front end complete)
     if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
-                             T, st)))
+                             T, decode_kernel, st)))
         return rc;
     if (idx_out && (rc = ck(cudaMemcpyAsync(idx_out, w.idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
     if (wt_out && (rc = ck(cudaMemcpyAsync(wt_out, w.wt, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
@@ -277,7 +281,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
 int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float *wt, const float *SH_rows,
                     const float *shgate, int shgate_stride, int D, int k, int T, void *stream) {
     if (!out || !Y_rows || !pos || !wt || D % 4 || k <= 0 || T < 0) return Q36_MOE_EINVAL;
-    return launch_combine(out, Y_rows, pos, wt, SH_rows, shgate, shgate_stride, D, k, T, (cudaStream_t)stream);
+    return launch_combine(out, Y_rows, pos, wt, SH_rows, shgate, shgate_stride, D, k, T, false, (cudaStream_t)stream);
 }
 
 uint64_t q36_moe_workspace_bytes(int T_max, int n_expert, int k, int D, int FF) {

@@ -281,7 +281,7 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     if ((rc = launch_gather_rows(w.Y, w.lpos, w.back, S, D * 4, st))) return rc;
     if ((rc = all_to_all(api, c, w.back, w.recv_y, (size_t)C * D * 4, st))) return rc;
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
-    return launch_combine(out, w.recv_y, w.ypos, w.wt, shared ? w.Y + (size_t)R * D : nullptr, shg, logit_stride, D, k, T, st);
+    return launch_combine(out, w.recv_y, w.ypos, w.wt, shared ? w.Y + (size_t)R * D : nullptr, shg, logit_stride, D, k, T, false, st);
 }
 
 }  // extern "C"

@@ -203,11 +203,17 @@ k_down_gemv(const uint8_t *__restrict__ Wd, int n_group, const int *__restrict__
 // ----------------------------------------------------------------- combine
 // k_moe_combine / k_moe_combine_pf (q36_engine.cu:785-791, 3393-3401): slot
 // order, fp32.  grid (D/1024, T), 256 threads x float4.
+// EARLY_META: the row positions, weights and gate logits are read BEFORE the grid dependency resolves.  Only
+// for a launch whose predecessor in the stream (a) does not write them and (b) lets its successor start only
+// after it has itself seen the kernel that wrote them complete -- the decode kernel, which synchronises on its
+// own dependency before it signals its successor.  It takes one memory latency off a kernel that is nothing else.
+template <bool EARLY_META>
 __global__ void __launch_bounds__(256)
 k_combine(float *__restrict__ out, const float *__restrict__ Y, const int *__restrict__ pos,
           const float *__restrict__ wt, const float *__restrict__ SH, const float *__restrict__ shgate,
           int shgate_stride, int D, int k) {
-    Q36_GDS();
+    if (!EARLY_META) Q36_GDS();
+    else cudaTriggerProgrammaticLaunchCompletion();
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= D) return;
@@ -224,6 +230,7 @@ k_combine(float *__restrict__ out, const float *__restrict__ Y, const int *__res
         w[s] = (s < k) ? wt[(size_t)t * k + s] : 0.f;
     }
     const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
+    if (EARLY_META) cudaGridDependencySynchronize();
     float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
     if (SH) ysh = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
 #pragma unroll
@@ -294,11 +301,12 @@ int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *
     return check_launch();
 }
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
-                   const float *shgate, int shgate_stride, int D, int k, int T, cudaStream_t st) {
+                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st) {
     if (T <= 0) return Q36_MOE_OK;
     if (k <= 0 || k > 8) return Q36_MOE_EINVAL;   // the kernel keeps one row per slot in registers
     dim3 grid((D / 4 + 255) / 256, T);
-    launch_k(k_combine, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
+    if (early_meta) launch_k(k_combine<true>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
+    else launch_k(k_combine<false>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
     return check_launch();
 }
 int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,

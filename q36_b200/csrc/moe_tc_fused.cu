@@ -124,7 +124,11 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    Q36_GDS();   // from here on: global memory written by earlier kernels (the plan, Xq/Xs)
+    // Synchronise FIRST, then let the next kernel of the stream start: whatever follows this kernel may rely on
+    // everything before it (the front end's routing results) being complete as soon as it runs at all.
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
+    // from here on: global memory written by earlier kernels (the plan, Xq/Xs)
 
     const int G = plan->n_groups;
     const int n0 = plan->n_tiles[0], n_tiles = n0 + plan->n_tiles[1];

@@ -116,7 +116,7 @@ def cpu_cores():
 
 
 # --------------------------------------------------------- CPU baseline arm
-def cpu_layer_rate(tokens: int, budget_s: float):
+def cpu_layer_rate(tokens: int, limit_s: float):
     """The reference's CPU implementation of the path -- its C dequantiser over the three matrices of an
     expert + a plain fp32 matmul (oracle/_ref when present, else the oracle port) -- on all host cores.
     A sample of (token, expert) evaluations of one T-token layer; returns token-layers/s."""
@@ -132,7 +132,7 @@ def cpu_layer_rate(tokens: int, budget_s: float):
     t0 = time.perf_counter()
     n_eval, spent = 0, 0.0
     kind = "port"
-    while spent < budget_s and n_eval < 40 * tokens * (K8 + 1):
+    while spent < limit_s and n_eval < 40 * tokens * (K8 + 1):
         e = n_eval % 4
         sec, _, kind, nthr = O.cpu_expert_seconds(w["gate"][e], w["up"][e], w["down"][e], D, FF, xd[n_eval % tokens],
                                                   reps=3, threads=cores)
@@ -160,13 +160,13 @@ def run_reference(args):
     if rank != 0:
         return
     T = args.tokens * args.gpus
-    per_step_budget = max(0.5, min(5.0, 120.0 / max(1, args.steps + args.warmup)))
+    per_step_limit = max(0.5, min(5.0, 120.0 / max(1, args.steps + args.warmup)))
     for _ in range(args.warmup):
-        cpu_layer_rate(T, per_step_budget / 4)
+        cpu_layer_rate(T, per_step_limit / 4)
     vals, base = [], None
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        r, base, per_eval = cpu_layer_rate(T, per_step_budget)
+        r, base, per_eval = cpu_layer_rate(T, per_step_limit)
         vals.append(r)
     wall = time.perf_counter() - t0
     v = sorted(vals)[len(vals) // 2]

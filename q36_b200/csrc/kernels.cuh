@@ -28,11 +28,11 @@ int launch_front_decode(const float *logits, int n_expert, int k, float scale, i
                         cudaStream_t st);
 int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
                                int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                               int *status, cudaStream_t st);
+                               int *status, int plan_tile_rows, cudaStream_t st);
 int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
                        int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
-                       int shared_row0, cudaStream_t st);
+                       int shared_row0, int plan_tile_rows, cudaStream_t st);
 
 // moe_gemv.cu
 // Sg/Su/Sd + soffs[2]: one extra group (the shared expert) with its own planes and row range, or NULL
@@ -51,7 +51,8 @@ int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t s
 // One plan per grouped-FFN call (groups = n_group routed + the shared expert's when soffs != NULL), then the
 // gate/up and the down launch read it.  status: 4 ints, [0] gate/up, [1] down.
 uint64_t tc_ws_bytes();
-int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
+// tile_rows: 0 for the two grouped-GEMM launches, 16 for the one-launch decode kernel
+int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status, int tile_rows,
                    cudaStream_t st);
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
                      int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
@@ -69,7 +70,8 @@ int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box
 int sm_count();
 
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
-int ffn_fused_small_max_rows(int D, int FF);   // largest R_max launch_ffn_fused_small accepts
+int ffn_fused_small_max_rows(int D, int FF);
+int fused_rows_limit();            // policy: rows up to which that kernel is preferred when groups may exceed 16 rows   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
                            uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st);

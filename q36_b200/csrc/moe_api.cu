@@ -67,6 +67,16 @@ static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
     return w;
 }
 
+// Rows up to which the one-launch decode kernel (token tiles of 16 rows) is used instead of the two grouped-GEMM
+// launches (token tiles of 112 / 128 rows) when groups may exceed 16 rows.  Measured per layer on B200: 24 tokens 63 us
+// against 100 us, 64 tokens 94 against 155, 96 tokens 107 against 169: no limit besides what the kernel's tile
+// table holds (ffn_fused_small_max_rows); the variable is there for experiments.
+int fused_rows_limit() {
+    static int v = -1;
+    if (v < 0) { const char *e = getenv("Q36_FUSE_ROWS"); v = e ? atoi(e) : 1 << 30; }
+    return v;
+}
+
 static int pick_path(int path, int T) {
     if (path == Q36_MOE_PATH_GEMV || path == Q36_MOE_PATH_TC) return path;
     // The engine switches from its GEMV kernels to its tiled kernels at 14 rows (q36_engine.cu:2217-2221).
@@ -92,6 +102,9 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     int rc;
     const bool use_tc = pick_path(path, T) == Q36_MOE_PATH_TC;
     const bool fused_front = n <= 1024;
+    static const bool no_fuse = getenv("Q36_NOFUSE") != nullptr;
+    // decode: gate/up and down in one persistent launch (its plan is cut in token tiles of 16 rows)
+    const bool decode_kernel = use_tc && !no_fuse && fused_front && R <= fused_rows_limit() && R <= ffn_fused_small_max_rows(D, FF);
     static const bool no_cluster = getenv("Q36_NOCLUSTER") != nullptr;
     // decode on the tensor-core path with every expert resident: one cluster launch does all of the front end
     const bool cluster_front = use_tc && T <= 16 && n <= 128 && se0 == 0 && se1 == E && D % 1024 == 0 && D * T <= 32 * 1024 && !no_cluster;
@@ -104,7 +117,8 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     } else if (fused_front) {
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, se0, se1, w.idx, w.wt, w.ecount, w.eoffs,
                                      w.elist, w.pos, w.soffs, n, shared ? n + T : n, use_tc ? w.plan : nullptr, D, FF,
-                                     w.status, fused_quant ? X : nullptr, x_is_bf16, w.Xq, w.Xs, shared ? n : -1, st)))
+                                     w.status, fused_quant ? X : nullptr, x_is_bf16, w.Xq, w.Xs, shared ? n : -1,
+                                     decode_kernel ? 16 : 0, st)))
             return rc;
     } else {
         if ((rc = ck(cudaMemsetAsync(w.status, 0, 16, st)))) return rc;
@@ -116,7 +130,6 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
     const int ng = se1 - se0;
     const int *goffs = w.eoffs + se0;
-    bool decode_kernel = false;     // the FFN is the one persistent decode launch
     if (!use_tc) {
         if ((rc = launch_gateup_gemv(Wg, Wu, ng, goffs, shared ? Sg : nullptr, shared ? Su : nullptr, w.soffs, w.Xq,
                                      w.Xs, w.Hq, w.Hs, D, FF, st)))
@@ -124,12 +137,9 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
             return rc;
     } else {
-        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st)))
+        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, 0, st)))
             return rc;
-        static const bool no_fuse = getenv("Q36_NOFUSE") != nullptr;
-        decode_kernel = T <= 16 && !no_fuse;
         if (decode_kernel) {
-            // decode: gate/up and down in one persistent launch
             if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
                                              ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, st)))
                 return rc;
@@ -264,8 +274,10 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     int *status = (int *)p;
     void *plan = p + 256;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
-    if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, st))) return rc;
-    if (stages == 3 && max_group_rows > 0 && max_group_rows <= 16 && R_max <= ffn_fused_small_max_rows(D, FF))
+    const bool one_launch = stages == 3 && max_group_rows > 0 && R_max <= ffn_fused_small_max_rows(D, FF) &&
+                            (max_group_rows <= 16 || R_max <= fused_rows_limit());
+    if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : 0, st))) return rc;
+    if (one_launch)
         return launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, n_group,
                                       R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, st);
     const int mgr = max_group_rows > 0 ? max_group_rows : R_max;
@@ -371,7 +383,7 @@ int q36_moe_tc_selftest(const uint8_t *A_codes_scales, const uint8_t *B_q, const
     int rc;
     if ((rc = ck(cudaMemsetAsync(ws, 0, 16, st)))) return rc;
     if ((rc = ck(cudaMemcpyAsync(goffs, h, sizeof h, cudaMemcpyHostToDevice, st)))) return rc;
-    if ((rc = launch_tc_plan(goffs, 1, nullptr, 128, K, (uint8_t *)ws + 512, (int *)ws, st))) return rc;
+    if ((rc = launch_tc_plan(goffs, 1, nullptr, 128, K, (uint8_t *)ws + 512, (int *)ws, 0, st))) return rc;
     if ((rc = launch_down_tc(A_codes_scales, nullptr, 1, N, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws + 1, st)))
         return rc;
     return q36_moe_ws_status(ws, stream);

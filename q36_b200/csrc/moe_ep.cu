@@ -235,7 +235,7 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
             return rc;
     } else if (n <= 1024) {
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, 0, E, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
-                                     w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, nullptr, 0, nullptr, nullptr, -1, st)))
+                                     w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, nullptr, 0, nullptr, nullptr, -1, 0, st)))
             return rc;
     } else {
         if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
@@ -249,9 +249,11 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     if ((rc = all_to_all(api, c, w.send, w.recv, (size_t)C * rowb, st))) return rc;
     // 4. local plan over the received slots; empty slots (-1) and nothing else drop out
     const bool small_plan = S <= 1024;   // one block sorts the slots and writes the work plan
+    // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count
+    const bool one_launch = R + T <= ffn_fused_small_max_rows(D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
     if (small_plan) {
         if ((rc = launch_dispatch_plan_small(w.recv + (D + nbs), rowb, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs,
-                                             R, shared ? R + T : R, w.plan, D, FF, w.status, st)))
+                                             R, shared ? R + T : R, w.plan, D, FF, w.status, one_launch ? 16 : 0, st)))
             return rc;
     } else {
         launch_k(k_ep_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)w.recv, S, rowb, D + nbs, w.reid);
@@ -263,10 +265,11 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     if ((rc = check_launch())) return rc;
     // 5. grouped expert FFN on the local shard (+ shared expert on the own tokens)
     const int *goffs = w.loffs + se0;
-    if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, st))) return rc;
+    if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, one_launch ? 16 : 0, st)))
+        return rc;
     // an expert receives at most one row per token of every rank: with at most 16 of them the decode kernel
     // (gate/up and down in one persistent launch) applies
-    if (world * T <= 16 && R + T <= ffn_fused_small_max_rows(D, FF)) {
+    if (one_launch) {
         if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, per,
                                          R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, st)))
             return rc;

@@ -313,7 +313,7 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
               int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1,
               TcPlan *plan, int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16,
               uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0,
-              const uint8_t *__restrict__ ent, int ent_stride, int n_ent) {
+              const uint8_t *__restrict__ ent, int ent_stride, int n_ent, int plan_tile_rows) {
     // ent != nullptr: no routing, the n_ent entries' expert ids are the ints at ent + i * ent_stride (T, k unused)
     Q36_GDS();
     __shared__ unsigned short cnt[FRONT_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // 32 KB
@@ -378,7 +378,7 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
         } else pos[tid] = -1;
     }
     // groups here hold at most T <= 128 rows, one or two token tiles: ranking by size would buy nothing
-    if (plan) tc_plan_block(s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, scratch, false);
+    if (plan) tc_plan_block(s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, scratch, false, plan_tile_rows);
     if (X) {   // decode: quantise and scatter the T rows here as well (pos[] of this block is visible after the barrier)
         __syncthreads();
         const int nbk = D / Q36_QK;
@@ -402,22 +402,23 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
 // dispatch (+ work plan) of entries whose expert ids sit in a strided buffer: k_front_small without the router
 int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
                                int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                               int *status, cudaStream_t st) {
+                               int *status, int plan_tile_rows, cudaStream_t st) {
     if (n_ent > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || !ent) return Q36_MOE_EINVAL;
     launch_k(k_front_small, dim3(1), dim3(1024), 0, st, (const float *)nullptr, n_expert, 1, 1.f, 0, 0, se0, se1, (int *)nullptr,
              (float *)nullptr, ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status,
-             (const void *)nullptr, 0, (uint8_t *)nullptr, (uint8_t *)nullptr, D, -1, (const uint8_t *)ent, ent_stride, n_ent);
+             (const void *)nullptr, 0, (uint8_t *)nullptr, (uint8_t *)nullptr, D, -1, (const uint8_t *)ent, ent_stride, n_ent,
+             plan_tile_rows);
     return check_launch();
 }
 
 int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
                        int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
-                       int shared_row0, cudaStream_t st) {
+                       int shared_row0, int plan_tile_rows, cudaStream_t st) {
     if (T * k > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E) return Q36_MOE_EINVAL;
     launch_k(k_front_small, dim3(1), dim3(1024), 0, st, logits, n_expert, k, scale, T, row_stride, se0, se1, idx, wt,
              ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D,
-             shared_row0, (const uint8_t *)nullptr, 0, 0);
+             shared_row0, (const uint8_t *)nullptr, 0, 0, plan_tile_rows);
     return check_launch();
 }
 
@@ -546,7 +547,7 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
                     G++;
                 }
                 plan->base[0][G] = ta; plan->base[1][G] = tb;
-                plan->n_tiles[0] = ta; plan->n_tiles[1] = tb; plan->n_groups = G; plan->gu_done = 0;
+                plan->n_tiles[0] = ta; plan->n_tiles[1] = tb; plan->n_groups = G; plan->gu_done = 0; plan->tile_rows = 16;
             }
         }
     }

@@ -76,11 +76,11 @@ struct TcCfg {
 // ------------------------------------------------------------- tile plan
 __global__ void __launch_bounds__(512)
 k_tc_plan(const int *__restrict__ goffs, int n_group, const int *__restrict__ soffs, TcPlan *plan, int mt_gu,
-          int mt_dn, int *status) {
+          int mt_dn, int *status, int tile_rows) {
     Q36_GDS();
     __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
     if (threadIdx.x < 4) status[threadIdx.x] = 0;
-    tc_plan_block(goffs, n_group, soffs != nullptr, soffs ? soffs[0] : 0, soffs ? soffs[1] : 0, plan, mt_gu, mt_dn, scratch, true);
+    tc_plan_block(goffs, n_group, soffs != nullptr, soffs ? soffs[0] : 0, soffs ? soffs[1] : 0, plan, mt_gu, mt_dn, scratch, true, tile_rows);
 }
 
 // ------------------------------------------------------------ main kernel
@@ -419,9 +419,9 @@ int sm_count() {
 uint64_t tc_ws_bytes() { return (sizeof(TcPlan) + 255) & ~(uint64_t)255; }
 
 int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int FF, void *plan, int *status,
-                   cudaStream_t st) {
+                   int tile_rows, cudaStream_t st) {
     if (n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
-    launch_k(k_tc_plan, dim3(1), dim3(512), 0, st, goffs, n_group, soffs, (TcPlan *)plan, FF / TC_M, D / TC_M, status);
+    launch_k(k_tc_plan, dim3(1), dim3(512), 0, st, goffs, n_group, soffs, (TcPlan *)plan, FF / TC_M, D / TC_M, status, tile_rows);
     return check_launch();
 }
 

@@ -68,7 +68,8 @@ struct FusedCfg {
     static constexpr int THREADS = 32 * (W_PUB + 1);
     static constexpr int DONE_PER_GROUP_PER_MTILE = 4;   // epilogue warps
     static constexpr int MAX_GROUPS = DISPATCH_MAX_GROUPS + 1;   // the plan lists every group, empty ones included
-    static constexpr int MAX_TILES = 40;                 // per CTA
+    static constexpr int MAX_TILES = 192;                // per CTA
+    static constexpr int TILE_ROWS = 16;                 // token rows per tile: the plan must be cut for this
     static constexpr int EXTRA_DOWN = 3;                 // extra down tiles of a CTA that is one gate/up tile short
 };
 static_assert(FusedCfg::STAGE_BYTES % 1024 == 0, "stage alignment");
@@ -145,7 +146,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     const int n_rest = n1 - extra_total;
     const int my_rest = b < n_rest ? (n_rest - b + grid - 1) / grid : 0;
     int my_tiles = my_gu + my_extra + my_rest;
-    const bool fits = G <= Cfg::MAX_GROUPS && my_tiles <= Cfg::MAX_TILES;
+    const bool fits = G <= Cfg::MAX_GROUPS && my_tiles <= Cfg::MAX_TILES && plan->tile_rows == Cfg::TILE_ROWS;
     if (!fits) {                                               // (uniform over the CTA) nothing is computed, the status says so
         my_tiles = 0;
         if (threadIdx.x == 0) atomicCAS(status, 0, 0x900);
@@ -170,8 +171,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
             const int mid = (lo + hi + 1) >> 1;
             if (base[mid] <= t) lo = mid; else hi = mid - 1;
         }
-        const int g = s_order[lo];
-        s_tiles[i] = make_int4(g | (kind << 16), t - base[lo], s_row0[g], s_cnt[g]);   // one token tile per group
+        // within a group: token tile slowest, row tile fastest (a group of more than 16 rows is several token tiles)
+        const int g = s_order[lo], local = t - base[lo], m_tiles = kind ? D / TC_M : mt_gu;
+        const int nt = local / m_tiles, mt = local - nt * m_tiles;
+        s_tiles[i] = make_int4(g | (kind << 16), mt, s_row0[g] + nt * Cfg::TILE_ROWS, min(Cfg::TILE_ROWS, (int)s_cnt[g] - nt * Cfg::TILE_ROWS));
     }
     __syncthreads();
     auto get_tile = [&](int j) {
@@ -192,9 +195,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         atomicCAS(status, 0, where);
         return false;
     };
-    // gate/up of group g is complete when every epilogue warp of each of its row tiles has published
-    const int done_target = mt_gu * Cfg::DONE_PER_GROUP_PER_MTILE;
+    // gate/up of group g is complete when every epilogue warp of each of its tiles has published
+    auto done_target_of = [&](int g) { return (((int)s_cnt[g] + Cfg::TILE_ROWS - 1) / Cfg::TILE_ROWS) * mt_gu * Cfg::DONE_PER_GROUP_PER_MTILE; };
     auto wait_group = [&](int g, int where) -> bool {
+        const int done_target = done_target_of(g);
         const volatile int *p = plan->done + g;
         for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
             int v;
@@ -375,7 +379,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                     // global count only when a wait was needed, to stop polling once the whole phase is over
                     int a;
                     asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(a) : "l"(plan->done + (v.x & 0xffff)) : "memory");
-                    if (a < done_target) {
+                    if (a < done_target_of(v.x & 0xffff)) {
                         if (!wait_group(v.x & 0xffff, 0x600)) break;
                         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(a) : "l"(&plan->gu_done) : "memory");
                         all_gu_done = a >= n0 * Cfg::DONE_PER_GROUP_PER_MTILE;

@@ -13,6 +13,7 @@ constexpr int TC_N_DOWN = 128;     // token rows per down tile
 // (0 = gate/up, 1 = down), so a tile index maps to (group, token tile, row tile) by a binary search.
 struct TcPlan {
     int n_groups, n_tiles[2];
+    int tile_rows;                        // token rows per tile the plan was cut for, both launches (0: 112 / 128)
     int gu_done;                          // gate/up tiles whose epilogue has finished (fused decode kernel only)
     int order[DISPATCH_MAX_GROUPS + 1];   // rank -> group
     int row0[DISPATCH_MAX_GROUPS + 1];    // group -> first row of the sorted space
@@ -28,7 +29,10 @@ struct TcPlan {
 // scratch: 4 * (DISPATCH_MAX_GROUPS + 1) ints of shared memory.  Needs at least one full warp; ends with all
 // plan fields written (no trailing barrier: the plan is read by later kernels only).
 __device__ __forceinline__ void tc_plan_block(const int *goffs, int n_group, bool has_extra, int s0, int s1,
-                                              TcPlan *plan, int mt_gu, int mt_dn, int *scratch, bool rank) {
+                                              TcPlan *plan, int mt_gu, int mt_dn, int *scratch, bool rank,
+                                              int tile_rows = 0) {
+    // tile_rows: token rows per tile of BOTH launches when not 0 (16: the one-launch decode kernel), else
+    // TC_N_GATEUP / TC_N_DOWN
     int *cnt = scratch, *order = cnt + DISPATCH_MAX_GROUPS + 1, *tg = order + DISPATCH_MAX_GROUPS + 1,
         *td = tg + DISPATCH_MAX_GROUPS + 1;
     const int tid = threadIdx.x;
@@ -53,8 +57,9 @@ __device__ __forceinline__ void tc_plan_block(const int *goffs, int n_group, boo
     __syncthreads();
     for (int r = tid; r < G; r += blockDim.x) {
         const int n = cnt[order[r]];
-        tg[r] = ((n + TC_N_GATEUP - 1) / TC_N_GATEUP) * mt_gu;
-        td[r] = ((n + TC_N_DOWN - 1) / TC_N_DOWN) * mt_dn;
+        const int ngu = tile_rows ? tile_rows : TC_N_GATEUP, ndn = tile_rows ? tile_rows : TC_N_DOWN;
+        tg[r] = ((n + ngu - 1) / ngu) * mt_gu;
+        td[r] = ((n + ndn - 1) / ndn) * mt_dn;
         plan->order[r] = order[r];
     }
     __syncthreads();
@@ -75,7 +80,7 @@ __device__ __forceinline__ void tc_plan_block(const int *goffs, int n_group, boo
         if (tid == 31) {
             plan->gu_done = 0;
             plan->base[0][G] = ia; plan->base[1][G] = ib;
-            plan->n_tiles[0] = ia; plan->n_tiles[1] = ib; plan->n_groups = G;
+            plan->n_tiles[0] = ia; plan->n_tiles[1] = ib; plan->n_groups = G; plan->tile_rows = tile_rows;
         }
     }
 }

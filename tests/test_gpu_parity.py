@@ -211,6 +211,42 @@ def _check_layer(moe, oracle, torch, layer, weights, T, path, rng, zipf=False, s
     return out
 
 
+@pytest.mark.parametrize("T", [5, 16, 40])
+def test_decode_layer_collisions_zero_rows_and_ties(moe, oracle, torch_cuda, layer, weights, T):
+    """Edge cases of the decode path: every token routes to the SAME eight experts (groups of T rows: one full
+    16-row token tile at T = 16, three token tiles at T = 40), some activation rows are all zero (block amax 0 ->
+    the smallest exponent), and the logits hold exact ties (lower expert id wins)."""
+    torch = torch_cuda
+    rng = np.random.default_rng(300 + T)
+    X = synth.activations(rng, T, D)
+    X[0] = 0.0
+    X[T - 1, 32:96] = 0.0                              # two whole 32-blocks of an otherwise normal row
+    row = synth.router_logits(rng, 1, E)[0]
+    row[[3, 40, 41, 200]] = row.max() + 1.0            # a four-way tie at the top, the rest distinct
+    L = np.tile(row, (T, 1)).astype(np.float32)
+    xt, lt = torch.from_numpy(X).cuda().to(torch.bfloat16), torch.from_numpy(L).cuda()
+    out, idx, wt = layer.forward(xt, lt, path=moe.PATH_TC, want_routing=True)
+    torch.cuda.synchronize()
+    layer.check_device_status()
+    widx, wwt = oracle.router_topk(L, K8, n_expert=E)
+    np.testing.assert_array_equal(idx.cpu().numpy(), widx)
+    assert list(widx[0][:4]) == [3, 40, 41, 200]
+    w = weights
+    want = oracle.moe_layer(w["gate"], w["up"], w["down"], w["sgate"][0], w["sup"][0], w["sdown"][0], D, FF, X, widx,
+                            wwt, L[:, E], tokens=np.arange(T), se0=layer.se0, se1=layer.se1, inc_shared=True)
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got[0]).max() == 0.0                 # a zero token stays zero through every stage
+    assert rel_l2(got, want) < TOL
+
+
+@pytest.mark.parametrize("T", [24, 64])
+def test_mid_size_layer_vs_oracle(moe, oracle, torch_cuda, layer, weights, T):
+    """Token counts between decode and prefill: the one-launch kernel with the shared expert's group (and any
+    routed group of more than 16 rows) cut into several 16-row token tiles."""
+    _check_layer(moe, oracle, torch_cuda, layer, weights, T, moe.PATH_TC, np.random.default_rng(400 + T), sample=8)
+
+
 @pytest.mark.parametrize("path", ["gemv", "tc"])
 @pytest.mark.parametrize("T", [1, 2, 4, 8, 16])
 def test_decode_layer_vs_oracle(moe, oracle, torch_cuda, layer, weights, T, path):

@@ -152,8 +152,8 @@ uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
  * max_group_rows: an upper bound on the rows of any single group when the
  * caller knows one (decode: the number of tokens), else 0.  With the
  * tensor-core path, stages == 3 and a bound given, gate/up and down run as
- * ONE persistent launch (token tiles of 16 rows) as long as its tile table
- * holds the call (about 1300 rows on 148 SMs). */
+ * ONE persistent launch (token tiles of 16 rows) up to 6300 rows in all,
+ * where the two launches with their 112/128-row token tiles take over. */
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group,
                               const int *goffs, const void *Sg, const void *Su, const void *Sd,
                               const int *soffs, int R_max, const uint8_t *Xq_rows,

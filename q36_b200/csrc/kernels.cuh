@@ -70,7 +70,7 @@ int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box
 int sm_count();
 
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
-int ffn_fused_small_max_rows(int D, int FF);
+bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF);   // does launch_ffn_fused_small take this call?
 int fused_rows_limit();            // policy: rows up to which that kernel is preferred when groups may exceed 16 rows   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,

@@ -69,11 +69,11 @@ static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
 
 // Rows up to which the one-launch decode kernel (token tiles of 16 rows) is used instead of the two grouped-GEMM
 // launches (token tiles of 112 / 128 rows) when groups may exceed 16 rows.  Measured per layer on B200: 24 tokens 63 us
-// against 100 us, 64 tokens 94 against 155, 96 tokens 107 against 169: no limit besides what the kernel's tile
-// table holds (ffn_fused_small_max_rows); the variable is there for experiments.
+// against 100 us, 64 tokens 94 against 155, 256 tokens 118 against 165, 512 tokens 150 against 181, 1024 tokens 220
+// against 198: the lines cross near 800 tokens (9 rows per token); the environment variable is there for experiments.
 int fused_rows_limit() {
     static int v = -1;
-    if (v < 0) { const char *e = getenv("Q36_FUSE_ROWS"); v = e ? atoi(e) : 1 << 30; }
+    if (v < 0) { const char *e = getenv("Q36_FUSE_ROWS"); v = e ? atoi(e) : 6300; }
     return v;
 }
 
@@ -104,7 +104,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     const bool fused_front = n <= 1024;
     static const bool no_fuse = getenv("Q36_NOFUSE") != nullptr;
     // decode: gate/up and down in one persistent launch (its plan is cut in token tiles of 16 rows)
-    const bool decode_kernel = use_tc && !no_fuse && fused_front && R <= fused_rows_limit() && R <= ffn_fused_small_max_rows(D, FF);
+    const bool decode_kernel = use_tc && !no_fuse && R <= fused_rows_limit() && ffn_fused_small_fits(R, se1 - se0, D, FF);
     static const bool no_cluster = getenv("Q36_NOCLUSTER") != nullptr;
     // decode on the tensor-core path with every expert resident: one cluster launch does all of the front end
     const bool cluster_front = use_tc && T <= 16 && n <= 128 && se0 == 0 && se1 == E && D % 1024 == 0 && D * T <= 32 * 1024 && !no_cluster;
@@ -137,7 +137,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
             return rc;
     } else {
-        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, 0, st)))
+        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, decode_kernel ? 16 : 0, st)))
             return rc;
         if (decode_kernel) {
             if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
@@ -274,7 +274,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     int *status = (int *)p;
     void *plan = p + 256;
     if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
-    const bool one_launch = stages == 3 && max_group_rows > 0 && R_max <= ffn_fused_small_max_rows(D, FF) &&
+    const bool one_launch = stages == 3 && max_group_rows > 0 && ffn_fused_small_fits(R_max, n_group, D, FF) &&
                             (max_group_rows <= 16 || R_max <= fused_rows_limit());
     if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : 0, st))) return rc;
     if (one_launch)

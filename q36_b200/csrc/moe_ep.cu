@@ -250,7 +250,7 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     // 4. local plan over the received slots; empty slots (-1) and nothing else drop out
     const bool small_plan = S <= 1024;   // one block sorts the slots and writes the work plan
     // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count
-    const bool one_launch = R + T <= ffn_fused_small_max_rows(D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
+    const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
     if (small_plan) {
         if ((rc = launch_dispatch_plan_small(w.recv + (D + nbs), rowb, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs,
                                              R, shared ? R + T : R, w.plan, D, FF, w.status, one_launch ? 16 : 0, st)))

@@ -472,16 +472,20 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
 }
 
 // every non-empty group has at least one row and one token tile, so the row count bounds the tiles of a CTA
-int ffn_fused_small_max_rows(int D, int FF) {
-    // per CTA: its round-robin shares of both tile kinds (rounded up) plus the extra down tiles of a short CTA
-    return (FusedCfg::MAX_TILES - 2 - (2 * D) / FF) * sm_count() / (FF / TC_M + D / TC_M);
+// Does the per-CTA tile table hold a call of R_max rows in n_group (+ 1 shared) groups?  A group of c rows is
+// ceil(c / 16) token tiles, so there are at most R_max / 16 + (non-empty groups) of them.
+bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF) {
+    using Cfg = FusedCfg;
+    const long tt = R_max / Cfg::TILE_ROWS + min(R_max, n_group + 1);
+    const long grid = sm_count(), n0 = tt * (FF / TC_M), n1 = tt * (D / TC_M);
+    return n_group + 1 <= Cfg::MAX_GROUPS && (n0 + grid - 1) / grid + (n1 + grid - 1) / grid + Cfg::EXTRA_DOWN + 1 <= Cfg::MAX_TILES;
 }
 
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
                            uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st) {
     using Cfg = FusedCfg;
-    if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || n_group + 1 > Cfg::MAX_GROUPS || R_max > ffn_fused_small_max_rows(D, FF)) return Q36_MOE_EINVAL;
+    if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || !ffn_fused_small_fits(R_max, n_group, D, FF)) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)FF * (D / 2) + (uint64_t)FF * (D / Q36_QK);   // same for [FF][D] and [D][FF]
     const uint64_t plane = (uint64_t)FF * (D / 2);
     if (!Sg) { Sg = Wg; Su = Wu; Sd = Wd; }

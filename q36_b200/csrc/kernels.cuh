@@ -74,6 +74,7 @@ bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF);   // does laun
 int fused_rows_limit();            // policy: rows up to which that kernel is preferred when groups may exceed 16 rows   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
-                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st);
+                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const int *rowmap, float *Ymap,
+                           int n_map, cudaStream_t st);
 
 }  // namespace q36

@@ -271,8 +271,8 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     // (gate/up and down in one persistent launch) applies
     if (one_launch) {
         if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, per,
-                                         R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, st)))
-            return rc;
+                                         R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, w.llist, w.back, R, st)))
+            return rc;   // (routed result rows land in the slots of the return exchange; the shared rows stay in Y)
     } else {
         if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
                                    w.Hq, w.Hs, D, FF, w.plan, w.status, st)))
@@ -281,7 +281,7 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
             return rc;
     }
     // 6. result rows back to their home ranks, then the weighted combine
-    if ((rc = launch_gather_rows(w.Y, w.lpos, w.back, S, D * 4, st))) return rc;
+    if (!one_launch && (rc = launch_gather_rows(w.Y, w.lpos, w.back, S, D * 4, st))) return rc;
     if ((rc = all_to_all(api, c, w.back, w.recv_y, (size_t)C * D * 4, st))) return rc;
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
     return launch_combine(out, w.recv_y, w.ypos, w.wt, shared ? w.Y + (size_t)R * D : nullptr, shg, logit_stride, D, k, T, false, st);

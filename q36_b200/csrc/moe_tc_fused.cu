@@ -83,7 +83,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                   const uint8_t *__restrict__ sfD, uint64_t sf_stride, const uint8_t *__restrict__ sfSG,
                   const uint8_t *__restrict__ sfSU, const uint8_t *__restrict__ sfSD, int n_routed,
                   const uint8_t *__restrict__ Xs, TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
-                  uint8_t *__restrict__ Hs, float *__restrict__ Y, int D, int FF, int *__restrict__ status) {
+                  uint8_t *__restrict__ Hs, float *__restrict__ Y, int D, int FF, int *__restrict__ status,
+                  const int *__restrict__ rowmap, float *__restrict__ Ymap, int n_map) {
+    // rowmap != nullptr: the result row of sorted row r < n_map goes to row rowmap[r] of Ymap instead of row r of Y
+    // (the expert-parallel step: straight into the slots of the return exchange)
     using Cfg = FusedCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -362,6 +365,16 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 // lane 0's CTA-scope release orders them before the publisher's device-scope one
                 __syncwarp();
                 if (lane == 0) asm volatile("red.release.cta.shared.add.s32 [%0], 1;" ::"r"(smem_u32(&s_pub)) : "memory");
+            } else if (rowmap && t.row0 < n_map) {
+                int dst[16];
+#pragma unroll
+                for (int c = 0; c < 16; c++) dst[c] = (c < t.nrows && t.row0 + c < n_map) ? rowmap[t.row0 + c] : -1;
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    if (c >= t.nrows) continue;
+                    if (dst[c] >= 0) Ymap[(size_t)dst[c] * D + mrow] = g[c];
+                    else if (t.row0 + c >= n_map) Y[(size_t)(t.row0 + c) * D + mrow] = g[c];
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < 16; c++)
@@ -483,7 +496,8 @@ bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF) {
 
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
-                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, cudaStream_t st) {
+                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const int *rowmap, float *Ymap,
+                           int n_map, cudaStream_t st) {
     using Cfg = FusedCfg;
     if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || !ffn_fused_small_fits(R_max, n_group, D, FF)) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)FF * (D / 2) + (uint64_t)FF * (D / Q36_QK);   // same for [FF][D] and [D][FF]
@@ -509,7 +523,7 @@ int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const
     const int grid = (int)min((long)sm_count(), max_tiles);
     launch_k(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
              (const uint8_t *)Wu + plane, (const uint8_t *)Wd + plane, estride, (const uint8_t *)Sg + plane,
-             (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status);
+             (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status, rowmap, Ymap, n_map);
     return check_launch();
 }
 

@@ -150,7 +150,7 @@ class NativeEP:
         # FFN (one launch when no expert can receive more than 16 rows, else two), gather, combine
         small = T <= 16 and world * T * layers[0].k <= 1024
         one_launch = world * T * layers[0].k + T <= 6300   # the library's switch to the two grouped-GEMM launches
-        self.launches_per_layer = (7 if one_launch else 8) if small else 14
+        self.launches_per_layer = (6 if one_launch else 8) if small else 14   # (one launch: no gather either)
         dev = layers[0].device
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:

@@ -26,6 +26,12 @@
  *     bytes.  Buffers that only this library reads and writes use hw order;
  *     q36_moe_quant_e4m3 writes logical order like the engine's kernel.
  *   - Experts outside [se0, se1) contribute zeros (q36_engine.cu:763-766).
+ *   - Weight scale bytes 0..254 are supported; byte 255 (NaN in the OCP MX
+ *     convention, 2^127 in ggml's) is not and gives unspecified values.
+ *   - The library keeps its per-device state (multiprocessor count, kernel
+ *     attributes) for the device that is current at the call, so one host
+ *     thread may drive several devices in turn with cudaSetDevice, as
+ *     q36_multi_prefill does (q36_engine.cu:4261-4306).
  */
 #ifndef Q36_MOE_H
 #define Q36_MOE_H
@@ -72,7 +78,8 @@ int q36_moe_dequant_mxfp4(const void *W, int M, int K, float *out, void *stream)
 /* ---- stages -------------------------------------------------------------- */
 
 /* k_router_topk (q36_ops.cuh:397-431): per row softmax statistics over
- * n_expert (= 256) logits, top-k (k <= 8) on the raw logits in descending
+ * n_expert (256, 128, 64 or 32; anything else is Q36_MOE_EINVAL here and in
+ * the whole-layer entries) logits, top-k (k <= 8) on the raw logits in descending
  * order with ties to the lower index, weights exp(v-m)/s, renormalised to
  * sum `scale` when renorm != 0.  logits row t starts at t*row_stride. */
 int q36_moe_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt,
@@ -90,7 +97,8 @@ int q36_moe_quant_e4m3(const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, i
  *   eoffs[n_expert+1]  exclusive prefix sum of ecount
  *   elist[n_entries]   packed buckets: elist[eoffs[e] + p] = p-th entry of e
  *   pos[n_entries]     inverse: row of entry i in elist, -1 if not resident
- * ws: q36_moe_dispatch_ws_bytes(n_entries, n_expert) bytes of scratch. */
+ * 0 <= se0 <= se1 <= n_expert <= 512; ids outside [se0, se1) or negative are
+ * not resident.  ws: q36_moe_dispatch_ws_bytes(n_entries, n_expert) bytes of scratch. */
 uint64_t q36_moe_dispatch_ws_bytes(int n_entries, int n_expert);
 int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1,
                      int *ecount, int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes,
@@ -140,9 +148,14 @@ int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, i
  *   Hq_rows [R][FF], Hs_rows [R][FF/32]: quantised SwiGLU output (hw order)
  *   Y_rows [R][D] f32
  * path: Q36_MOE_PATH_GEMV or Q36_MOE_PATH_TC.  ws (tensor-core path only):
- * q36_moe_ffn_ws_bytes(...) bytes; its first 16 bytes are device status
- * words, see q36_moe_ws_status. */
+ * q36_moe_ffn_ws_bytes(...) bytes; its first 256 bytes are the sticky device
+ * status words (q36_moe_ws_reset once after allocation, q36_moe_ws_status). */
 uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
+/* 1 when the one-launch decode kernel takes a call of R_max rows in n_group
+ * (+ 1 shared) groups with these matrix sizes, else 0 (then the two
+ * grouped-GEMM launches run): it needs D, FF <= 2048 and multiples of 512, and
+ * a per-block tile table that holds the call. */
+int q36_moe_one_launch_fits(int R_max, int n_group, int D, int FF);
 /* Sg/Su/Sd (or NULL): one extra group, the shared expert, with its own planes
  * and the row range [soffs[0], soffs[1]) (device ints).  stages: bit 0 runs
  * gate/up + SwiGLU, bit 1 runs down; 3 = both (the intermediate Hq/Hs is the
@@ -180,16 +193,32 @@ int q36_moe_combine(float *out, const float *Y_rows, const int *pos, const float
  * inc_shared == 0 suppresses its term (non-owner ranks, :3398-3400).
  * Optional outputs idx_out [T][k], wt_out [T][k] (may be NULL). */
 uint64_t q36_moe_workspace_bytes(int T_max, int n_expert, int k, int D, int FF);
-/* Synchronises `stream` and reports whether a tensor-core launch that used
- * the workspace `ws` gave up on a bounded wait (Q36_MOE_EDEVICE) or not
- * (Q36_MOE_OK).  The launch-only entry points cannot report this themselves. */
+/* The first 256 bytes of every workspace hold device status words.  They are
+ * STICKY: a kernel whose bounded wait gives up records where, and nothing but
+ * q36_moe_ws_reset clears it, so one check after many launches that shared a
+ * workspace (a 40-layer step, a benchmark loop) still sees a failure in any
+ * of them.  Call q36_moe_ws_reset once after allocating a workspace (its
+ * memory is not assumed to be zero) and again to clear a recorded failure. */
+int q36_moe_ws_reset(void *ws, void *stream);
+/* Synchronises `stream` and reports whether any launch that used the
+ * workspace `ws` since the last reset gave up on a bounded wait
+ * (Q36_MOE_EDEVICE; q36_moe_last_cuda_error() = 200000 + role * 256 + stage)
+ * or not (Q36_MOE_OK).  The launch-only entry points cannot report this
+ * themselves. */
 int q36_moe_ws_status(const void *ws, void *stream);
+/* Exercises the give-up path on its own: launches one warp that waits, with
+ * a limit of 1024 polls, on a barrier that nothing completes, records the
+ * give-up in ws like the tensor-core kernels do, and returns what
+ * q36_moe_ws_status then reports (Q36_MOE_EDEVICE when the mechanism works).
+ * The context stays usable; q36_moe_ws_reset clears the record. */
+int q36_moe_selftest_wait_timeout(void *ws, void *stream);
 int q36_moe_layer(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                   const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
                   const void *X, int x_is_bf16, const float *logits, int logit_stride,
                   int shgate_col, float route_scale, int inc_shared, float *out, int *idx_out,
                   float *wt_out, int T, int path, void *ws, uint64_t ws_bytes, void *stream);
-/* moe_ffn / pf_moe_block by name: the same call with the path fixed. */
+/* moe_ffn / pf_moe_block by name: q36_moe_layer with path = Q36_MOE_PATH_AUTO
+ * (the fastest measured path for the call's size) and no routing outputs. */
 int q36_moe_decode(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                    const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
                    const void *X, int x_is_bf16, const float *logits, int logit_stride,
@@ -228,7 +257,7 @@ int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows
  *   q36_moe_ep_init       collective; returns an opaque communicator
  *   q36_moe_ep_layer      launch-only: X [T][D], logits [T][stride] of this rank's T tokens -> out [T][D];
  *                         the exchange uses a fixed capacity of T*k rows per peer, so no count reaches the host
- *   ws: q36_moe_ep_workspace_bytes(...) bytes; its first 16 bytes are the status words of q36_moe_ws_status. */
+ *   ws: q36_moe_ep_workspace_bytes(...) bytes; its first 256 bytes are the status words (q36_moe_ws_reset, q36_moe_ws_status). */
 int q36_moe_ep_unique_id(void *out128);
 int q36_moe_ep_init(const void *id128, int rank, int world, void **comm_out);
 int q36_moe_ep_destroy(void *comm);

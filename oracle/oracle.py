@@ -30,8 +30,19 @@ def build(force: bool = False) -> None:
         os.path.getmtime(_LIB) < os.path.getmtime(os.path.join(_HERE, "q36_oracle.c"))
     ):
         subprocess.check_call(["make", "-s", "-C", _HERE, "_build/libq36oracle.so"])
-    if os.path.isdir("/root/reference") and (force or not os.path.exists(_REF)):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+    ref_dir = reference_dir()
+    if ref_dir and (force or not os.path.exists(_REF)):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_dir}"])
+
+
+def reference_dir() -> str | None:
+    """Root of the reference source tree: the Q36_REFERENCE environment variable, else a `reference`
+    directory beside the repository.  None when neither exists (then a prebuilt _ref is used as is)."""
+    cand = [os.environ.get("Q36_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cand:
+        if c and os.path.isfile(os.path.join(c, "q36_dequant.cuh")):
+            return c
+    return None
 
 
 def _p(a, t):

@@ -8,6 +8,8 @@ namespace q36 {
 
 constexpr int DISPATCH_MAX_GROUPS = 512;  // upper bound on expert groups per call
 
+bool router_supports(int n_expert);   // moe_api.cu: expert counts the router kernels are built for
+
 // moe_route.cu
 int launch_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale,
                        int renorm, int T, int row_stride, cudaStream_t st);
@@ -57,6 +59,8 @@ int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int F
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
                      int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF, const void *plan,
                      int *status, cudaStream_t st);
+// a 32-thread kernel that waits (1024 polls) on a barrier nobody completes, records the give-up in status[0] and returns
+int launch_wait_timeout(int *status, cudaStream_t st);
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq, const uint8_t *Hs,
                    float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st);
 
@@ -67,7 +71,11 @@ int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows);
 // K steps as consecutive 128-byte-swizzled tiles (coordinates: 0, row, K step [, expert])
 int make_map_codes_ksteps(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride, int ksteps);
 int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box_rows, int ksteps);
-int sm_count();
+int sm_count();            // of the CURRENT device
+int current_device();      // -1 when it cannot be determined or is beyond MAX_DEVICES
+constexpr int MAX_DEVICES = 64;   // per-device state of the library is kept for device ordinals below this
+// once per (kernel, device): allow `bytes` of dynamic shared memory; done = 64 flags owned by the caller
+int ensure_smem_attr(const void *kernel, int bytes, bool *done);
 
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
 bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF);   // does launch_ffn_fused_small take this call?

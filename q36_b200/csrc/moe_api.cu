@@ -27,6 +27,8 @@ static int ck(cudaError_t e) {
     return Q36_MOE_OK;
 }
 
+bool router_supports(int n_expert) { return n_expert == 256 || n_expert == 128 || n_expert == 64 || n_expert == 32; }
+
 static inline uint64_t al(uint64_t x) { return (x + 255) & ~(uint64_t)255; }
 
 // Carves the caller's workspace of one layer call.  Every region is 256-byte
@@ -95,6 +97,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     if (T <= 0 || k <= 0 || k > 8 || E <= 0 || E > DISPATCH_MAX_GROUPS || se0 < 0 || se1 > E || se0 >= se1)
         return Q36_MOE_EINVAL;
     if (D % 128 || FF % 128 || logit_stride < E) return Q36_MOE_EINVAL;
+    if (!router_supports(E)) return Q36_MOE_EINVAL;   // the router keeps E / 32 logits per lane: 32, 64, 128 or 256 experts
     const LayerWs w = carve(ws, T, E, k, D, FF);
     if (w.total > ws_bytes) return Q36_MOE_ENOSPACE;
     const bool shared = Sg && Su && Sd && inc_shared;
@@ -121,7 +124,6 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
                                      decode_kernel ? 16 : 0, st)))
             return rc;
     } else {
-        if ((rc = ck(cudaMemsetAsync(w.status, 0, 16, st)))) return rc;
         if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
         if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
                                   shared ? n + T : n, st)))
@@ -179,7 +181,7 @@ const char *q36_moe_strerror(int s) {
     }
 }
 int q36_moe_last_cuda_error(void) { return last_cuda_error(); }
-int q36_moe_abi_version(void) { return 1; }
+int q36_moe_abi_version(void) { return 2; }
 
 uint64_t q36_moe_expert_stride(int M, int K) { return (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK); }
 
@@ -217,7 +219,7 @@ int q36_moe_dequant_mxfp4(const void *W, int M, int K, float *out, void *stream)
 int q36_moe_router_topk(const float *logits, int n_expert, int k, int *idx, float *wt, float scale, int renorm,
                         int T, int row_stride, void *stream) {
     if (!logits || !idx || !wt || k <= 0 || k > 32 || k > n_expert) return Q36_MOE_EINVAL;
-    if (n_expert != 256 && n_expert != 128 && n_expert != 64 && n_expert != 32) return Q36_MOE_EINVAL;
+    if (!router_supports(n_expert)) return Q36_MOE_EINVAL;
     if (T < 0 || row_stride < n_expert) return Q36_MOE_EINVAL;
     return launch_router_topk(logits, n_expert, k, idx, wt, scale, renorm, T, row_stride, (cudaStream_t)stream);
 }
@@ -233,6 +235,7 @@ int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, in
                      int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes, void *stream) {
     if (!expert_of_entry || !ecount || !eoffs || !elist || !pos || !ws) return Q36_MOE_EINVAL;
     if (n_entries < 0 || n_expert <= 0 || n_expert > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (se0 < 0 || se0 > se1 || se1 > n_expert) return Q36_MOE_EINVAL;
     if (ws_bytes < dispatch_ws_bytes(n_entries, n_expert)) return Q36_MOE_ENOSPACE;
     return launch_dispatch(expert_of_entry, n_entries, n_expert, se0, se1, ecount, eoffs, elist, pos, ws, nullptr, 0,
                            0, (cudaStream_t)stream);
@@ -247,6 +250,11 @@ int q36_moe_quant_scatter(const void *X, int x_is_bf16, const int *pos, int k, i
 uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF) {
     (void)n_group; (void)R_max; (void)D; (void)FF;
     return 256 + tc_ws_bytes();
+}
+
+int q36_moe_one_launch_fits(int R_max, int n_group, int D, int FF) {
+    if (R_max <= 0 || n_group <= 0 || D <= 0 || FF <= 0) return 0;
+    return ffn_fused_small_fits(R_max, n_group, D, FF) ? 1 : 0;
 }
 
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
@@ -273,7 +281,6 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     uint8_t *p = (uint8_t *)ws;
     int *status = (int *)p;
     void *plan = p + 256;
-    if ((rc = ck(cudaMemsetAsync(p, 0, 16, st)))) return rc;
     const bool one_launch = stages == 3 && max_group_rows > 0 && ffn_fused_small_fits(R_max, n_group, D, FF) &&
                             (max_group_rows <= 16 || R_max <= fused_rows_limit());
     if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : 0, st))) return rc;
@@ -301,7 +308,13 @@ uint64_t q36_moe_workspace_bytes(int T_max, int n_expert, int k, int D, int FF) 
     return carve(nullptr, T_max, n_expert, k, D, FF).total;
 }
 
+int q36_moe_ws_reset(void *ws, void *stream) {
+    if (!ws) return Q36_MOE_EINVAL;
+    return ck(cudaMemsetAsync(ws, 0, 256, (cudaStream_t)stream));
+}
+
 int q36_moe_ws_status(const void *ws, void *stream) {
+    if (!ws) return Q36_MOE_EINVAL;
     int h[4] = {0, 0, 0, 0};
     int rc = ck(cudaMemcpyAsync(h, ws, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     if (rc) return rc;
@@ -327,7 +340,7 @@ int q36_moe_decode(const void *Wg, const void *Wu, const void *Wd, const void *S
                    const float *logits, int logit_stride, int shgate_col, float route_scale, int inc_shared,
                    float *out, int T, void *ws, uint64_t ws_bytes, void *stream) {
     return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
-                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_GEMV, ws, ws_bytes,
+                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_AUTO, ws, ws_bytes,
                       (cudaStream_t)stream);
 }
 int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd,
@@ -335,7 +348,7 @@ int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *
                     const float *logits, int logit_stride, int shgate_col, float route_scale, int inc_shared,
                     float *out, int T, void *ws, uint64_t ws_bytes, void *stream) {
     return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
-                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_TC, ws, ws_bytes,
+                      shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_AUTO, ws, ws_bytes,
                       (cudaStream_t)stream);
 }
 
@@ -386,6 +399,13 @@ int q36_moe_tc_selftest(const uint8_t *A_codes_scales, const uint8_t *B_q, const
     if ((rc = launch_tc_plan(goffs, 1, nullptr, 128, K, (uint8_t *)ws + 512, (int *)ws, 0, st))) return rc;
     if ((rc = launch_down_tc(A_codes_scales, nullptr, 1, N, N, B_q, B_s, Dout, 128, K, (uint8_t *)ws + 512, (int *)ws + 1, st)))
         return rc;
+    return q36_moe_ws_status(ws, stream);
+}
+
+int q36_moe_selftest_wait_timeout(void *ws, void *stream) {
+    if (!ws) return Q36_MOE_EINVAL;
+    int rc = launch_wait_timeout((int *)ws, (cudaStream_t)stream);
+    if (rc) return rc;
     return q36_moe_ws_status(ws, stream);
 }
 

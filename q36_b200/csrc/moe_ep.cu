@@ -219,6 +219,7 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     const int world = c->world, rank = c->rank, E = n_expert;
     if (T <= 0 || k <= 0 || k > 8 || E % world || E > DISPATCH_MAX_GROUPS || D % 512 || FF % 512 || logit_stride < E)
         return Q36_MOE_EINVAL;
+    if (!router_supports(E)) return Q36_MOE_EINVAL;
     const EpWs w = ep_carve(ws, T, world, E, k, D, FF);
     if (w.total > ws_bytes) return Q36_MOE_ENOSPACE;
     cudaStream_t st = (cudaStream_t)stream;

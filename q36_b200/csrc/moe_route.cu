@@ -90,7 +90,7 @@ k_dispatch_count(const int *__restrict__ eid, int n, int n_expert, int se0, int 
     int e = -1;
     if (i < n) {
         e = eid[i];
-        if (e < se0 || e >= se1 || e >= n_expert) e = -1;
+        if (e < 0 || e < se0 || e >= se1 || e >= n_expert) e = -1;
     }
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
@@ -323,7 +323,6 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
     const int n = ent ? n_ent : T * k;
     const int used_warps = (n + 31) / 32;          // only the warps that own entries contribute counts
     for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
-    if (status && tid < 4) status[tid] = 0;
     for (int t = warp; t < T && !ent; t += nwarp) {
         const float *l = logits + (size_t)t * row_stride;
         int *ix = idx + (size_t)t * k;
@@ -337,7 +336,7 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
     int e = -1;
     if (tid < n) {
         e = ent ? *reinterpret_cast<const int *>(ent + (size_t)tid * ent_stride) : idx[tid];
-        if (e < se0 || e >= se1 || e >= n_expert) e = -1;
+        if (e < 0 || e < se0 || e >= se1 || e >= n_expert) e = -1;
     }
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
@@ -488,7 +487,6 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
         else route_row<1>(l, k, s_idx + warp * k, s_wt + warp * k, scale, 1, lane);
     } else {
         for (int i = tid - 32 * T; i < used_warps * DISPATCH_MAX_E; i += FD_THREADS - 32 * T) (&cnt[0][0])[i] = 0;
-        if (status && lane < 4 && warp == T) status[lane] = 0;
     }
     __syncthreads();
     int e = -1;
@@ -496,7 +494,7 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
         e = s_idx[tid];
         idx[tid] = e;
         wt[tid] = s_wt[tid];
-        if (e >= n_expert) e = -1;
+        if (e < 0 || e >= n_expert) e = -1;
     }
     int r_in_warp = 0;
     if (warp < used_warps) {
@@ -653,7 +651,7 @@ static int *g_noalloc_ptr[64] = {nullptr};
 extern "C" int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1,
                                         int *ecount, int *eoffs, int *elist, int *pos, void *stream) {
     if (!expert_of_entry || !ecount || !eoffs || !elist || !pos) return Q36_MOE_EINVAL;
-    if (n_entries < 0 || n_expert <= 0) return Q36_MOE_EINVAL;
+    if (n_entries < 0 || n_expert <= 0 || se0 < 0 || se0 > se1 || se1 > n_expert) return Q36_MOE_EINVAL;
     if (n_entries > NOALLOC_MAX_ENTRIES || n_expert > NOALLOC_MAX_EXPERTS) {
         fprintf(stderr,
                 "q36_moe_dispatch_noalloc: %d entries / %d experts exceed the built-in scratch (max %d entries, %d "
@@ -663,7 +661,11 @@ extern "C" int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entrie
     }
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= 64) { q36::last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    if (e != cudaSuccess) { q36::last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    if (dev < 0 || dev >= 64) {
+        fprintf(stderr, "q36_moe_dispatch_noalloc: device ordinal %d is beyond the 64 this entry keeps an address for\n", dev);
+        return Q36_MOE_EINVAL;
+    }
     if (!g_noalloc_ptr[dev]) {   // first call on this device: resolve the array's device address
         int *p = nullptr;
         e = cudaGetSymbolAddress((void **)&p, g_noalloc_scratch);

@@ -79,8 +79,29 @@ k_tc_plan(const int *__restrict__ goffs, int n_group, const int *__restrict__ so
           int mt_dn, int *status, int tile_rows) {
     Q36_GDS();
     __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
-    if (threadIdx.x < 4) status[threadIdx.x] = 0;
+    (void)status;   // (the status words are sticky: only q36_moe_ws_reset clears them)
     tc_plan_block(goffs, n_group, soffs != nullptr, soffs ? soffs[0] : 0, soffs ? soffs[1] : 0, plan, mt_gu, mt_dn, scratch, true, tile_rows);
+}
+
+// The give-up path of the bounded waits on its own: one warp waits on an mbarrier phase that nothing ever
+// completes, with a limit of 1024 polls instead of 2^22, records `where` in the status word like every role of
+// the grouped-GEMM kernels does, and returns.  Lets a test see Q36_MOE_EDEVICE reported with the context intact.
+__global__ void k_wait_timeout(int *status) {
+    Q36_GDS();
+    __shared__ uint64_t bar;
+    __shared__ volatile int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 0xA00, 1024u);
+    __syncthreads();
+}
+int launch_wait_timeout(int *status, cudaStream_t st) {
+    launch_k(k_wait_timeout, dim3(1), dim3(32), 0, st, status);
+    return check_launch();
 }
 
 // ------------------------------------------------------------ main kernel
@@ -351,69 +372,105 @@ static EncodeTiledFn encode_fn() {
     }
     return fn;
 }
-// code plane of n_group experts: [n_group][M][K] 4-bit elements
-int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride) {
+// Encoding a tensor map is host work (a driver call per map, 8 to 11 maps per launch); the engine builds everything
+// that depends only on its buffers once at creation (q36_engine.cu:1467-1512).  The maps of a call depend only on
+// pointers and shapes, which repeat from step to step, so every encode goes through a small per-thread cache.
+struct MapKey {
+    const void *base;
+    uint64_t stride;
+    int kind, a, b, c, d;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && stride == o.stride && kind == o.kind && a == o.a && b == o.b && c == o.c && d == o.d;
+    }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int MAP_CACHE_SLOTS = 2048;   // direct-mapped; a collision just re-encodes
+static MapSlot *map_cache() {
+    static thread_local MapSlot *slots = nullptr;
+    if (!slots) slots = new MapSlot[MAP_CACHE_SLOTS]();
+    return slots;
+}
+static inline uint64_t mix64(uint64_t x) {
+    x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+    return x;
+}
+static int encode_cached(CUtensorMap *m, const MapKey &k, CUtensorMapDataType dt, int rank, const cuuint64_t *dims,
+                         const cuuint64_t *strides, const cuuint32_t *box, CUtensorMapSwizzle sw) {
+    uint64_t h = mix64((uint64_t)(uintptr_t)k.base) ^ mix64(k.stride + 0x9e3779b97f4a7c15ull * (uint64_t)k.kind);
+    h ^= mix64(((uint64_t)(uint32_t)k.a << 32) | (uint32_t)k.b) ^ mix64(((uint64_t)(uint32_t)k.c << 32) | (uint32_t)k.d);
+    MapSlot &slot = map_cache()[h % MAP_CACHE_SLOTS];
+    if (slot.used && slot.key == k) { *m = slot.map; return Q36_MOE_OK; }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return Q36_MOE_ECUDA;
+    const cuuint32_t el[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void *>(k.base), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
+    slot.key = k; slot.map = *m; slot.used = true;
+    return Q36_MOE_OK;
+}
+
+// code plane of n_group experts: [n_group][M][K] 4-bit elements
+int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride) {
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)M, (cuuint64_t)n_group};
     cuuint64_t strides[2] = {(cuuint64_t)(K / 2), (cuuint64_t)expert_stride};
-    cuuint32_t box[3] = {128, TC_M, 1}, el[3] = {1, 1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void *>(base), dims, strides, box, el,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    cuuint32_t box[3] = {128, TC_M, 1};
+    return encode_cached(m, MapKey{base, expert_stride, 1, M, K, n_group, 0}, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, dims,
+                         strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 // A thread needs ~140 cycles to issue any asynchronous copy, whatever its size, so the decode kernel fetches
 // several K steps per copy: the K axis is split into (step, 128 elements) and the step index becomes a box
 // dimension AFTER the rows, which lays the steps down as consecutive [rows][128 B] swizzled tiles.
 int make_map_codes_ksteps(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride, int ksteps) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[4] = {128, (cuuint64_t)M, (cuuint64_t)(K / 128), (cuuint64_t)n_group};
     cuuint64_t strides[3] = {(cuuint64_t)(K / 2), 64, (cuuint64_t)expert_stride};
-    cuuint32_t box[4] = {128, TC_M, (cuuint32_t)ksteps, 1}, el[4] = {1, 1, 1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, const_cast<void *>(base), dims, strides, box, el,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    cuuint32_t box[4] = {128, TC_M, (cuuint32_t)ksteps, 1};
+    return encode_cached(m, MapKey{base, expert_stride, 2, M, K, n_group, ksteps}, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, dims,
+                         strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 int make_map_rows_ksteps(CUtensorMap *m, const void *base, int R, int K, int box_rows, int ksteps) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[3] = {128, (cuuint64_t)R, (cuuint64_t)(K / 128)};
     cuuint64_t strides[2] = {(cuuint64_t)K, 128};
-    cuuint32_t box[3] = {128, (cuuint32_t)box_rows, (cuuint32_t)ksteps}, el[3] = {1, 1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, el,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    cuuint32_t box[3] = {128, (cuuint32_t)box_rows, (cuuint32_t)ksteps};
+    return encode_cached(m, MapKey{base, 0, 3, R, K, box_rows, ksteps}, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
 }
 // activation rows: [R][K] bytes, boxes of box_rows rows x 128 B
 int make_map_rows(CUtensorMap *m, const void *base, int R, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)R};
     cuuint64_t strides[1] = {(cuuint64_t)K};
-    cuuint32_t box[2] = {128, (cuuint32_t)box_rows}, el[2] = {1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, el,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
+    return encode_cached(m, MapKey{base, 0, 4, R, K, box_rows, 0}, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// The multiprocessor count and the kernels' opt-in to more than 48 KB of dynamic shared memory are per DEVICE:
+// a host thread that drives several devices in turn (q36_multi_create / q36_multi_prefill, q36_engine.cu:4234-4306)
+// must find both set for whichever device is current.
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return -1;
+    return dev;
+}
 int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
+    static int n[MAX_DEVICES] = {0};
+    const int dev = current_device();
+    if (dev < 0) return 148;
+    if (!n[dev]) {
+        int v = 0;
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        n[dev] = v > 0 ? v : 148;
     }
-    return n;
+    return n[dev];
+}
+// Once per (kernel, device): allow `bytes` of dynamic shared memory.  done: MAX_DEVICES flags owned by the caller.
+int ensure_smem_attr(const void *kernel, int bytes, bool *done) {
+    const int dev = current_device();
+    if (dev < 0) return Q36_MOE_EINVAL;
+    if (done[dev]) return Q36_MOE_OK;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return check_launch();
+    done[dev] = true;
+    return Q36_MOE_OK;
 }
 
 uint64_t tc_ws_bytes() { return (sizeof(TcPlan) + 255) & ~(uint64_t)255; }
@@ -428,16 +485,11 @@ int launch_tc_plan(const int *goffs, int n_group, const int *soffs, int D, int F
 // scale plane of n_group experts: [n_group][rows][nb] bytes (n_group = 0: a plain [rows][nb] matrix),
 // boxes of 16 B (four K steps) x box_rows rows
 static int make_map_scales(CUtensorMap *m, const void *base, int rows, int nb, int n_group, uint64_t stride3, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return Q36_MOE_ECUDA;
     cuuint64_t dims[3] = {(cuuint64_t)nb, (cuuint64_t)rows, (cuuint64_t)(n_group > 0 ? n_group : 1)};
     cuuint64_t strides[2] = {(cuuint64_t)nb, (cuuint64_t)stride3};
-    cuuint32_t box[3] = {16, (cuuint32_t)box_rows, 1}, el[3] = {1, 1, 1};
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, n_group > 0 ? 3 : 2, const_cast<void *>(base), dims, strides, box, el,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    cuuint32_t box[3] = {16, (cuuint32_t)box_rows, 1};
+    return encode_cached(m, MapKey{base, stride3, 5, rows, nb, n_group, box_rows}, CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                         n_group > 0 ? 3 : 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // A0/A1: routed experts' planes (A1 unused for NA = 1); S0/S1: the shared expert's planes or NULL.
@@ -466,12 +518,8 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     if ((rc = make_map_scales(&maps.fs0, (const uint8_t *)S0 + plane, M, nb, 1, estride, TC_M))) return rc;
     if ((rc = make_map_scales(&maps.fs1, (const uint8_t *)S1 + plane, M, nb, 1, estride, TC_M))) return rc;
     if ((rc = make_map_scales(&maps.fb, Bs, R_max, nb, 0, 0, Cfg::N))) return rc;
-    static bool attr_set = false;   // one per instantiation
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_grouped_mma<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-            return check_launch();
-        attr_set = true;
-    }
+    static bool attr_done[MAX_DEVICES] = {false};   // one array per instantiation
+    if ((rc = ensure_smem_attr((const void *)k_grouped_mma<NA>, Cfg::SMEM_BYTES, attr_done))) return rc;
     const int m_tiles = M / TC_M;
     const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
     const int grid = (int)min((long)sm_count(), max_tiles);

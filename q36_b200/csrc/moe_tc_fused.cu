@@ -18,7 +18,7 @@
 
 namespace q36 {
 
-// What sets the layout (all measured on B200, see ub_tma_rate.cu and ub_mma_issue.cu):
+// What sets the layout (all measured on B200 with single-purpose timing loops around the instruction in question):
 //  * a thread needs ~140 cycles to issue ANY asynchronous copy, so a stage is TWO K steps fetched by two copies
 //    (one 4-bit weight box of 2 x [128 rows][128 elements], one box of 2 x [16 token rows][128 B]);
 //  * a thread gets one block-scaled MMA through per ~90-110 cycles, the pipe takes one per ~40, so FOUR warps
@@ -54,8 +54,9 @@ struct FusedCfg {
     // of a tile are contiguous in the row-major scale planes (128 rows x K/32 bytes).  Loads issued by the
     // loader threads themselves were measured to expose a full HBM latency per 4 K steps (register prefetch
     // does not help: a warp's loads retire through a handful of shared scoreboards).
-    static constexpr int SFT_A = TC_M * 64;          // up to K = 2048: 64 scale bytes per row
-    static constexpr int SFT_B = 16 * 64;
+    static constexpr int K_MAX = 2048;               // largest D or FF this kernel takes (sizes the staged scale bytes)
+    static constexpr int SFT_A = TC_M * (K_MAX / Q36_QK);   // 64 scale bytes per weight row
+    static constexpr int SFT_B = 16 * (K_MAX / Q36_QK);
     static constexpr int SFT_BYTES = 2 * SFT_A + SFT_B;      // 17 KB: gate (or down), up, tokens
     static constexpr int SFT_SLOTS = 2;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFT_SLOTS * SFT_BYTES + 1024 + 256;
@@ -489,6 +490,8 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
 // ceil(c / 16) token tiles, so there are at most R_max / 16 + (non-empty groups) of them.
 bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF) {
     using Cfg = FusedCfg;
+    // the staged scale bytes of a tile are sized for K <= K_MAX; larger layers take the two grouped-GEMM launches
+    if (D > Cfg::K_MAX || FF > Cfg::K_MAX || D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP)) return false;
     const long tt = R_max / Cfg::TILE_ROWS + min(R_max, n_group + 1);
     const long grid = sm_count(), n0 = tt * (FF / TC_M), n1 = tt * (D / TC_M);
     return n_group + 1 <= Cfg::MAX_GROUPS && (n0 + grid - 1) / grid + (n1 + grid - 1) / grid + Cfg::EXTRA_DOWN + 1 <= Cfg::MAX_TILES;
@@ -513,12 +516,8 @@ int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const
     if ((rc = make_map_codes_ksteps(&maps.sd, Sd, D, FF, 1, estride, Cfg::KS))) return rc;
     if ((rc = make_map_rows_ksteps(&maps.x, Xq, R_max, D, 16, Cfg::KS))) return rc;
     if ((rc = make_map_rows_ksteps(&maps.h, Hq, R_max, FF, 16, Cfg::KS))) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_ffn_fused_small, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
-            return check_launch();
-        attr_set = true;
-    }
+    static bool attr_done[MAX_DEVICES] = {false};
+    if ((rc = ensure_smem_attr((const void *)k_ffn_fused_small, Cfg::SMEM_BYTES, attr_done))) return rc;
     const long max_tiles = (long)(R_max + n_group + 1) * (FF / TC_M + D / TC_M);
     const int grid = (int)min((long)sm_count(), max_tiles);
     launch_k(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,

@@ -37,8 +37,9 @@ __device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
 // Bounded wait.  Returns false (and raises *abort_flag) when it gives up or
 // when another role already gave up.
 // `where` identifies the waiter (role * 256 + stage or tile parity) and is what the status word receives.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag, int *status, int where,
+                                          uint32_t limit = TC_SPIN_LIMIT) {
+    for (uint32_t i = 0; i < limit; i++) {
         if (mbar_try(a, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }

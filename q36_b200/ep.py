@@ -166,6 +166,7 @@ class NativeEP:
         ly = layers[0]
         n = int(moe.lib.q36_moe_ep_workspace_bytes(T, world, ly.E, ly.k, ly.D, ly.FF))
         self.ws = torch.empty(n, dtype=torch.uint8, device=dev)
+        moe.check(moe.lib.q36_moe_ws_reset(self.ws.data_ptr(), moe.stream_ptr()), "ws_reset")
 
     def layer(self, ly, X, logits, out):
         m = self.moe

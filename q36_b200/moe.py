@@ -47,11 +47,14 @@ _SIGS = {
     "q36_moe_dispatch_noalloc": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp]),
     "q36_moe_quant_scatter": (i32, [vp, i32, vp, i32, i32, vp, vp, i32, i32, vp]),
     "q36_moe_ffn_ws_bytes": (u64, [i32, i32, i32, i32]),
+    "q36_moe_one_launch_fits": (i32, [i32, i32, i32, i32]),
     "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32,
                                         i32, i32, vp, u64, vp]),
     "q36_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "q36_moe_workspace_bytes": (u64, [i32, i32, i32, i32, i32]),
     "q36_moe_ws_status": (i32, [vp, vp]),
+    "q36_moe_ws_reset": (i32, [vp, vp]),
+    "q36_moe_selftest_wait_timeout": (i32, [vp, vp]),
     "q36_moe_layer": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, vp, vp, i32, i32, vp, u64, vp]),
     "q36_moe_decode": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
     "q36_moe_prefill": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
@@ -166,7 +169,7 @@ def expert_ffn_sorted(Wg, Wu, Wd, n_group: int, goffs: torch.Tensor, Xq: torch.T
     Hq, Hs, Y = bufs
     wsb = int(lib.q36_moe_ffn_ws_bytes(n_group, R, D, FF))
     if ws is None:
-        ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+        ws = torch.zeros(wsb, dtype=torch.uint8, device=dev)
     Sg, Su, Sd = shared if shared is not None else (None, None, None)
     check(lib.q36_moe_expert_ffn_sorted(Wg.data_ptr(), Wu.data_ptr(), Wd.data_ptr(), n_group, goffs.data_ptr(),
                                         ptr(Sg), ptr(Su), ptr(Sd), ptr(soffs), R, Xq.data_ptr(), Xs.data_ptr(),
@@ -257,6 +260,7 @@ class MoELayer:
         if self._ws is None or T > self._ws_T:
             nbytes = int(lib.q36_moe_workspace_bytes(T, self.E, self.k, self.D, self.FF))
             self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            check(lib.q36_moe_ws_reset(self._ws.data_ptr(), stream_ptr()), "ws_reset")
             self._ws_T = T
         return self._ws
 
@@ -280,6 +284,32 @@ class MoELayer:
                                 logits.data_ptr(), stride, shgate_col, route_scale, int(inc_shared), out.data_ptr(),
                                 ptr(idx), ptr(wt), T, path, ws.data_ptr(), ws.numel(), stream_ptr(stream)), "moe_layer")
         return (out, idx, wt) if want_routing else out
+
+    def _by_name(self, fn, name, X, logits, out, shgate_col, route_scale, inc_shared, stream):
+        T = X.shape[0]
+        stride = logits.shape[1]
+        if shgate_col is None:
+            shgate_col = self.E if stride > self.E else -1
+        if out is None:
+            out = torch.empty((T, self.D), dtype=torch.float32, device=X.device)
+        ws = self.workspace(T)
+        check(fn(self.Wg.data_ptr(), self.Wu.data_ptr(), self.Wd.data_ptr(), ptr(self.Sg), ptr(self.Su), ptr(self.Sd),
+                 self.E, self.se0, self.se1, self.k, self.D, self.FF, X.data_ptr(), int(X.dtype == torch.bfloat16),
+                 logits.data_ptr(), stride, shgate_col, route_scale, int(inc_shared), out.data_ptr(), T, ws.data_ptr(),
+                 ws.numel(), stream_ptr(stream)), name)
+        return out
+
+    def decode(self, X, logits, out=None, shgate_col=None, route_scale=1.0, inc_shared=True, stream=None):
+        """q36_moe_decode: the engine's moe_ffn by name (q36_engine.cu:1592-1654)."""
+        return self._by_name(lib.q36_moe_decode, "moe_decode", X, logits, out, shgate_col, route_scale, inc_shared, stream)
+
+    def prefill(self, X, logits, out=None, shgate_col=None, route_scale=1.0, inc_shared=True, stream=None):
+        """q36_moe_prefill: the engine's pf_moe_block by name (q36_engine.cu:3423-3472)."""
+        return self._by_name(lib.q36_moe_prefill, "moe_prefill", X, logits, out, shgate_col, route_scale, inc_shared, stream)
+
+    def reset_device_status(self):
+        if self._ws is not None:
+            check(lib.q36_moe_ws_reset(self._ws.data_ptr(), stream_ptr()), "ws_reset")
 
     def check_device_status(self):
         if self._ws is not None:

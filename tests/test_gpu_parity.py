@@ -273,6 +273,73 @@ def test_decode_paths_agree_and_repeat(moe, oracle, torch_cuda, layer, weights):
     assert rel_l2(g.cpu().numpy(), ref.cpu().numpy()) < 2e-3
 
 
+@pytest.mark.parametrize("T", [1, 8])
+def test_decode_entry_by_name(moe, oracle, torch_cuda, layer, weights, T):
+    """q36_moe_decode (the drop-in for moe_ffn) takes the fastest path: bit-identical to q36_moe_layer with
+    path AUTO, and within tolerance of the oracle."""
+    torch = torch_cuda
+    rng = np.random.default_rng(900 + T)
+    X = synth.activations(rng, T, D)
+    L = synth.router_logits(rng, T, E)
+    xt, lt = torch.from_numpy(X).cuda().to(torch.bfloat16), torch.from_numpy(L).cuda()
+    ref = layer.forward(xt, lt, path=moe.PATH_AUTO).clone()
+    got = layer.decode(xt, lt)
+    torch.cuda.synchronize()
+    layer.check_device_status()
+    assert torch.equal(got, ref)
+    widx, wwt = oracle.router_topk(L, K8, n_expert=E)
+    w = weights
+    want = oracle.moe_layer(w["gate"], w["up"], w["down"], w["sgate"][0], w["sup"][0], w["sdown"][0], D, FF, X, widx, wwt,
+                            L[:, E], tokens=np.arange(T))
+    assert rel_l2(got.cpu().numpy(), want) < TOL
+
+
+def test_prefill_entry_by_name(moe, oracle, torch_cuda, layer, weights):
+    """q36_moe_prefill (the drop-in for pf_moe_block): bit-identical to q36_moe_layer with path AUTO at a
+    prefill-sized call, and within tolerance of the oracle on sampled tokens."""
+    torch = torch_cuda
+    T = 300
+    rng = np.random.default_rng(901)
+    X = synth.activations(rng, T, D)
+    L = synth.router_logits(rng, T, E, zipf=True)
+    xt, lt = torch.from_numpy(X).cuda().to(torch.bfloat16), torch.from_numpy(L).cuda()
+    ref = layer.forward(xt, lt, path=moe.PATH_AUTO).clone()
+    got = layer.prefill(xt, lt)
+    torch.cuda.synchronize()
+    layer.check_device_status()
+    assert torch.equal(got, ref)
+    widx, wwt = oracle.router_topk(L, K8, n_expert=E)
+    toks = rng.choice(T, size=8, replace=False)
+    w = weights
+    want = oracle.moe_layer(w["gate"], w["up"], w["down"], w["sgate"][0], w["sup"][0], w["sdown"][0], D, FF, X, widx, wwt,
+                            L[:, E], tokens=toks)
+    assert rel_l2(got.cpu().numpy()[toks], want) < TOL
+
+
+def test_bounded_wait_gives_up_and_the_status_is_sticky(moe, torch_cuda, layer):
+    """A wait that nothing completes must end by itself: the kernel records where it gave up, returns, and the
+    host reads Q36_MOE_EDEVICE; the context stays usable.  The record survives later launches on the same
+    workspace (they never clear it) until q36_moe_ws_reset."""
+    torch = torch_cuda
+    rng = np.random.default_rng(5)
+    T = 4
+    xt = torch.from_numpy(synth.activations(rng, T, D)).cuda().to(torch.bfloat16)
+    lt = torch.from_numpy(synth.router_logits(rng, T, E)).cuda()
+    ref = layer.forward(xt, lt, path=moe.PATH_TC).clone()
+    layer.check_device_status()                                   # clean so far
+    ws = layer.workspace(T)
+    rc = moe.lib.q36_moe_selftest_wait_timeout(ws.data_ptr(), moe.stream_ptr())
+    assert rc == moe.EDEVICE
+    assert moe.lib.q36_moe_last_cuda_error() == 200000 + 0xA00    # role 0xA, stage 0: the self-test's waiter
+    out = layer.forward(xt, lt, path=moe.PATH_TC)                 # the device still works ...
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
+    with pytest.raises(moe.MoEError):                             # ... and the record is still there
+        layer.check_device_status()
+    layer.reset_device_status()
+    layer.check_device_status()
+
+
 def test_layer_host_buffers_and_f32_input(moe, oracle, torch_cuda, layer, weights):
     torch = torch_cuda
     rng = np.random.default_rng(77)

@@ -44,6 +44,17 @@ def test_noalloc_dispatch_matches_workspace_dispatch_twice(moe):
             assert torch.equal(g, w), f"{name} differs from q36_moe_dispatch (n={n})"
 
 
+def test_noalloc_empty_input(moe):
+    """No entries at all: every expert's count is zero and all offsets are zero, as with q36_moe_dispatch."""
+    import torch
+    eid = torch.zeros(0, dtype=torch.int32, device="cuda")
+    want = moe.dispatch(eid, E, 0, E)
+    got = _noalloc(moe, torch, eid, 0, E)
+    torch.cuda.synchronize()
+    assert torch.equal(got[0], want[0]) and int(got[0].sum()) == 0
+    assert torch.equal(got[1], want[1]) and int(got[1].abs().sum()) == 0
+
+
 def test_noalloc_rejects_sizes_beyond_the_builtin_scratch(moe):
     import torch
     one = torch.zeros(8, dtype=torch.int32, device="cuda")

@@ -48,6 +48,8 @@ extern "C" {
 #define Q36_MOE_ECUDA (-2)    /* a CUDA call failed: q36_moe_last_cuda_error()  */
 #define Q36_MOE_ENOSPACE (-3) /* workspace smaller than q36_moe_workspace_bytes */
 #define Q36_MOE_EDEVICE (-4)  /* a bounded device-side wait gave up             */
+#define Q36_MOE_EUNSUPPORTED (-5) /* well-formed input this path does not take (a tensor type, a shape) */
+#define Q36_MOE_EIO (-6)      /* a file could not be opened, mapped or parsed: q36_gguf_last_error() */
 
 /* Path selection for the grouped expert FFN. */
 #define Q36_MOE_PATH_AUTO 0
@@ -74,6 +76,44 @@ int q36_moe_upload_mxfp4(const void *host_blocks, int K, int M, int e0, int e1, 
  * on-device form of q36_deq_row(Q36_GGML_MXFP4, ...) (q36_dequant.cuh:168-181),
  * used to prove bit-exact dequantisation. */
 int q36_moe_dequant_mxfp4(const void *W, int M, int K, float *out, void *stream);
+
+/* ---- on-disk format in: GGUF ----------------------------------------------
+ * Replaces, for this path, the engine's GGUF v3 reader (gguf.c:129-261), its
+ * tensor binding by name (q36_model.c:62-75) and the MXFP4 branch of upload()
+ * (q36_engine.cu:202-228).  The file is mapped read-only; nothing is copied
+ * until a tensor is repacked for the device.  Messages for Q36_MOE_EIO /
+ * Q36_MOE_EUNSUPPORTED come from q36_gguf_last_error() (per thread). */
+int q36_gguf_open(const char *path, void **gguf_out);
+int q36_gguf_close(void *gguf);
+const char *q36_gguf_last_error(void);
+/* Directory entry of one tensor: ggml type id (q36.h:133-141), dimensions
+ * (fastest first, unused ones 1), pointer into the mapping, bytes on disk.
+ * Any out pointer may be NULL. */
+int q36_gguf_tensor(const void *gguf, const char *name, int *ggml_type, int *n_dims, uint64_t *dims4,
+                    const void **host_data, uint64_t *nbytes);
+/* Integer metadata value (u32/i32/u64/i64 keys such as "general.alignment"). */
+int q36_gguf_meta_u32(const void *gguf, const char *key, uint32_t *out);
+/* Shapes of blk.<layer>.ffn_{gate,up,down}_exps.weight: gate/up [K=D, M=FF, E],
+ * down [K=FF, M=D, E] (q36_model.h:75-77); ggml_types3 (or NULL) receives the
+ * three tensor types. */
+int q36_moe_gguf_layer_shape(const void *gguf, int layer, int *n_expert, int *D, int *FF, int *ggml_types3);
+/* Experts [e0, e1) of the three tensors -> split planes in the caller's
+ * device buffers of (e1-e0)*q36_moe_expert_stride(...) bytes each.  MXFP4
+ * tensors only: the published model's Q5_K / Q6_K down projections
+ * (requantised to Q8 by the engine, q36_engine.cu:229-252) return
+ * Q36_MOE_EUNSUPPORTED.  Synchronous. */
+int q36_moe_gguf_upload_layer(const void *gguf, int layer, int e0, int e1, void *dev_Wg, void *dev_Wu,
+                              void *dev_Wd);
+/* blk.<layer>.ffn_{gate,up,down}_shexp.weight as one-expert split planes;
+ * MXFP4 only (the published model stores them as Q8_0: Q36_MOE_EUNSUPPORTED). */
+int q36_moe_gguf_upload_shared(const void *gguf, int layer, void *dev_Sg, void *dev_Su, void *dev_Sd);
+/* Router rows and the shared-gate row as ONE f32 matrix [n_expert + 1][D], the
+ * concatenation the engine makes at load (q36_engine.cu:1599-1601), from
+ * blk.<layer>.ffn_gate_inp.weight [D, E] and ffn_gate_inp_shexp.weight [D]
+ * (F32 or BF16, widened). */
+int q36_moe_gguf_upload_router(const void *gguf, int layer, float *dev_router);
+/* Any F32 / BF16 tensor of n elements (norm weights) -> f32 on the device. */
+int q36_moe_gguf_upload_f32(const void *gguf, const char *name, float *dev_dst, uint64_t n);
 
 /* ---- stages -------------------------------------------------------------- */
 

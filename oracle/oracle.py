@@ -82,6 +82,11 @@ def ref():
         R.ref_fp16.restype = C.c_float
         R.ref_fp16.argtypes = [C.c_uint16]
         R.ref_sizeof_block_mxfp4.restype = C.c_int
+        if hasattr(R, "ref_gguf_probe"):
+            R.ref_gguf_probe.restype = C.c_int
+            R.ref_gguf_probe.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
+                                         C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
+                                         C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]
         _ref = R
     return _ref
 
@@ -226,3 +231,20 @@ def cpu_expert_seconds(gate, up, down, D, FF, xd, reps: int, threads: int | None
                              _p(scratch, f32p), _p(y, f32p))
         ts.append(time.perf_counter() - t0)
     return float(np.median(ts)), y, kind, nthr
+
+
+def ref_gguf_probe(path: str, name: str):
+    """What the reference's own GGUF reader (gguf.c) reports for tensor `name` of the file at `path`:
+    dict(type, dims, file_offset, nbytes, alignment, n_tensors), or None when oracle/_ref lacks the reader."""
+    R = ref()
+    if R is None or not hasattr(R, "ref_gguf_probe"):
+        return None
+    t, nd, al = C.c_uint32(), C.c_uint32(), C.c_uint32()
+    off, nb, nt = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    dims = (C.c_uint64 * 4)()
+    rc = R.ref_gguf_probe(os.fsencode(path), name.encode(), C.byref(t), C.byref(nd), dims, C.byref(off), C.byref(nb),
+                          C.byref(al), C.byref(nt))
+    if rc != 0:
+        raise KeyError(f"reference reader: rc {rc} for {name}")
+    return {"type": t.value, "dims": tuple(dims[d] for d in range(nd.value)), "file_offset": off.value,
+            "nbytes": nb.value, "alignment": al.value, "n_tensors": nt.value}

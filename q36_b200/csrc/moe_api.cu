@@ -177,6 +177,8 @@ const char *q36_moe_strerror(int s) {
         case Q36_MOE_ECUDA: return "CUDA error (see q36_moe_last_cuda_error)";
         case Q36_MOE_ENOSPACE: return "workspace too small";
         case Q36_MOE_EDEVICE: return "a bounded device-side wait gave up";
+        case Q36_MOE_EUNSUPPORTED: return "input not supported by this path (see q36_gguf_last_error)";
+        case Q36_MOE_EIO: return "file error (see q36_gguf_last_error)";
         default: return "unknown status";
     }
 }

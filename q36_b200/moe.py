@@ -22,7 +22,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libq36moe.so")
 
 PATH_AUTO, PATH_GEMV, PATH_TC = 0, 1, 2
-OK, EINVAL, ECUDA, ENOSPACE, EDEVICE = 0, -1, -2, -3, -4
+OK, EINVAL, ECUDA, ENOSPACE, EDEVICE, EUNSUPPORTED, EIO = 0, -1, -2, -3, -4, -5, -6
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -39,6 +39,16 @@ _SIGS = {
     "q36_moe_expert_stride": (u64, [i32, i32]),
     "q36_moe_repack_mxfp4": (i32, [vp, i32, i32, i32, i32, vp]),
     "q36_moe_upload_mxfp4": (i32, [vp, i32, i32, i32, i32, vp]),
+    "q36_gguf_open": (i32, [C.c_char_p, C.POINTER(vp)]),
+    "q36_gguf_close": (i32, [vp]),
+    "q36_gguf_last_error": (C.c_char_p, []),
+    "q36_gguf_tensor": (i32, [vp, C.c_char_p, C.POINTER(i32), C.POINTER(i32), C.POINTER(u64), C.POINTER(vp), C.POINTER(u64)]),
+    "q36_gguf_meta_u32": (i32, [vp, C.c_char_p, C.POINTER(C.c_uint32)]),
+    "q36_moe_gguf_layer_shape": (i32, [vp, i32, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]),
+    "q36_moe_gguf_upload_layer": (i32, [vp, i32, i32, i32, vp, vp, vp]),
+    "q36_moe_gguf_upload_shared": (i32, [vp, i32, vp, vp, vp]),
+    "q36_moe_gguf_upload_router": (i32, [vp, i32, vp]),
+    "q36_moe_gguf_upload_f32": (i32, [vp, C.c_char_p, vp, u64]),
     "q36_moe_dequant_mxfp4": (i32, [vp, i32, i32, vp, vp]),
     "q36_moe_router_topk": (i32, [vp, i32, i32, vp, vp, f32, i32, i32, i32, vp]),
     "q36_moe_quant_e4m3": (i32, [vp, i32, vp, vp, i32, i32, vp]),
@@ -81,6 +91,8 @@ def check(rc: int, what: str = "") -> None:
     if rc != OK:
         msg = lib.q36_moe_strerror(rc).decode()
         extra = f" (code {lib.q36_moe_last_cuda_error()})" if rc in (ECUDA, EDEVICE) else ""
+        if rc in (EIO, EUNSUPPORTED):
+            extra = f": {lib.q36_gguf_last_error().decode()}"
         raise MoEError(f"{what}: {msg}{extra}")
 
 
@@ -206,6 +218,44 @@ def tc_selftest(A: torch.Tensor, Bq: torch.Tensor, Bs: torch.Tensor, N: int, K: 
     return D
 
 
+class GgufFile:
+    """A GGUF v3 file opened through the library's reader (the role of gguf.c in the engine)."""
+
+    def __init__(self, path: str):
+        self.h = vp()
+        check(lib.q36_gguf_open(os.fsencode(path), C.byref(self.h)), "gguf_open")
+
+    def close(self):
+        if self.h:
+            lib.q36_gguf_close(self.h)
+            self.h = vp()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def tensor(self, name: str):
+        """(ggml type, dims tuple, numpy uint8 view of the bytes in the mapping)."""
+        t, nd, nb, data = i32(), i32(), u64(), vp()
+        dims = (u64 * 4)()
+        check(lib.q36_gguf_tensor(self.h, name.encode(), C.byref(t), C.byref(nd), dims, C.byref(data), C.byref(nb)), "gguf_tensor")
+        buf = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(nb.value,)) if nb.value else np.zeros(0, np.uint8)
+        return t.value, tuple(dims[d] for d in range(nd.value)), buf
+
+    def meta_u32(self, key: str) -> int:
+        v = C.c_uint32()
+        check(lib.q36_gguf_meta_u32(self.h, key.encode(), C.byref(v)), "gguf_meta_u32")
+        return v.value
+
+    def layer_shape(self, layer: int):
+        e, d, ff = i32(), i32(), i32()
+        types = (i32 * 3)()
+        check(lib.q36_moe_gguf_layer_shape(self.h, layer, C.byref(e), C.byref(d), C.byref(ff), types), "gguf_layer_shape")
+        return e.value, d.value, ff.value, tuple(types)
+
+
 class MoELayer:
     """One MoE layer resident on one GPU: routed experts [se0, se1) of n_expert,
     plus (optionally) the shared expert."""
@@ -231,6 +281,24 @@ class MoELayer:
             self.Sg = upload_mxfp4(sgate, D, FF, 0, 1, self.device)
             self.Su = upload_mxfp4(sup, D, FF, 0, 1, self.device)
             self.Sd = upload_mxfp4(sdown, FF, D, 0, 1, self.device)
+        return self
+
+    def load_gguf(self, gguf: "GgufFile", layer: int, shared: bool = True):
+        """Expert planes of block `layer` straight from a GGUF file (MXFP4 tensors); only the shard is uploaded."""
+        E, D, FF, _ = gguf.layer_shape(layer)
+        assert (E, D, FF) == (self.E, self.D, self.FF), f"file has E={E} D={D} FF={FF}"
+        n = self.se1 - self.se0
+        self.Wg = torch.empty(n * expert_stride(FF, D), dtype=torch.uint8, device=self.device)
+        self.Wu = torch.empty_like(self.Wg)
+        self.Wd = torch.empty(n * expert_stride(D, FF), dtype=torch.uint8, device=self.device)
+        check(lib.q36_moe_gguf_upload_layer(gguf.h, layer, self.se0, self.se1, self.Wg.data_ptr(), self.Wu.data_ptr(),
+                                            self.Wd.data_ptr()), "gguf_upload_layer")
+        if shared:
+            self.Sg = torch.empty(expert_stride(FF, D), dtype=torch.uint8, device=self.device)
+            self.Su = torch.empty_like(self.Sg)
+            self.Sd = torch.empty(expert_stride(D, FF), dtype=torch.uint8, device=self.device)
+            check(lib.q36_moe_gguf_upload_shared(gguf.h, layer, self.Sg.data_ptr(), self.Su.data_ptr(), self.Sd.data_ptr()),
+                  "gguf_upload_shared")
         return self
 
     def set_device_planes(self, Wg, Wu, Wd, Sg=None, Su=None, Sd=None):

@@ -59,3 +59,78 @@ def layer(seed: int, n_expert: int = N_EXPERT, D: int = D_MODEL, FF: int = EXPER
         "sup": mxfp4_blocks(rng, 1, FF, D),
         "sdown": mxfp4_blocks(rng, 1, D, FF),
     }
+
+
+# ---------------------------------------------------------------- GGUF out
+# ggml tensor type ids used by the engine's model file (q36.h:133-141)
+GGML_F32, GGML_BF16, GGML_Q8_0, GGML_MXFP4 = 0, 30, 8, 39
+
+
+def write_gguf(path: str, tensors: dict, meta: dict | None = None, alignment: int = 32) -> None:
+    """Writes a GGUF v3 file.  tensors: name -> (ggml_type, dims fastest-first, bytes-like data).
+    meta: key -> int | float | str | list of int | list of str (written as u32 / f32 / string / arrays).
+    Layout as the engine's reader expects it (gguf.c:129-190): header, metadata, tensor directory, padding to
+    `general.alignment`, then each tensor's data at its aligned offset."""
+    import struct
+
+    def s(x: str) -> bytes:
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    meta = dict(meta or {})
+    meta.setdefault("general.alignment", alignment)
+    out = [b"GGUF", struct.pack("<IQQ", 3, len(tensors), len(meta))]
+    for k, v in meta.items():
+        out.append(s(k))
+        if isinstance(v, bool):
+            out.append(struct.pack("<IB", 7, int(v)))
+        elif isinstance(v, int):
+            out.append(struct.pack("<II", 4, v))
+        elif isinstance(v, float):
+            out.append(struct.pack("<If", 6, v))
+        elif isinstance(v, str):
+            out.append(struct.pack("<I", 8) + s(v))
+        elif isinstance(v, (list, tuple)) and v and isinstance(v[0], str):
+            out.append(struct.pack("<IIQ", 9, 8, len(v)) + b"".join(s(x) for x in v))
+        elif isinstance(v, (list, tuple)):
+            out.append(struct.pack("<IIQ", 9, 5, len(v)) + b"".join(struct.pack("<i", x) for x in v))
+        else:
+            raise TypeError(f"metadata value of {k}")
+    off = 0
+    blobs = []
+    for name, (typ, dims, data) in tensors.items():
+        data = bytes(data)
+        out.append(s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) +
+                   struct.pack("<IQ", typ, off))
+        pad = (-len(data)) % alignment
+        blobs.append(data + b"\0" * pad)
+        off += len(data) + pad
+    head = b"".join(out)
+    head += b"\0" * ((-len(head)) % alignment)
+    with open(path, "wb") as f:
+        f.write(head)
+        for b in blobs:
+            f.write(b)
+
+
+def layer_tensors(w: dict, layer: int, router: np.ndarray | None = None, shared_gate: np.ndarray | None = None,
+                  post_norm: np.ndarray | None = None) -> dict:
+    """The tensors of one MoE block under the engine's names (q36_model.c:62-75) from `layer()`'s dict.
+    GGUF dims are fastest-first: expert tensors [K, M, E], router [D, E]."""
+    E, FF, nb, _ = w["gate"].shape
+    D = nb * 32
+    t = {
+        f"blk.{layer}.ffn_gate_exps.weight": (GGML_MXFP4, (D, FF, E), w["gate"].tobytes()),
+        f"blk.{layer}.ffn_up_exps.weight": (GGML_MXFP4, (D, FF, E), w["up"].tobytes()),
+        f"blk.{layer}.ffn_down_exps.weight": (GGML_MXFP4, (FF, D, E), w["down"].tobytes()),
+        f"blk.{layer}.ffn_gate_shexp.weight": (GGML_MXFP4, (D, FF), w["sgate"].tobytes()),
+        f"blk.{layer}.ffn_up_shexp.weight": (GGML_MXFP4, (D, FF), w["sup"].tobytes()),
+        f"blk.{layer}.ffn_down_shexp.weight": (GGML_MXFP4, (FF, D), w["sdown"].tobytes()),
+    }
+    if router is not None:
+        t[f"blk.{layer}.ffn_gate_inp.weight"] = (GGML_F32, (D, E), np.ascontiguousarray(router, np.float32).tobytes())
+    if shared_gate is not None:
+        t[f"blk.{layer}.ffn_gate_inp_shexp.weight"] = (GGML_F32, (D,), np.ascontiguousarray(shared_gate, np.float32).tobytes())
+    if post_norm is not None:
+        t[f"blk.{layer}.post_attention_norm.weight"] = (GGML_F32, (D,), np.ascontiguousarray(post_norm, np.float32).tobytes())
+    return t

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared():
     txt = open(os.path.join(ROOT, "include", "q36_moe.h")).read()
     txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
-    return sorted(set(re.findall(r"\b(q36_moe_\w+)\s*\(", txt)))
+    return sorted(set(re.findall(r"\b(q36_(?:moe|gguf)_\w+)\s*\(", txt)))
 
 
 def test_every_declared_symbol_is_exported(moe):

@@ -353,6 +353,34 @@ def test_layer_host_buffers_and_f32_input(moe, oracle, torch_cuda, layer, weight
     np.testing.assert_array_equal(ho.numpy(), ref)       # same kernels, same order: bit-identical
 
 
+def test_layer_loaded_from_a_gguf_file(moe, oracle, torch_cuda, weights, tmp_path):
+    """On-disk format in: blk.N.ffn_*_exps.weight of a GGUF v3 file -> split planes on the device through the
+    library's reader; the layer built that way gives the bits of the layer built from the same blocks in memory,
+    on a shard, and the router matrix arrives as the engine's [E + 1][D] concatenation."""
+    torch = torch_cuda
+    rng = np.random.default_rng(41)
+    w = weights
+    router = rng.standard_normal((E, D), dtype=np.float32)
+    sgate = rng.standard_normal(D, dtype=np.float32)
+    path = str(tmp_path / "block7.gguf")
+    synth.write_gguf(path, synth.layer_tensors(w, 7, router=router, shared_gate=sgate))
+    T = 6
+    xt = torch.from_numpy(synth.activations(rng, T, D)).cuda().to(torch.bfloat16)
+    lt = torch.from_numpy(synth.router_logits(rng, T, E)).cuda()
+    with moe.GgufFile(path) as g:
+        assert g.layer_shape(7) == (E, D, FF, (39, 39, 39))
+        for se0, se1 in ((0, E), (64, 192)):
+            a = moe.MoELayer(se0=se0, se1=se1).load_gguf(g, 7)
+            b = moe.MoELayer(se0=se0, se1=se1).load_gguf_blocks(w["gate"], w["up"], w["down"], w["sgate"], w["sup"], w["sdown"])
+            for pa, pb in ((a.Wg, b.Wg), (a.Wu, b.Wu), (a.Wd, b.Wd), (a.Sg, b.Sg), (a.Su, b.Su), (a.Sd, b.Sd)):
+                assert torch.equal(pa, pb)
+            assert torch.equal(a.forward(xt, lt, path=moe.PATH_TC), b.forward(xt, lt, path=moe.PATH_TC))
+            a.check_device_status()
+        rt = torch.empty((E + 1, D), dtype=torch.float32, device="cuda")
+        moe.check(moe.lib.q36_moe_gguf_upload_router(g.h, 7, rt.data_ptr()), "gguf_upload_router")
+        np.testing.assert_array_equal(rt.cpu().numpy(), np.concatenate([router, sgate[None]], 0))
+
+
 def test_shard_contract(moe, oracle, torch_cuda, weights):
     """Experts outside [se0,se1) contribute zeros; shards sum to the whole; only the owner adds the shared expert
     (q36_engine.cu:763-766, 3398-3400, 4245-4248)."""

@@ -270,6 +270,42 @@ int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *
                     int shgate_col, float route_scale, int inc_shared, float *out, int T, void *ws,
                     uint64_t ws_bytes, void *stream);
 
+/* ---- the block from the residual stream -----------------------------------
+ * The steps the engine runs either side of moe_ffn / pf_moe_block, so that a
+ * caller can hand over the residual stream instead of pre-made logits.
+ *
+ * Before (k_add_rmsnorm, q36_engine.cu:696-706,1962, + k_matvec_f32_row,
+ * q36_ops.cuh:331-342, at decode; k_rmsnorm_b + pf_gemm, q36_engine.cu:3426-3427,
+ * 3469, when batched):
+ *   h [T][D] f32 += a   (a == NULL: no add, as in the batched path)
+ *   x [T][D] f32  = h * rsqrt(mean(h^2) + eps) * norm_w
+ *   logits[t][r]  = router_w[r][:] . x[t][:]   for r < n_rows
+ * router_w is [n_rows][D] f32; gate_row (n_rows - 1 or -1) names the
+ * shared-gate row of the engine's concatenated router (q36_engine.cu:1599-1601).
+ * f32 dot products at every T (the engine's batched path rounds to fp16). */
+int q36_moe_pre_norm_router(float *h, const float *a, const float *norm_w, float eps, const float *router_w,
+                            int n_rows, int gate_row, float *x, float *logits, int logit_stride, int T,
+                            int D, void *stream);
+/* After (k_moe_combine(_pf) + k_add_rmsnorm, q36_engine.cu:785-791,3393-3401,
+ * 696-706,1966) as one launch: moe = q36_moe_combine(...) (written to moe_out
+ * when not NULL), h += moe, x_next = rmsnorm(h) * next_norm_w.  D <= 4096. */
+int q36_moe_combine_add_rmsnorm(float *moe_out, const float *Y_rows, const int *pos, const float *wt,
+                                const float *SH_rows, const float *shgate, int shgate_stride, float *h,
+                                const float *next_norm_w, float eps, float *x_next, int D, int k, int T,
+                                void *stream);
+/* One MoE block of the decode / prefill loop (q36_engine.cu:1962-1966) from
+ * the residual stream: the step before, the layer (path AUTO; router_w has
+ * n_expert + 1 rows, the last one the shared gate), the step after.
+ * h [T][D] in/out; a [T][D] or NULL; x_next [T][D] out; moe_out or NULL.
+ * ws: q36_moe_block_workspace_bytes(...) bytes (status words first, as for
+ * q36_moe_layer). */
+uint64_t q36_moe_block_workspace_bytes(int T_max, int n_expert, int k, int D, int FF);
+int q36_moe_block(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                  const void *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
+                  const float *post_norm_w, const float *router_w, const float *next_norm_w, float eps,
+                  float route_scale, int inc_shared, float *h, const float *a, float *x_next, float *moe_out,
+                  int T, void *ws, uint64_t ws_bytes, void *stream);
+
 /* Host-buffer form of q36_moe_layer: X, logits and out are HOST pointers
  * (pinned or pageable); the call copies in, runs the layer and copies out on
  * `stream`, then synchronises it.  dev_io: device staging of

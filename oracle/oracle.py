@@ -205,6 +205,20 @@ def moe_layer(Wg, Wu, Wd, Sg, Su, Sd, D, FF, X, idx, wt, shg, tokens=None,
 
 
 # ------------------------------------------------------------- CPU baseline
+def add_rmsnorm(h: np.ndarray, a: np.ndarray | None, w: np.ndarray, eps: float):
+    """k_add_rmsnorm (q36_engine.cu:696-706) / k_rmsnorm_b (:3230-3240) per row: h += a (f32), then
+    y = h * rsqrt(mean(h^2) + eps) * w, the reduction in float64.  Returns (h_new f32, y f64)."""
+    hn = np.asarray(h, np.float32) if a is None else (np.asarray(h, np.float32) + np.asarray(a, np.float32))
+    h64 = hn.astype(np.float64)
+    ss = 1.0 / np.sqrt((h64 * h64).mean(axis=-1, keepdims=True) + float(eps))
+    return hn, h64 * ss * np.asarray(w, np.float64)
+
+
+def router_logits(x: np.ndarray, router_w: np.ndarray) -> np.ndarray:
+    """k_matvec_f32_row (q36_ops.cuh:331-342) over the concatenated router [n_rows][D]: float64 dot products."""
+    return np.asarray(x, np.float64) @ np.asarray(router_w, np.float64).T
+
+
 def cpu_expert_seconds(gate, up, down, D, FF, xd, reps: int, threads: int | None = None,
                        use_ref: bool = True):
     """Times `reps` runs of the reference's CPU path for one (token, expert)

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq36moe.so")
-SOURCES = ["moe_api.cu", "moe_route.cu", "moe_gemv.cu", "moe_tc.cu", "moe_tc_fused.cu", "moe_ep.cu", "moe_gguf.cu"]
+SOURCES = ["moe_api.cu", "moe_route.cu", "moe_gemv.cu", "moe_tc.cu", "moe_tc_fused.cu", "moe_ep.cu", "moe_gguf.cu", "moe_block.cu"]
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--shared", "-cudart", "shared", "-ldl",

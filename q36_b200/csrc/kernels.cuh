@@ -49,6 +49,15 @@ int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows,
                        cudaStream_t st);
 int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st);
 
+// moe_block.cu: the steps before and after the expert computation
+// h += a (a may be NULL); x = rmsnorm(h) * norm_w; logits[:, 0:n_rows) = router_w . x.  gate_row: index of the
+// shared-gate row inside router_w (must be the last row, n_rows - 1) or -1.
+int launch_pre_norm_router(float *h, const float *a, const float *norm_w, float eps, const float *router_w, int n_rows,
+                           int gate_row, float *x, float *logits, int logit_stride, int T, int D, cudaStream_t st);
+int launch_combine_add_rmsnorm(float *moe_out, const float *Y, const int *pos, const float *wt, const float *SH,
+                               const float *shgate, int shgate_stride, float *h, const float *w_next, float eps, float *x_next,
+                               int D, int k, int T, bool early_meta, cudaStream_t st);
+
 // moe_tc.cu
 // One plan per grouped-FFN call (groups = n_group routed + the shared expert's when soffs != NULL), then the
 // gate/up and the down launch read it.  status: 4 ints, [0] gate/up, [1] down.

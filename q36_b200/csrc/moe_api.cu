@@ -88,12 +88,16 @@ static int pick_path(int path, int T) {
     return Q36_MOE_PATH_TC;
 }
 
+// What follows the combine when the caller drives the block from the residual stream: h += moe, then the next
+// RMSNorm (q36_engine.cu:1966).  h == nullptr: the layer ends at the combine.
+struct PostNorm { float *h; const float *w_next; float eps; float *x_next; };
+
 static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                       const void *Sd, int E, int se0, int se1, int k, int D, int FF, const void *X,
                       int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
                       float route_scale, int inc_shared, float *out, int *idx_out, float *wt_out, int T,
-                      int path, void *ws, uint64_t ws_bytes, cudaStream_t st) {
-    if (!Wg || !Wu || !Wd || !X || !logits || !out || !ws) return Q36_MOE_EINVAL;
+                      int path, void *ws, uint64_t ws_bytes, cudaStream_t st, PostNorm post = PostNorm{nullptr, nullptr, 0.f, nullptr}) {
+    if (!Wg || !Wu || !Wd || !X || !logits || (!out && !post.h) || !ws) return Q36_MOE_EINVAL;
     if (T <= 0 || k <= 0 || k > 8 || E <= 0 || E > DISPATCH_MAX_GROUPS || se0 < 0 || se1 > E || se0 >= se1)
         return Q36_MOE_EINVAL;
     if (D % 128 || FF % 128 || logit_stride < E) return Q36_MOE_EINVAL;
@@ -156,8 +160,12 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
     // (behind the decode kernel the combine may read the routing results before its grid dependency resolves:
     // that kernel lets its successor start only after it has seen the front end complete)
-    if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
-                             T, decode_kernel, st)))
+    if (post.h) {
+        if ((rc = launch_combine_add_rmsnorm(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride,
+                                             post.h, post.w_next, post.eps, post.x_next, D, k, T, decode_kernel, st)))
+            return rc;
+    } else if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
+                                    T, decode_kernel, st)))
         return rc;
     if (idx_out && (rc = ck(cudaMemcpyAsync(idx_out, w.idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
     if (wt_out && (rc = ck(cudaMemcpyAsync(wt_out, w.wt, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
@@ -352,6 +360,45 @@ int q36_moe_prefill(const void *Wg, const void *Wu, const void *Wd, const void *
     return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, X, x_is_bf16, logits, logit_stride,
                       shgate_col, route_scale, inc_shared, out, nullptr, nullptr, T, Q36_MOE_PATH_AUTO, ws, ws_bytes,
                       (cudaStream_t)stream);
+}
+
+int q36_moe_pre_norm_router(float *h, const float *a, const float *norm_w, float eps, const float *router_w, int n_rows,
+                            int gate_row, float *x, float *logits, int logit_stride, int T, int D, void *stream) {
+    if (!h || !norm_w || !router_w || !x || !logits || T < 0) return Q36_MOE_EINVAL;
+    return launch_pre_norm_router(h, a, norm_w, eps, router_w, n_rows, gate_row, x, logits, logit_stride, T, D, (cudaStream_t)stream);
+}
+
+int q36_moe_combine_add_rmsnorm(float *moe_out, const float *Y_rows, const int *pos, const float *wt, const float *SH_rows,
+                                const float *shgate, int shgate_stride, float *h, const float *next_norm_w, float eps,
+                                float *x_next, int D, int k, int T, void *stream) {
+    if (!Y_rows || !pos || !wt || !h || !next_norm_w || !x_next || T < 0) return Q36_MOE_EINVAL;
+    return launch_combine_add_rmsnorm(moe_out, Y_rows, pos, wt, SH_rows, shgate, shgate_stride, h, next_norm_w, eps, x_next, D, k, T,
+                                      false, (cudaStream_t)stream);
+}
+
+// block workspace = [layer workspace][x: T*D f32][logits: T*(E+1) f32]
+uint64_t q36_moe_block_workspace_bytes(int T_max, int n_expert, int k, int D, int FF) {
+    const uint64_t base = q36_moe_workspace_bytes(T_max, n_expert, k, D, FF);
+    if (!base) return 0;
+    return base + al((uint64_t)T_max * D * 4) + al((uint64_t)T_max * (n_expert + 1) * 4);
+}
+
+int q36_moe_block(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su, const void *Sd, int n_expert,
+                  int se0, int se1, int k, int D, int FF, const float *post_norm_w, const float *router_w,
+                  const float *next_norm_w, float eps, float route_scale, int inc_shared, float *h, const float *a,
+                  float *x_next, float *moe_out, int T, void *ws, uint64_t ws_bytes, void *stream) {
+    if (!post_norm_w || !router_w || !next_norm_w || !h || !x_next || !ws || T <= 0 || n_expert <= 0 || k <= 0) return Q36_MOE_EINVAL;
+    const uint64_t base = q36_moe_workspace_bytes(T, n_expert, k, D, FF);
+    if (!base) return Q36_MOE_EINVAL;
+    if (q36_moe_block_workspace_bytes(T, n_expert, k, D, FF) > ws_bytes) return Q36_MOE_ENOSPACE;
+    float *x = (float *)((uint8_t *)ws + base);
+    float *logits = (float *)((uint8_t *)x + al((uint64_t)T * D * 4));
+    const int stride = n_expert + 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    if ((rc = launch_pre_norm_router(h, a, post_norm_w, eps, router_w, stride, n_expert, x, logits, stride, T, D, st))) return rc;
+    return layer_impl(Wg, Wu, Wd, Sg, Su, Sd, n_expert, se0, se1, k, D, FF, x, 0, logits, stride, n_expert, route_scale, inc_shared,
+                      moe_out, nullptr, nullptr, T, Q36_MOE_PATH_AUTO, ws, base, st, PostNorm{h, next_norm_w, eps, x_next});
 }
 
 uint64_t q36_moe_host_io_bytes(int T, int D, int logit_stride, int x_is_bf16) {

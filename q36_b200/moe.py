@@ -68,6 +68,10 @@ _SIGS = {
     "q36_moe_layer": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, vp, vp, i32, i32, vp, u64, vp]),
     "q36_moe_decode": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
     "q36_moe_prefill": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, vp, u64, vp]),
+    "q36_moe_pre_norm_router": (i32, [vp, vp, vp, f32, vp, i32, i32, vp, vp, i32, i32, i32, vp]),
+    "q36_moe_combine_add_rmsnorm": (i32, [vp, vp, vp, vp, vp, vp, i32, vp, vp, f32, vp, i32, i32, i32, vp]),
+    "q36_moe_block_workspace_bytes": (u64, [i32, i32, i32, i32, i32]),
+    "q36_moe_block": (i32, [vp] * 6 + [i32] * 6 + [vp, vp, vp, f32, f32, i32, vp, vp, vp, vp, i32, vp, u64, vp]),
     "q36_moe_host_io_bytes": (u64, [i32, i32, i32, i32]),
     "q36_moe_layer_host": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, i32, vp, vp, u64, vp]),
     "q36_moe_gather_rows": (i32, [vp, vp, vp, i32, i32, vp]),
@@ -197,6 +201,28 @@ def combine(Y, pos, wt, SH, shgate, shgate_stride: int, D: int, k: int, T: int):
     check(lib.q36_moe_combine(out.data_ptr(), Y.data_ptr(), pos.data_ptr(), wt.data_ptr(), ptr(SH), ptr(shgate),
                               shgate_stride, D, k, T, stream_ptr()), "combine")
     return out
+
+
+def pre_norm_router(h, a, norm_w, router_w, eps=1e-6, gate_row=None):
+    """h [T,D] f32 (updated in place when a is given) -> (x [T,D], logits [T, n_rows])."""
+    T, D = h.shape
+    n_rows = router_w.shape[0]
+    x = torch.empty_like(h)
+    logits = torch.empty((T, n_rows), dtype=torch.float32, device=h.device)
+    check(lib.q36_moe_pre_norm_router(h.data_ptr(), ptr(a), norm_w.data_ptr(), eps, router_w.data_ptr(), n_rows,
+                                      -1 if gate_row is None else gate_row, x.data_ptr(), logits.data_ptr(), n_rows, T, D,
+                                      stream_ptr()), "pre_norm_router")
+    return x, logits
+
+
+def combine_add_rmsnorm(Y, pos, wt, SH, shgate, shgate_stride, h, next_norm_w, eps, D, k, T):
+    """Returns (moe [T,D], x_next [T,D]); h is updated in place."""
+    moe_out = torch.empty((T, D), dtype=torch.float32, device=Y.device)
+    x_next = torch.empty((T, D), dtype=torch.float32, device=Y.device)
+    check(lib.q36_moe_combine_add_rmsnorm(moe_out.data_ptr(), Y.data_ptr(), pos.data_ptr(), wt.data_ptr(), ptr(SH),
+                                          ptr(shgate), shgate_stride, h.data_ptr(), next_norm_w.data_ptr(), eps,
+                                          x_next.data_ptr(), D, k, T, stream_ptr()), "combine_add_rmsnorm")
+    return moe_out, x_next
 
 
 def gather_rows(src: torch.Tensor, index: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
@@ -374,6 +400,24 @@ class MoELayer:
     def prefill(self, X, logits, out=None, shgate_col=None, route_scale=1.0, inc_shared=True, stream=None):
         """q36_moe_prefill: the engine's pf_moe_block by name (q36_engine.cu:3423-3472)."""
         return self._by_name(lib.q36_moe_prefill, "moe_prefill", X, logits, out, shgate_col, route_scale, inc_shared, stream)
+
+    def block(self, h, a, post_norm_w, router_w, next_norm_w, eps=1e-6, route_scale=1.0, inc_shared=True, stream=None):
+        """q36_moe_block: the block from the residual stream.  h [T,D] f32 is updated in place; returns
+        (x_next [T,D], moe [T,D])."""
+        T = h.shape[0]
+        need = int(lib.q36_moe_block_workspace_bytes(T, self.E, self.k, self.D, self.FF))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+            check(lib.q36_moe_ws_reset(self._ws.data_ptr(), stream_ptr()), "ws_reset")
+            self._ws_T = T
+        x_next = torch.empty((T, self.D), dtype=torch.float32, device=h.device)
+        moe_out = torch.empty((T, self.D), dtype=torch.float32, device=h.device)
+        check(lib.q36_moe_block(self.Wg.data_ptr(), self.Wu.data_ptr(), self.Wd.data_ptr(), ptr(self.Sg), ptr(self.Su),
+                                ptr(self.Sd), self.E, self.se0, self.se1, self.k, self.D, self.FF, post_norm_w.data_ptr(),
+                                router_w.data_ptr(), next_norm_w.data_ptr(), eps, route_scale, int(inc_shared), h.data_ptr(),
+                                ptr(a), x_next.data_ptr(), moe_out.data_ptr(), T, self._ws.data_ptr(), self._ws.numel(),
+                                stream_ptr(stream)), "moe_block")
+        return x_next, moe_out
 
     def reset_device_status(self):
         if self._ws is not None:

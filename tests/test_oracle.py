@@ -166,3 +166,17 @@ def test_linearity_of_down_stage(oracle):
     s0 = oracle.moe_layer(w["gate"], w["up"], w["down"], None, None, None, D, FF, X, idx, wt, None, se0=0, se1=1, inc_shared=False)
     s1 = oracle.moe_layer(w["gate"], w["up"], w["down"], None, None, None, D, FF, X, idx, wt, None, se0=1, se1=2, inc_shared=False)
     np.testing.assert_allclose(s0 + s1, a, rtol=1e-12)
+
+
+def test_add_rmsnorm_and_router_logits_restatement(oracle):
+    """The oracle's restatement of k_add_rmsnorm / k_matvec_f32_row on a case small enough to check by hand."""
+    h = np.array([[3.0, 4.0, 0.0, 0.0]], np.float32)
+    a = np.array([[0.0, 0.0, 0.0, 0.0]], np.float32)
+    w = np.array([1.0, 2.0, 1.0, 1.0], np.float32)
+    hn, y = oracle.add_rmsnorm(h, a, w, 0.0)
+    np.testing.assert_array_equal(hn, h)
+    np.testing.assert_allclose(y, [[3 / 2.5, 2 * 4 / 2.5, 0, 0]], rtol=1e-12)       # mean(h^2) = 25/4
+    hn2, _ = oracle.add_rmsnorm(h, np.ones_like(h), w, 1e-6)
+    np.testing.assert_array_equal(hn2, h + 1)
+    W = np.array([[1, 0, 0, 0], [1, 1, 1, 1]], np.float32)
+    np.testing.assert_allclose(oracle.router_logits(y, W), [[1.2, 1.2 + 3.2]], rtol=1e-12)

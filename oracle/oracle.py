@@ -17,6 +17,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = os.path.join(_HERE, "_build", "libq36oracle.so")
 _REF = os.path.join(_HERE, "_ref", "libq36ref.so")
+_REF_GPU = os.path.join(_HERE, "_ref", "libq36ref_gpu.so")
 
 u8p = C.POINTER(C.c_uint8)
 f32p = C.POINTER(C.c_float)
@@ -33,6 +34,8 @@ def build(force: bool = False) -> None:
     ref_dir = reference_dir()
     if ref_dir and (force or not os.path.exists(_REF)):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref_dir}"])
+    if ref_dir and (force or not os.path.exists(_REF_GPU)):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref_gpu", f"REF={ref_dir}"])
 
 
 def reference_dir() -> str | None:
@@ -262,3 +265,27 @@ def ref_gguf_probe(path: str, name: str):
         raise KeyError(f"reference reader: rc {rc} for {name}")
     return {"type": t.value, "dims": tuple(dims[d] for d in range(nd.value)), "file_offset": off.value,
             "nbytes": nb.value, "alignment": al.value, "n_tensors": nt.value}
+
+
+_ref_gpu = None
+
+
+def ref_gpu():
+    """The reference's own device kernels compiled for sm_100a (oracle/_ref/libq36ref_gpu.so), or None when that
+    file was never built.  Every function takes raw device pointers, runs on the legacy default stream,
+    synchronises the device and returns the CUDA error code (0 = ok)."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        if not os.path.exists(_REF_GPU):
+            return None
+        G = C.CDLL(_REF_GPU)
+        vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+        G.ref_gpu_router_topk.argtypes = [vp, i32, i32, vp, vp, f32, i32, i32, i32]
+        G.ref_gpu_silu_mul.argtypes = [vp, vp, i32]
+        G.ref_gpu_rmsnorm.argtypes = [vp, vp, vp, i32, f32]
+        G.ref_gpu_matvec_f32_row.argtypes = [vp, vp, vp, i32, i32]
+        G.ref_gpu_dot_mxfp4_split.argtypes = [vp, vp, vp, i32, i32, i32]
+        for fn in (G.ref_gpu_router_topk, G.ref_gpu_silu_mul, G.ref_gpu_rmsnorm, G.ref_gpu_matvec_f32_row, G.ref_gpu_dot_mxfp4_split):
+            fn.restype = i32
+        _ref_gpu = G
+    return _ref_gpu

@@ -324,24 +324,48 @@ int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const voi
 int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
                         void *stream);
 
-/* Native expert-parallel layer step (the role of q36_multi_prefill, q36_engine.cu:4261-4306, with the
- * reference's gather + sum + broadcast through device 0 replaced by two all-to-alls of routed rows).
- * One process per GPU; rank r owns experts [r*n_expert/world, (r+1)*n_expert/world) and passes ITS shard's
- * planes as Wg/Wu/Wd; the shared expert (Sg/Su/Sd, may be NULL) is replicated and runs on the rank's own
- * tokens.  NCCL is looked up at run time (libnccl.so.2); without it these calls return Q36_MOE_EINVAL.
- *   q36_moe_ep_unique_id  rank 0 fills 128 bytes that the caller distributes to every rank
- *   q36_moe_ep_init       collective; returns an opaque communicator
- *   q36_moe_ep_layer      launch-only: X [T][D], logits [T][stride] of this rank's T tokens -> out [T][D];
- *                         the exchange uses a fixed capacity of T*k rows per peer, so no count reaches the host
- *   ws: q36_moe_ep_workspace_bytes(...) bytes; its first 256 bytes are the status words (q36_moe_ws_reset, q36_moe_ws_status). */
+/* Expert-parallel layer step: the role of q36_multi_create / q36_multi_prefill (q36_engine.cu:4234-4306), with
+ * the reference's gather + sum + broadcast through device 0 replaced by a dispatch and a combine that the
+ * library's own kernels write straight into the destination rank's memory over NVLink.  Rank r owns experts
+ * [r*n_expert/world, (r+1)*n_expert/world) (q36_engine.cu:4245) and passes ITS shard's planes as Wg/Wu/Wd; the
+ * shared expert (Sg/Su/Sd, may be NULL) is replicated and runs on the rank's own tokens.
+ *
+ * Two ways to form the ranks:
+ *   q36_moe_ep_unique_id + q36_moe_ep_init   one process per GPU; NCCL (looked up at run time, libnccl.so.2)
+ *                          carries the bootstrap.  rank 0 fills 128 bytes that the caller gives to every rank.
+ *   q36_moe_ep_init_local  one process, `world` ranks on the listed devices, as the engine's own driver runs
+ *                          them from one host thread; a device may be listed several times (its ranks then take
+ *                          turns on it, which is how a single GPU exercises the 2/4/8-rank data path).
+ * q36_moe_ep_open_window (collective over the ranks of a process group; for local ranks one call on any of them
+ * opens all) allocates each rank's exchange window for calls of at most T_max tokens per rank and maps the
+ * others' windows (CUDA IPC, or peer access for local ranks).  cap_rows: rows one rank may send to one other rank
+ * per call; 0 = T_max*k, which can never overflow; a smaller cap drops the rows beyond it and records 0xD00 in
+ * the status words.  Not launch-only: it allocates and synchronises; the layer calls below allocate nothing.
+ *
+ * q36_moe_ep_layer is launch-only: X [T][D], logits [T][stride] of this rank's T tokens -> out [T][D].
+ * q36_moe_ep_layer_phase issues one of its three phases (0 route + send, 1 expert work + return, 2 combine): a
+ * host thread that drives several local ranks must issue phase p for EVERY rank before phase p + 1 of any, and a
+ * caller may put phase 0 of the next call's tokens on another stream to overlap it with phase 1 of this one.
+ * Every cross-rank wait is bounded and reports through the status words (0xB00 + source, 0xC00 + source).
+ * ws: q36_moe_ep_workspace_bytes(...) bytes with the T_max / cap_rows the window was opened with; its first 256
+ * bytes are the status words (q36_moe_ws_reset, q36_moe_ws_status).
+ * q36_moe_ep_set_transport: 0 = peer memory (default), 1 = the same kernels over local staging buffers moved
+ * by grouped ncclSend/ncclRecv (process-per-GPU ranks only), kept for comparison. */
 int q36_moe_ep_unique_id(void *out128);
 int q36_moe_ep_init(const void *id128, int rank, int world, void **comm_out);
-int q36_moe_ep_destroy(void *comm);
-uint64_t q36_moe_ep_workspace_bytes(int T, int world, int n_expert, int k, int D, int FF);
+int q36_moe_ep_init_local(int world, const int *devices, void **comms_out);
+int q36_moe_ep_destroy(void *comm);   /* local ranks: destroy rank 0 last */
+int q36_moe_ep_open_window(void *comm, int T_max, int k, int D, int cap_rows);
+int q36_moe_ep_set_transport(void *comm, int transport);
+uint64_t q36_moe_ep_workspace_bytes(int T_max, int cap_rows, int world, int n_expert, int k, int D, int FF);
 int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd, const void *Sg,
                      const void *Su, const void *Sd, int n_expert, int k, int D, int FF, const void *X,
                      int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
                      float route_scale, float *out, int T, void *ws, uint64_t ws_bytes, void *stream);
+int q36_moe_ep_layer_phase(void *comm, int phase, const void *Wg, const void *Wu, const void *Wd, const void *Sg,
+                           const void *Su, const void *Sd, int n_expert, int k, int D, int FF, const void *X,
+                           int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
+                           float route_scale, float *out, int T, void *ws, uint64_t ws_bytes, void *stream);
 
 /* ---- tensor-core self-check (the role of test_mma_bs.cu:45-175) ----------
  * Runs 128 x N x K block-scaled tcgen05 tiles on caller data and returns the

@@ -28,9 +28,12 @@ int launch_front_decode(const float *logits, int n_expert, int k, float scale, i
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
                         int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0, int put_k,
                         cudaStream_t st);
-int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
-                               int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                               int *status, int plan_tile_rows, cudaStream_t st);
+// expert-parallel: wait (bounded) for every source rank's header of this call in the exchange window, bucket the
+// received slots by local expert, write the work plan; counts_out[world] receives the per-source slot counts
+int launch_ep_recv_plan(const void *win, uint64_t off_hdr0, uint64_t off_hdr1, uint64_t off_rows0, uint64_t off_rows1, const int *ctr,
+                        int world, int cap, int row_bytes, int eid_off, unsigned limit, int *status, int n_expert, int se0, int se1,
+                        int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
+                        int plan_tile_rows, int *counts_out, cudaStream_t st);
 int launch_front_small(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
                        int *idx, float *wt, int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1,
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,

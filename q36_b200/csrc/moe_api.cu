@@ -243,8 +243,8 @@ uint64_t q36_moe_dispatch_ws_bytes(int n_entries, int n_expert) { return dispatc
 
 int q36_moe_dispatch(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1, int *ecount,
                      int *eoffs, int *elist, int *pos, void *ws, uint64_t ws_bytes, void *stream) {
-    if (!expert_of_entry || !ecount || !eoffs || !elist || !pos || !ws) return Q36_MOE_EINVAL;
-    if (n_entries < 0 || n_expert <= 0 || n_expert > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (!ecount || !eoffs || !ws || n_entries < 0 || n_expert <= 0 || n_expert > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    if (n_entries > 0 && (!expert_of_entry || !elist || !pos)) return Q36_MOE_EINVAL;   // no entries: nothing to read or place
     if (se0 < 0 || se0 > se1 || se1 > n_expert) return Q36_MOE_EINVAL;
     if (ws_bytes < dispatch_ws_bytes(n_entries, n_expert)) return Q36_MOE_ENOSPACE;
     return launch_dispatch(expert_of_entry, n_entries, n_expert, se0, se1, ecount, eoffs, elist, pos, ws, nullptr, 0,

@@ -1,19 +1,35 @@
-// Expert-parallel MoE layer step, host orchestration in C with NCCL send/recv as the all-to-all.
+// Expert-parallel MoE layer step: dispatch and combine as the library's own kernels over peer memory.
 //
-// The reference's multi-GPU driver is native host code too (q36_multi_prefill, q36_engine.cu:4261-4306): every
-// device runs the layer on its expert shard and device 0 gathers, sums and broadcasts the partial outputs with
-// peer copies.  Here tokens stay on their home rank and only routed rows travel:
-//   route + dispatch (all experts) -> quantise -> pack rows per destination rank (fixed capacity C = T*k per
-//   peer, so no count ever reaches the host) -> all-to-all -> local dispatch of the received rows -> grouped
-//   expert FFN on the local shard (+ the shared expert on the rank's own tokens) -> result rows back by
-//   all-to-all -> weighted combine on the home rank.
-// A packed row is [2048 E4M3 bytes | 64 UE8M0 scale bytes | expert id (int32, -1 = empty slot) | 12 B pad].
+// The reference's multi-GPU driver is native host code (q36_multi_create / q36_multi_prefill,
+// q36_engine.cu:4234-4306): every device runs the layer on its expert shard and device 0 gathers, sums and
+// broadcasts the partial outputs with peer copies.  Here tokens stay on their home rank and only routed rows
+// travel, written by kernels STRAIGHT INTO THE DESTINATION RANK'S MEMORY over NVLink:
 //
-// NCCL is resolved at run time (dlopen of libnccl.so.2, the one the process already has loaded), so the library
-// keeps loading on machines without it.  All kernels read local memory only; the transport is NCCL's.
+//   phase 0 (home)    route + dispatch over all experts, quantise the rank's rows once, then k_ep_send stores
+//                     every routed row into the window of the rank that owns its expert and publishes
+//                     (count, epoch) there
+//   phase 1 (expert)  wait (bounded) for every source's header, bucket the received rows by local expert, run the
+//                     grouped FFN on the shard (+ the shared expert on the rank's own tokens), then k_ep_return
+//                     stores each result row into its home rank's window and publishes the epoch there
+//   phase 2 (home)    wait (bounded) for every expert rank's header, weighted combine
+//
+// Each rank owns one "window" (device memory allocated once when the window is opened, mapped into the other
+// ranks with CUDA IPC or, for ranks of one process, by peer access): [2 parities] x { headers, rows of every
+// source, result rows of every expert rank }.  A call uses parity (call number & 1); a rank can run at most one
+// call ahead of a peer because its combine needs that peer's results, so two parities suffice.  The call
+// number lives on the device, which makes a stack of calls capturable in a CUDA graph.
+//
+// Every wait is bounded; a wait that gives up records 0xB00 + source (dispatch) or 0xC00 + source (results) in
+// the status words and the step goes on (with garbage, but it ends and the host can see why).
+// No TMA or bulk copy ever touches another GPU's memory: peers are reached by plain st.global only, and every
+// tensor-core operand is read from local memory.
+//
+// NCCL carries the bootstrap (the IPC handles) and is kept as an alternative transport for comparison
+// (q36_moe_ep_set_transport): the same kernels then fill local staging buffers that grouped ncclSend/ncclRecv move.
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -29,6 +45,7 @@ struct NcclApi {
     ncclResult_t (*GroupEnd)();
     ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
     ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
     bool ok;
 };
 static NcclApi *nccl() {
@@ -46,116 +63,304 @@ static NcclApi *nccl() {
             api.GroupEnd = (decltype(api.GroupEnd))dlsym(h, "ncclGroupEnd");
             api.Send = (decltype(api.Send))dlsym(h, "ncclSend");
             api.Recv = (decltype(api.Recv))dlsym(h, "ncclRecv");
-            api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.GroupStart && api.GroupEnd && api.Send && api.Recv;
+            api.AllGather = (decltype(api.AllGather))dlsym(h, "ncclAllGather");
+            api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.GroupStart && api.GroupEnd && api.Send &&
+                     api.Recv && api.AllGather;
         }
     }
     return api.ok ? &api : nullptr;
 }
 
-struct EpComm { ncclComm_t comm; int rank, world; };
+constexpr int EP_MAX_WORLD = 16;
+constexpr int EP_TAIL = 16;   // behind the quantised row: expert id (int32) + 12 B pad
+constexpr unsigned EP_SPIN_LIMIT = 1u << 22;
 
-constexpr int EP_PAD = 16;   // expert id + padding behind the quantised row
+// Byte offsets inside a window, the same on every rank.
+struct WinLayout {
+    uint64_t hdr[2], rhdr[2], rows[2], ret[2], ctl, bytes;
+    int cap, D, world, row_bytes;
+};
+static WinLayout win_layout(int world, int cap, int D) {
+    WinLayout L;
+    L.cap = cap; L.D = D; L.world = world;
+    L.row_bytes = D + D / Q36_QK + EP_TAIL;
+    uint64_t o = 0;
+    auto take = [&](uint64_t b) { const uint64_t r = o; o += (b + 255) & ~(uint64_t)255; return r; };
+    for (int p = 0; p < 2; p++) { L.hdr[p] = take(8 * EP_MAX_WORLD); L.rhdr[p] = take(8 * EP_MAX_WORLD); }
+    L.ctl = take(256);   // [0] call counter, [1..3] tickets of the three "last block" patterns
+    for (int p = 0; p < 2; p++) L.rows[p] = take((uint64_t)world * cap * L.row_bytes);
+    for (int p = 0; p < 2; p++) L.ret[p] = take((uint64_t)world * cap * D * 4);
+    L.bytes = o;
+    return L;
+}
+
+enum { EP_KIND_PROCS = 0, EP_KIND_LOCAL = 1 };
+enum { EP_TRANSPORT_PEER = 0, EP_TRANSPORT_NCCL = 1 };
+
+struct EpComm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1, kind = EP_KIND_PROCS, device = 0, transport = EP_TRANSPORT_PEER;
+    EpComm **group = nullptr;            // EP_KIND_LOCAL: all ranks of the process (shared array, owned by rank 0)
+    bool open = false;
+    WinLayout L{};
+    int T_max = 0, k = 0;                // what the window was opened for
+    uint8_t *win = nullptr;              // this rank's window
+    uint8_t *peer[EP_MAX_WORLD] = {};    // every rank's window as mapped here (peer[rank] == win)
+    bool ipc_opened[EP_MAX_WORLD] = {};
+    uint8_t **d_peer = nullptr;          // device copy of peer[] (or of stage pointers for the NCCL transport)
+    uint8_t *stage = nullptr;            // NCCL transport: local staging laid out like a window
+    unsigned spin_limit = EP_SPIN_LIMIT;
+    unsigned long long calls = 0;        // host mirror of the device call counter (NCCL transport only)
+};
+
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acq_sys_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int wait_hdr(const unsigned long long *hdr, unsigned epoch, unsigned limit, int *status, int where) {
+    for (unsigned i = 0; i < limit; i++) {
+        const unsigned long long v = ld_acq_sys_u64(hdr);
+        if ((unsigned)(v >> 32) == epoch) return (int)(unsigned)v;
+        if (i > 64) __nanosleep(i < 4096 ? 32 : 256);
+    }
+    atomicCAS(status, 0, where);
+    return -1;
+}
 
 // ------------------------------------------------------------------ kernels
-// One block per send slot.  Slot (r, j) of the block for rank r carries the j-th row (in expert order) routed to
-// r: entry elist[base_r + j]; slots beyond the rank's count are marked empty.  Entry i comes back in slot
-// ypos[i] = r*C + (pos[i] - base_r).
+// One block per sorted row s (entry elist[s], expert e, destination rank r = e / per, j-th row for r): the
+// quantised row of its token + the expert id go to slot (me, j) of r's window.  The last block to finish
+// publishes (count_r, epoch) in every destination.  ypos[entry] = r * cap + j: where the result comes back.
+// slot_major_dst: NCCL transport, the "peers" are local staging blocks indexed by DESTINATION instead.
 __global__ void __launch_bounds__(128)
-k_ep_pack(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const int *__restrict__ idx,
-          const int *__restrict__ eoffs, const int *__restrict__ elist, const int *__restrict__ pos, int world, int E,
-          int k, int T, int C, int D, uint8_t *__restrict__ send, int *__restrict__ ypos) {
+k_ep_send(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const int *__restrict__ idx,
+          const int *__restrict__ eoffs, const int *__restrict__ elist, int world, int per, int k, int cap, int D,
+          uint8_t *const *__restrict__ peers, int me, uint64_t rows0, uint64_t rows1, uint64_t hdr0, uint64_t hdr1, int *ctl,
+          int *__restrict__ ypos, int slot_major_dst, int *status) {
     Q36_GDS();
-    const int slot = blockIdx.x, r = slot / C, j = slot % C, per = E / world;
-    const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_PAD;
-    const int base = eoffs[r * per], cnt = eoffs[(r + 1) * per] - base;
-    uint8_t *dst = send + (size_t)slot * row_bytes;
-    int eid = -1;
-    if (j < cnt) {
-        const int entry = elist[base + j], t = entry / k;
-        eid = idx[entry];
+    const int s = blockIdx.x;
+    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const bool odd = epoch & 1u;
+    const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_TAIL;
+    const int entry = elist[s], t = entry / k, e = idx[entry], r = e / per;
+    const int j = s - eoffs[r * per];
+    if (j < cap) {
+        uint8_t *dst = peers[r] + (odd ? rows1 : rows0) + ((size_t)(slot_major_dst ? r : me) * cap + j) * row_bytes;
         const uint4 *sq = reinterpret_cast<const uint4 *>(Xq + (size_t)t * D);
         for (int i = threadIdx.x; i < D / 16; i += blockDim.x) reinterpret_cast<uint4 *>(dst)[i] = sq[i];
         const uint4 *ss = reinterpret_cast<const uint4 *>(Xs + (size_t)t * nbs);
         for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) reinterpret_cast<uint4 *>(dst + D)[i] = ss[i];
+        if (threadIdx.x == 0) {
+            *reinterpret_cast<int4 *>(dst + D + nbs) = make_int4(e, 0, 0, 0);
+            ypos[entry] = r * cap + j;
+        }
+    } else if (threadIdx.x == 0) {
+        ypos[entry] = -1;                       // beyond the window's capacity: dropped, and reported
+        atomicCAS(status, 0, 0xD00);
     }
-    if (threadIdx.x == 0) *reinterpret_cast<int4 *>(dst + D + nbs) = make_int4(eid, 0, 0, 0);
-    // entries -> return slots (each entry handled once, by the blocks of slot index < T*k)
-    const int i = slot * blockDim.x + threadIdx.x;
-    if (i < T * k) {
-        const int p = pos[i];
-        const int rr = idx[i] / per;
-        ypos[i] = (p >= 0) ? rr * C + (p - eoffs[rr * per]) : -1;
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 1, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        if (threadIdx.x < world) {
+            const int rr = threadIdx.x;
+            const int cnt = min(cap, eoffs[(rr + 1) * per] - eoffs[rr * per]);
+            unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[rr] + (odd ? hdr1 : hdr0)) + (slot_major_dst ? rr : me);
+            st_release_sys_u64(h, (unsigned long long)(unsigned)cnt | ((unsigned long long)epoch << 32));
+        }
+        if (threadIdx.x == 0) ctl[1] = 0;
     }
 }
 
-__global__ void k_ep_eids(const uint8_t *__restrict__ recv, int n_slots, int row_bytes, int eid_off, int *__restrict__ eid) {
+// Received slots beyond FRONT_MAX_ENTRIES: wait for the headers in every block, then list each slot's expert id
+// (-1 for a slot its source did not fill) for the general dispatch kernels.
+__global__ void __launch_bounds__(256)
+k_ep_wait_eids(const uint8_t *__restrict__ win, uint64_t hdr0, uint64_t hdr1, uint64_t rows0, uint64_t rows1, const int *ctl,
+               int world, int cap, int row_bytes, int eid_off, unsigned limit, int *status, int *__restrict__ eid,
+               int *__restrict__ counts_out) {
     Q36_GDS();
+    __shared__ int s_cnt[EP_MAX_WORLD];
+    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const bool odd = epoch & 1u;
+    if (threadIdx.x < world) {
+        const int c = wait_hdr(reinterpret_cast<const unsigned long long *>(win + (odd ? hdr1 : hdr0)) + threadIdx.x, epoch, limit,
+                               status, 0xB00 + threadIdx.x);
+        s_cnt[threadIdx.x] = max(0, min(c, cap));
+        if (blockIdx.x == 0) counts_out[threadIdx.x] = s_cnt[threadIdx.x];
+    }
+    __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n_slots) eid[i] = *reinterpret_cast<const int *>(recv + (size_t)i * row_bytes + eid_off);
+    if (i < world * cap)
+        eid[i] = ((i % cap) < s_cnt[i / cap]) ? *reinterpret_cast<const int *>(win + (odd ? rows1 : rows0) + (size_t)i * row_bytes + eid_off) : -1;
 }
 
-// Sorted row r (< R) <- received slot llist[r] (zeros when r is beyond the resident count: llist holds -1 there);
-// rows [R, R+T) <- the rank's own tokens (the shared expert's group).
+// Sorted row r (< R) <- received slot llist[r] (zeros beyond the resident count); rows [R, R + T) <- the rank's
+// own tokens (the shared expert's group).
 __global__ void __launch_bounds__(128)
-k_ep_unpack(const uint8_t *__restrict__ recv, const int *__restrict__ llist, const int *__restrict__ loffs_end,
-            const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, int R, int T, int D,
+k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, const int *ctl, const int *__restrict__ llist,
+            const int *__restrict__ loffs_end, const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, int R, int T, int D,
             uint8_t *__restrict__ rows_q, uint8_t *__restrict__ rows_s) {
     Q36_GDS();
-    const int r = blockIdx.x;
-    const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_PAD;
-    const uint8_t *sq = nullptr, *ss = nullptr;
-    if (r < R) {
-        if (r < *loffs_end) {
-            const uint8_t *src = recv + (size_t)llist[r] * row_bytes;
-            sq = src;
-            ss = src + D;
+    const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_TAIL;
+    const bool odd = ((unsigned)ctl[0] + 1u) & 1u;
+    const uint8_t *recv = win + (odd ? rows1 : rows0);
+    const int n_res = *loffs_end;          // rows that arrived; rows [n_res, R) belong to no group and are never used
+    for (int x = blockIdx.x; x < n_res + T; x += gridDim.x) {
+        const int r = x < n_res ? x : R + (x - n_res);
+        const uint8_t *sq, *ss;
+        if (r < R) {
+            sq = recv + (size_t)llist[r] * row_bytes;
+            ss = sq + D;
+        } else {
+            sq = Xq + (size_t)(r - R) * D;
+            ss = Xs + (size_t)(r - R) * nbs;
         }
-    } else {
-        sq = Xq + (size_t)(r - R) * D;
-        ss = Xs + (size_t)(r - R) * nbs;
+        uint4 *dq = reinterpret_cast<uint4 *>(rows_q + (size_t)r * D), *ds = reinterpret_cast<uint4 *>(rows_s + (size_t)r * nbs);
+        for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dq[i] = reinterpret_cast<const uint4 *>(sq)[i];
+        for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) ds[i] = reinterpret_cast<const uint4 *>(ss)[i];
     }
-    uint4 *dq = reinterpret_cast<uint4 *>(rows_q + (size_t)r * D), *ds = reinterpret_cast<uint4 *>(rows_s + (size_t)r * nbs);
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dq[i] = sq ? reinterpret_cast<const uint4 *>(sq)[i] : z;
-    for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) ds[i] = ss ? reinterpret_cast<const uint4 *>(ss)[i] : z;
+}
+
+// One block per received slot (source rank s, j): its result row Y[lpos[slot]] goes to slot (me, j) of the
+// result area in s's window; the last block publishes the epoch in every source rank.
+__global__ void __launch_bounds__(256)
+k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int *__restrict__ counts, int world, int cap, int D,
+            uint8_t *const *__restrict__ peers, int me, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1, int *ctl,
+            int slot_major_dst) {
+    Q36_GDS();
+    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const bool odd = epoch & 1u;
+    // work items: the filled slots of every source, (s, j) with j < counts[s], numbered source by source
+    int total = 0;
+    for (int s = 0; s < world; s++) total += counts[s];
+    for (int x = blockIdx.x; x < total; x += gridDim.x) {
+        int s = 0, j = x;
+        while (j >= counts[s]) { j -= counts[s]; s++; }
+        const int p = lpos[s * cap + j];
+        float4 *dst = reinterpret_cast<float4 *>(peers[s] + (odd ? ret1 : ret0) + ((size_t)(slot_major_dst ? s : me) * cap + j) * D * 4);
+        const float4 *src = reinterpret_cast<const float4 *>(Y + (size_t)(p < 0 ? 0 : p) * D);
+        for (int i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = (p >= 0) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 2, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (s_last) {
+        __threadfence_system();
+        if (threadIdx.x < world) {
+            unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[threadIdx.x] + (odd ? rhdr1 : rhdr0)) + (slot_major_dst ? threadIdx.x : me);
+            st_release_sys_u64(h, (unsigned long long)epoch << 32);
+        }
+        if (threadIdx.x == 0) ctl[2] = 0;
+    }
+}
+
+// k_moe_combine_pf (q36_engine.cu:3393-3401) on the home rank: waits (bounded) for every expert rank's results of
+// this call, then out[t] = sum_s wt[t][s] * ret[ypos[t*k+s]] + sigmoid(gate) * SH[t] in slot order.  The last
+// block to finish advances the call counter.  grid (D / 1024, T).
+__global__ void __launch_bounds__(256)
+k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1,
+             int *ctl, int world, unsigned limit, int *status, const int *__restrict__ ypos, const float *__restrict__ wt,
+             const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k) {
+    Q36_GDS();
+    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const bool odd = epoch & 1u;
+    if (threadIdx.x < world)
+        wait_hdr(reinterpret_cast<const unsigned long long *>(win + (odd ? rhdr1 : rhdr0)) + threadIdx.x, epoch, limit, status,
+                 0xC00 + threadIdx.x);
+    __syncthreads();
+    const float *Y = reinterpret_cast<const float *>(win + (odd ? ret1 : ret0));
+    const int t = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i < D) {
+        constexpr int KMAX = 8;
+        int p[KMAX];
+        float w[KMAX];
+        float4 y[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; s++) {
+            p[s] = (s < k) ? ypos[(size_t)t * k + s] : -1;
+            w[s] = (s < k) ? wt[(size_t)t * k + s] : 0.f;
+        }
+        const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
+        float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (SH) ysh = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
+#pragma unroll
+        for (int s = 0; s < KMAX; s++)
+            y[s] = (p[s] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[s] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < KMAX; s++) {
+            if (p[s] < 0) continue;
+            acc.x = fmaf(w[s], y[s].x, acc.x); acc.y = fmaf(w[s], y[s].y, acc.y);
+            acc.z = fmaf(w[s], y[s].z, acc.z); acc.w = fmaf(w[s], y[s].w, acc.w);
+        }
+        if (SH) {
+            acc.x = fmaf(gs, ysh.x, acc.x); acc.y = fmaf(gs, ysh.y, acc.y);
+            acc.z = fmaf(gs, ysh.z, acc.z); acc.w = fmaf(gs, ysh.w, acc.w);
+        }
+        *reinterpret_cast<float4 *>(out + (size_t)t * D + i) = acc;
+    }
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 3, 1) == (int)(gridDim.x * gridDim.y) - 1);
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) { ctl[3] = 0; ctl[0] = (int)epoch; }   // the call is over: next call, other parity
 }
 
 static inline uint64_t al256(uint64_t x) { return (x + 255) & ~(uint64_t)255; }
 
 struct EpWs {
-    int *status, *idx, *ecount, *eoffs, *elist, *pos, *ypos, *reid, *lcount, *loffs, *llist, *lpos, *soffs;
-    float *wt, *Y, *back, *recv_y;
+    int *status, *idx, *ecount, *eoffs, *elist, *pos, *ypos, *reid, *lcount, *loffs, *llist, *lpos, *soffs, *counts;
+    float *wt, *Y;
     void *disp, *ldisp, *plan;
-    uint8_t *Xq, *Xs, *send, *recv, *rows_q, *rows_s, *Hq, *Hs;
+    uint8_t *Xq, *Xs, *rows_q, *rows_s, *Hq, *Hs;
     uint64_t total;
 };
-static EpWs ep_carve(void *base, int T, int world, int E, int k, int D, int FF) {
+// T: most tokens per call on this rank; cap: rows one rank may send to one other rank per call
+static EpWs ep_carve(void *base, int T, int cap, int world, int E, int k, int D, int FF) {
     EpWs w;
     uint8_t *p = (uint8_t *)base;
     uint64_t o = 0;
     auto take = [&](uint64_t b) { uint8_t *r = p + o; o += al256(b); return (void *)r; };
-    const uint64_t n = (uint64_t)T * k, C = n, S = (uint64_t)world * C, R = S, RT = R + T;
-    const uint64_t nbs = D / Q36_QK, rowb = D + nbs + EP_PAD;
+    const uint64_t n = (uint64_t)T * k, C = (uint64_t)cap, S = (uint64_t)world * C, R = S, RT = R + T;
+    const uint64_t nbs = D / Q36_QK;
     w.status = (int *)take(256);
     w.idx = (int *)take(n * 4); w.wt = (float *)take(n * 4);
     w.ecount = (int *)take((uint64_t)E * 4); w.eoffs = (int *)take((uint64_t)(E + 1) * 4);
     w.elist = (int *)take(n * 4); w.pos = (int *)take(n * 4); w.ypos = (int *)take(n * 4);
     w.disp = take(dispatch_ws_bytes((int)n, E));
     w.Xq = (uint8_t *)take((uint64_t)T * D); w.Xs = (uint8_t *)take((uint64_t)T * nbs);
-    w.send = (uint8_t *)take(S * rowb); w.recv = (uint8_t *)take(S * rowb);
     w.reid = (int *)take(S * 4);
     w.lcount = (int *)take((uint64_t)E * 4); w.loffs = (int *)take((uint64_t)(E + 1) * 4);
-    w.llist = (int *)take(S * 4); w.lpos = (int *)take(S * 4); w.soffs = (int *)take(8);
+    w.llist = (int *)take(S * 4); w.lpos = (int *)take(S * 4); w.soffs = (int *)take(8); w.counts = (int *)take(4 * EP_MAX_WORLD);
     w.ldisp = take(dispatch_ws_bytes((int)S, E));
     w.rows_q = (uint8_t *)take(RT * D); w.rows_s = (uint8_t *)take(RT * nbs);
     w.Hq = (uint8_t *)take(RT * FF); w.Hs = (uint8_t *)take(RT * (FF / Q36_QK));
     w.Y = (float *)take(RT * D * 4);
-    w.back = (float *)take(S * D * 4); w.recv_y = (float *)take(S * D * 4);
     w.plan = take(tc_ws_bytes());
     w.total = o;
     return w;
 }
 
+static int ckc(cudaError_t e) {
+    if (e != cudaSuccess) { last_cuda_error() = (int)e; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+static int ckn(ncclResult_t r) {
+    if (r != ncclSuccess) { last_cuda_error() = 300000 + (int)r; return Q36_MOE_ECUDA; }
+    return Q36_MOE_OK;
+}
+
+// NCCL transport: block p of `send` (bytes_per_peer each) -> rank p's `recv` block of this rank
 static int all_to_all(NcclApi *api, EpComm *c, const void *send, void *recv, size_t bytes_per_peer, cudaStream_t st) {
     ncclResult_t r = api->GroupStart();
     for (int p = 0; p < c->world && r == ncclSuccess; p++) {
@@ -163,9 +368,142 @@ static int all_to_all(NcclApi *api, EpComm *c, const void *send, void *recv, siz
         if (r == ncclSuccess) r = api->Recv((uint8_t *)recv + (size_t)p * bytes_per_peer, bytes_per_peer, ncclUint8, p, c->comm, st);
     }
     const ncclResult_t e = api->GroupEnd();
-    if (r == ncclSuccess) r = e;
-    if (r != ncclSuccess) { last_cuda_error() = 300000 + (int)r; return Q36_MOE_ECUDA; }
-    return Q36_MOE_OK;
+    return ckn(r == ncclSuccess ? e : r);
+}
+
+static void close_window(EpComm *c) {
+    if (!c->open) return;
+    cudaSetDevice(c->device);
+    for (int r = 0; r < c->world; r++)
+        if (c->ipc_opened[r]) { cudaIpcCloseMemHandle(c->peer[r]); c->ipc_opened[r] = false; }
+    if (c->d_peer) cudaFree(c->d_peer);
+    if (c->stage) cudaFree(c->stage);
+    if (c->win) cudaFree(c->win);
+    c->d_peer = nullptr; c->stage = nullptr; c->win = nullptr;
+    c->open = false;
+}
+
+// device copy of the table the kernels index by rank: the ranks' windows, or (NCCL transport) the local staging
+static int push_peer_table(EpComm *c) {
+    uint8_t *tbl[EP_MAX_WORLD];
+    for (int r = 0; r < EP_MAX_WORLD; r++) tbl[r] = (c->transport == EP_TRANSPORT_NCCL) ? c->stage : c->peer[r];
+    return ckc(cudaMemcpy(c->d_peer, tbl, sizeof tbl, cudaMemcpyHostToDevice));
+}
+
+struct LayerArgs {
+    const void *Wg, *Wu, *Wd, *Sg, *Su, *Sd;
+    int E, k, D, FF;
+    const void *X;
+    int x_is_bf16;
+    const float *logits;
+    int logit_stride, shgate_col;
+    float route_scale;
+    float *out;
+    int T;
+    void *ws;
+    uint64_t ws_bytes;
+};
+
+static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
+    const int world = c->world, rank = c->rank, E = a.E, k = a.k, D = a.D, FF = a.FF, T = a.T;
+    if (!c->open) return Q36_MOE_EINVAL;
+    if (!a.Wg || !a.Wu || !a.Wd || !a.X || !a.logits || !a.out || !a.ws) return Q36_MOE_EINVAL;
+    if (T <= 0 || k <= 0 || k > 8 || E % world || E > DISPATCH_MAX_GROUPS || D % 512 || FF % 512 || a.logit_stride < E) return Q36_MOE_EINVAL;
+    if (!router_supports(E)) return Q36_MOE_EINVAL;
+    const int n = T * k, C = c->L.cap, S = world * C, R = S, per = E / world, se0 = rank * per, se1 = se0 + per;
+    if (D != c->L.D || k != c->k || T > c->T_max) return Q36_MOE_ENOSPACE;   // the window was opened for other sizes
+    // the private workspace is carved for the window's sizes so that every call sees the same layout
+    const EpWs w = ep_carve(a.ws, c->T_max, C, world, E, k, D, FF);
+    if (w.total > a.ws_bytes) return Q36_MOE_ENOSPACE;
+    const int nbs = D / Q36_QK, rowb = c->L.row_bytes;
+    const bool shared = a.Sg && a.Su && a.Sd;
+    const WinLayout &L = c->L;
+    int *ctl = (int *)(c->win + L.ctl);
+    const bool use_nccl = c->transport == EP_TRANSPORT_NCCL;
+    NcclApi *api = use_nccl ? nccl() : nullptr;
+    if (use_nccl && (!api || c->kind != EP_KIND_PROCS)) return Q36_MOE_EINVAL;
+    const int par = (int)((c->calls + 1) & 1);                    // NCCL transport only (host mirror of the call counter)
+    int rc;
+    if (phase == 0) {
+        // route + dispatch over ALL experts (their order is the destination-rank order); quantise the rank's tokens
+        // once, in token order (hw order inside the blocks): one cluster launch at decode sizes
+        const bool cluster_front = T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
+        if (cluster_front) {
+            if ((rc = launch_front_decode(a.logits, E, k, a.route_scale, T, a.logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
+                                          w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, a.X, a.x_is_bf16, w.Xq, w.Xs, 0, 0, st)))
+                return rc;
+        } else if (n <= 1024) {
+            if ((rc = launch_front_small(a.logits, E, k, a.route_scale, T, a.logit_stride, 0, E, w.idx, w.wt, w.ecount, w.eoffs,
+                                         w.elist, w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, nullptr, 0, nullptr, nullptr, -1, 0, st)))
+                return rc;
+        } else {
+            if ((rc = launch_router_topk(a.logits, E, k, w.idx, w.wt, a.route_scale, 1, T, a.logit_stride, st))) return rc;
+            if ((rc = launch_dispatch(w.idx, n, E, 0, E, w.ecount, w.eoffs, w.elist, w.pos, w.disp, nullptr, 0, 0, st))) return rc;
+        }
+        if (!cluster_front && (rc = launch_quant(a.X, a.x_is_bf16, w.Xq, w.Xs, T, D, nullptr, 0, 0, true, st))) return rc;
+        launch_k(k_ep_send, dim3(n), dim3(128), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
+                 (const int *)w.eoffs, (const int *)w.elist, world, per, k, C, D, (uint8_t *const *)c->d_peer, rank, L.rows[0], L.rows[1],
+                 L.hdr[0], L.hdr[1], ctl, w.ypos, use_nccl ? 1 : 0, w.status);
+        if ((rc = check_launch())) return rc;
+        if (use_nccl) {   // staging blocks (indexed by destination) -> the destinations' windows (indexed by source)
+            if ((rc = all_to_all(api, c, c->stage + L.rows[par], c->win + L.rows[par], (size_t)C * rowb, st))) return rc;
+            if ((rc = all_to_all(api, c, c->stage + L.hdr[par], c->win + L.hdr[par], 8, st))) return rc;
+        }
+        return Q36_MOE_OK;
+    }
+    if (phase == 1) {
+        // local plan over the received slots
+        const bool small_plan = S <= 1024;   // one block waits, sorts the slots and writes the work plan
+        // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count
+        const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
+        if (small_plan) {
+            if ((rc = launch_ep_recv_plan(c->win, L.hdr[0], L.hdr[1], L.rows[0], L.rows[1], ctl, world, C, rowb, D + nbs, c->spin_limit,
+                                          w.status, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs, R, shared ? R + T : R,
+                                          w.plan, D, FF, one_launch ? 16 : 0, w.counts, st)))
+                return rc;
+        } else {
+            launch_k(k_ep_wait_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)c->win, L.hdr[0], L.hdr[1], L.rows[0],
+                     L.rows[1], (const int *)ctl, world, C, rowb, D + nbs, c->spin_limit, w.status, w.reid, w.counts);
+            if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st)))
+                return rc;
+        }
+        launch_k(k_ep_unpack, dim3(min(R + T, 8 * sm_count())), dim3(128), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,
+                 (const int *)w.llist, (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s);
+        if ((rc = check_launch())) return rc;
+        // grouped expert FFN on the local shard (+ shared expert on the own tokens)
+        const int *goffs = w.loffs + se0;
+        if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, one_launch ? 16 : 0, st)))
+            return rc;
+        if (one_launch) {
+            if ((rc = launch_ffn_fused_small(a.Wg, a.Wu, a.Wd, shared ? a.Sg : nullptr, shared ? a.Su : nullptr, shared ? a.Sd : nullptr,
+                                             per, R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, nullptr, nullptr, 0, st)))
+                return rc;
+        } else {
+            if ((rc = launch_gateup_tc(a.Wg, a.Wu, shared ? a.Sg : nullptr, shared ? a.Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
+                                       w.Hq, w.Hs, D, FF, w.plan, w.status, st)))
+                return rc;
+            if ((rc = launch_down_tc(a.Wd, shared ? a.Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+                return rc;
+        }
+        // result rows straight into their home ranks' windows
+        launch_k(k_ep_return, dim3(min(S, 8 * sm_count())), dim3(256), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
+                 (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0);
+        if ((rc = check_launch())) return rc;
+        if (use_nccl) {
+            if ((rc = all_to_all(api, c, c->stage + L.ret[par], c->win + L.ret[par], (size_t)C * D * 4, st))) return rc;
+            if ((rc = all_to_all(api, c, c->stage + L.rhdr[par], c->win + L.rhdr[par], 8, st))) return rc;
+        }
+        return Q36_MOE_OK;
+    }
+    if (phase == 2) {
+        const float *shg = (shared && a.shgate_col >= 0) ? a.logits + a.shgate_col : nullptr;
+        launch_k(k_ep_combine, dim3((D / 4 + 255) / 256, T), dim3(256), 0, st, a.out, (const uint8_t *)c->win, L.ret[0], L.ret[1],
+                 L.rhdr[0], L.rhdr[1], ctl, world, c->spin_limit, w.status, (const int *)w.ypos, (const float *)w.wt,
+                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k);
+        c->calls++;
+        return check_launch();
+    }
+    return Q36_MOE_EINVAL;
 }
 
 }  // namespace q36
@@ -185,107 +523,161 @@ int q36_moe_ep_unique_id(void *out128) {
 
 int q36_moe_ep_init(const void *id128, int rank, int world, void **comm_out) {
     NcclApi *api = nccl();
-    if (!api || !id128 || !comm_out || world < 1 || rank < 0 || rank >= world) return Q36_MOE_EINVAL;
+    if (!api || !id128 || !comm_out || world < 1 || world > EP_MAX_WORLD || rank < 0 || rank >= world) return Q36_MOE_EINVAL;
     ncclUniqueId id;
     memcpy(&id, id128, sizeof id);
-    EpComm *c = new EpComm{nullptr, rank, world};
-    const ncclResult_t r = api->CommInitRank(&c->comm, world, id, rank);
-    if (r != ncclSuccess) { last_cuda_error() = 300000 + (int)r; delete c; return Q36_MOE_ECUDA; }
+    EpComm *c = new EpComm;
+    c->rank = rank; c->world = world; c->kind = EP_KIND_PROCS;
+    cudaGetDevice(&c->device);
+    const int rc = ckn(api->CommInitRank(&c->comm, world, id, rank));
+    if (rc) { delete c; return rc; }
     *comm_out = c;
     return Q36_MOE_OK;
 }
 
+int q36_moe_ep_init_local(int world, const int *devices, void **comms_out) {
+    if (!devices || !comms_out || world < 1 || world > EP_MAX_WORLD) return Q36_MOE_EINVAL;
+    EpComm **group = new EpComm *[world];
+    for (int r = 0; r < world; r++) {
+        EpComm *c = new EpComm;
+        c->rank = r; c->world = world; c->kind = EP_KIND_LOCAL; c->device = devices[r]; c->group = group;
+        group[r] = c;
+        comms_out[r] = c;
+    }
+    return Q36_MOE_OK;
+}
+
 int q36_moe_ep_destroy(void *comm) {
-    NcclApi *api = nccl();
     EpComm *c = (EpComm *)comm;
-    if (!api || !c) return Q36_MOE_EINVAL;
-    api->CommDestroy(c->comm);
+    if (!c) return Q36_MOE_EINVAL;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    close_window(c);
+    cudaSetDevice(dev);
+    if (c->kind == EP_KIND_PROCS) {
+        NcclApi *api = nccl();
+        if (api && c->comm) api->CommDestroy(c->comm);
+    } else if (c->rank == 0) {
+        // rank 0 owns the shared array; the caller destroys rank 0 last
+        delete[] c->group;
+    }
     delete c;
     return Q36_MOE_OK;
 }
 
-uint64_t q36_moe_ep_workspace_bytes(int T, int world, int n_expert, int k, int D, int FF) {
-    if (T <= 0 || world <= 0 || n_expert <= 0 || k <= 0) return 0;
-    return ep_carve(nullptr, T, world, n_expert, k, D, FF).total;
+int q36_moe_ep_set_transport(void *comm, int transport) {
+    EpComm *c = (EpComm *)comm;
+    if (!c || (transport != EP_TRANSPORT_PEER && transport != EP_TRANSPORT_NCCL)) return Q36_MOE_EINVAL;
+    if (transport == EP_TRANSPORT_NCCL && c->kind != EP_KIND_PROCS) return Q36_MOE_EINVAL;
+    c->transport = transport;
+    if (!c->open) return Q36_MOE_OK;
+    if (transport == EP_TRANSPORT_NCCL && !c->stage) {
+        int rc = ckc(cudaMalloc((void **)&c->stage, c->L.bytes));
+        if (rc) return rc;
+        if ((rc = ckc(cudaMemset(c->stage, 0, c->L.bytes)))) return rc;
+    }
+    return push_peer_table(c);
+}
+
+int q36_moe_ep_open_window(void *comm, int T_max, int k, int D, int cap_rows) {
+    EpComm *c0 = (EpComm *)comm;
+    if (!c0 || T_max <= 0 || k <= 0 || k > 8 || D % 512 || cap_rows < 0 || cap_rows > T_max * k) return Q36_MOE_EINVAL;
+    int dev0 = 0;
+    cudaGetDevice(&dev0);
+    const int world = c0->world;
+    const WinLayout L = win_layout(world, cap_rows ? cap_rows : T_max * k, D);
+    int rc = Q36_MOE_OK;
+    auto alloc_one = [&](EpComm *c) -> int {
+        close_window(c);
+        int r;
+        if ((r = ckc(cudaSetDevice(c->device)))) return r;
+        c->L = L; c->T_max = T_max; c->k = k;
+        if ((r = ckc(cudaMalloc((void **)&c->win, L.bytes)))) return r;
+        if ((r = ckc(cudaMemset(c->win, 0, L.bytes)))) return r;
+        if ((r = ckc(cudaMalloc((void **)&c->d_peer, sizeof(uint8_t *) * EP_MAX_WORLD)))) return r;
+        c->calls = 0;
+        c->open = true;
+        return Q36_MOE_OK;
+    };
+    if (c0->kind == EP_KIND_LOCAL) {
+        // one process: every rank's window is plain device memory; ranks on different devices reach it by peer access
+        for (int r = 0; r < world && !rc; r++) rc = alloc_one(c0->group[r]);
+        for (int r = 0; r < world && !rc; r++) {
+            EpComm *c = c0->group[r];
+            cudaSetDevice(c->device);
+            bool same_device_only = true;
+            for (int p = 0; p < world; p++) {
+                c->peer[p] = c0->group[p]->win;
+                if (c0->group[p]->device != c->device) {
+                    same_device_only = false;
+                    const cudaError_t e = cudaDeviceEnablePeerAccess(c0->group[p]->device, 0);
+                    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) rc = ckc(e);
+                    cudaGetLastError();
+                }
+            }
+            // ranks that take turns on ONE device run their phases in stream order: a header is there before the kernel
+            // that reads it starts, so a wait never has to spin; keep the limit small so a wrong phase order ends at once
+            if (same_device_only) c->spin_limit = 1024;
+            if (!rc) rc = push_peer_table(c);
+        }
+        if (!rc) rc = ckc(cudaDeviceSynchronize());
+        cudaSetDevice(dev0);
+        return rc;
+    }
+    // one process per GPU: exchange CUDA IPC handles of the windows over NCCL
+    NcclApi *api = nccl();
+    if (!api) return Q36_MOE_EINVAL;
+    if ((rc = alloc_one(c0))) return rc;
+    cudaIpcMemHandle_t mine, all[EP_MAX_WORLD];
+    if ((rc = ckc(cudaIpcGetMemHandle(&mine, c0->win)))) return rc;
+    uint8_t *d_h = nullptr;
+    if ((rc = ckc(cudaMalloc((void **)&d_h, sizeof(mine) * (world + 1))))) return rc;
+    if (!rc) rc = ckc(cudaMemcpy(d_h, &mine, sizeof mine, cudaMemcpyHostToDevice));
+    if (!rc) rc = ckn(api->AllGather(d_h, d_h + sizeof mine, sizeof mine, ncclUint8, c0->comm, (cudaStream_t)0));
+    if (!rc) rc = ckc(cudaStreamSynchronize((cudaStream_t)0));
+    if (!rc) rc = ckc(cudaMemcpy(all, d_h + sizeof mine, sizeof(mine) * world, cudaMemcpyDeviceToHost));
+    cudaFree(d_h);
+    for (int p = 0; p < world && !rc; p++) {
+        if (p == c0->rank) { c0->peer[p] = c0->win; continue; }
+        void *ptr = nullptr;
+        rc = ckc(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess));
+        if (!rc) { c0->peer[p] = (uint8_t *)ptr; c0->ipc_opened[p] = true; }
+    }
+    if (!rc && c0->transport == EP_TRANSPORT_NCCL) {
+        rc = ckc(cudaMalloc((void **)&c0->stage, L.bytes));
+        if (!rc) rc = ckc(cudaMemset(c0->stage, 0, L.bytes));
+    }
+    if (!rc) rc = push_peer_table(c0);
+    if (!rc) rc = ckc(cudaDeviceSynchronize());
+    return rc;
+}
+
+uint64_t q36_moe_ep_workspace_bytes(int T_max, int cap_rows, int world, int n_expert, int k, int D, int FF) {
+    if (T_max <= 0 || world <= 0 || n_expert <= 0 || k <= 0 || cap_rows < 0) return 0;
+    return ep_carve(nullptr, T_max, cap_rows ? cap_rows : T_max * k, world, n_expert, k, D, FF).total;
+}
+
+int q36_moe_ep_layer_phase(void *comm, int phase, const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
+                           const void *Sd, int n_expert, int k, int D, int FF, const void *X, int x_is_bf16, const float *logits,
+                           int logit_stride, int shgate_col, float route_scale, float *out, int T, void *ws, uint64_t ws_bytes,
+                           void *stream) {
+    EpComm *c = (EpComm *)comm;
+    if (!c) return Q36_MOE_EINVAL;
+    const LayerArgs a{Wg, Wu, Wd, Sg, Su, Sd, n_expert, k, D, FF, X, x_is_bf16, logits, logit_stride, shgate_col, route_scale, out, T, ws, ws_bytes};
+    return ep_phase(c, phase, a, (cudaStream_t)stream);
 }
 
 int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                      const void *Sd, int n_expert, int k, int D, int FF, const void *X, int x_is_bf16,
                      const float *logits, int logit_stride, int shgate_col, float route_scale, float *out, int T,
                      void *ws, uint64_t ws_bytes, void *stream) {
-    NcclApi *api = nccl();
     EpComm *c = (EpComm *)comm;
-    if (!api || !c || !Wg || !Wu || !Wd || !X || !logits || !out || !ws) return Q36_MOE_EINVAL;
-    const int world = c->world, rank = c->rank, E = n_expert;
-    if (T <= 0 || k <= 0 || k > 8 || E % world || E > DISPATCH_MAX_GROUPS || D % 512 || FF % 512 || logit_stride < E)
-        return Q36_MOE_EINVAL;
-    if (!router_supports(E)) return Q36_MOE_EINVAL;
-    const EpWs w = ep_carve(ws, T, world, E, k, D, FF);
-    if (w.total > ws_bytes) return Q36_MOE_ENOSPACE;
-    cudaStream_t st = (cudaStream_t)stream;
-    const int n = T * k, C = n, S = world * C, R = S, per = E / world, se0 = rank * per, se1 = se0 + per;
-    const int nbs = D / Q36_QK, rowb = D + nbs + EP_PAD;
-    const bool shared = Sg && Su && Sd;
+    if (!c) return Q36_MOE_EINVAL;
+    const LayerArgs a{Wg, Wu, Wd, Sg, Su, Sd, n_expert, k, D, FF, X, x_is_bf16, logits, logit_stride, shgate_col, route_scale, out, T, ws, ws_bytes};
     int rc;
-    // 1. route + dispatch over ALL experts (their order is the destination-rank order), and
-    // 2. quantise the rank's tokens once, in token order (hw order inside the blocks): one cluster launch at decode sizes
-    const bool cluster_front = T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
-    if (cluster_front) {
-        if ((rc = launch_front_decode(logits, E, k, route_scale, T, logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist, w.pos,
-                                      nullptr, 0, 0, nullptr, D, FF, w.status, X, x_is_bf16, w.Xq, w.Xs, 0, 0, st)))
-            return rc;
-    } else if (n <= 1024) {
-        if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, 0, E, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
-                                     w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, nullptr, 0, nullptr, nullptr, -1, 0, st)))
-            return rc;
-    } else {
-        if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
-        if ((rc = launch_dispatch(w.idx, n, E, 0, E, w.ecount, w.eoffs, w.elist, w.pos, w.disp, nullptr, 0, 0, st))) return rc;
-    }
-    if (!cluster_front && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, nullptr, 0, 0, true, st))) return rc;
-    // 3. pack per destination rank and exchange
-    launch_k(k_ep_pack, dim3(S), dim3(128), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
-             (const int *)w.eoffs, (const int *)w.elist, (const int *)w.pos, world, E, k, T, C, D, w.send, w.ypos);
-    if ((rc = check_launch())) return rc;
-    if ((rc = all_to_all(api, c, w.send, w.recv, (size_t)C * rowb, st))) return rc;
-    // 4. local plan over the received slots; empty slots (-1) and nothing else drop out
-    const bool small_plan = S <= 1024;   // one block sorts the slots and writes the work plan
-    // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count
-    const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
-    if (small_plan) {
-        if ((rc = launch_dispatch_plan_small(w.recv + (D + nbs), rowb, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs,
-                                             R, shared ? R + T : R, w.plan, D, FF, w.status, one_launch ? 16 : 0, st)))
-            return rc;
-    } else {
-        launch_k(k_ep_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)w.recv, S, rowb, D + nbs, w.reid);
-        if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st)))
-            return rc;
-    }
-    launch_k(k_ep_unpack, dim3(R + T), dim3(128), 0, st, (const uint8_t *)w.recv, (const int *)w.llist,
-             (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s);
-    if ((rc = check_launch())) return rc;
-    // 5. grouped expert FFN on the local shard (+ shared expert on the own tokens)
-    const int *goffs = w.loffs + se0;
-    if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, one_launch ? 16 : 0, st)))
-        return rc;
-    // an expert receives at most one row per token of every rank: with at most 16 of them the decode kernel
-    // (gate/up and down in one persistent launch) applies
-    if (one_launch) {
-        if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, per,
-                                         R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, w.llist, w.back, R, st)))
-            return rc;   // (routed result rows land in the slots of the return exchange; the shared rows stay in Y)
-    } else {
-        if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
-                                   w.Hq, w.Hs, D, FF, w.plan, w.status, st)))
-            return rc;
-        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
-            return rc;
-    }
-    // 6. result rows back to their home ranks, then the weighted combine
-    if (!one_launch && (rc = launch_gather_rows(w.Y, w.lpos, w.back, S, D * 4, st))) return rc;
-    if ((rc = all_to_all(api, c, w.back, w.recv_y, (size_t)C * D * 4, st))) return rc;
-    const float *shg = (shared && shgate_col >= 0) ? logits + shgate_col : nullptr;
-    return launch_combine(out, w.recv_y, w.ypos, w.wt, shared ? w.Y + (size_t)R * D : nullptr, shg, logit_stride, D, k, T, false, st);
+    for (int phase = 0; phase < 3; phase++)
+        if ((rc = ep_phase(c, phase, a, (cudaStream_t)stream))) return rc;
+    return Q36_MOE_OK;
 }
 
 }  // extern "C"

@@ -307,23 +307,77 @@ __global__ void k_quant_e4m3(const void *__restrict__ X, uint8_t *__restrict__ X
 // Same results as the separate kernels: the same route_row, the same stable order.
 constexpr int FRONT_MAX_ENTRIES = 1024;
 
+// Block-wide stable bucketing of up to FRONT_MAX_ENTRIES entries by expert (thread i owns entry i, e = its expert
+// id or anything outside [se0, se1) for "not resident"), then the tensor-core work plan.  Shared arrays come from
+// the caller.  All threads of the block call; ends with every output written (no trailing barrier).
+struct SortSmem {
+    unsigned short cnt[FRONT_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // 32 KB: per (entry warp, expert) count, then base
+    int s_eoffs[DISPATCH_MAX_E + 1];
+    int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
+};
+__device__ __forceinline__ void sort_entries_block(SortSmem &sm, int e, int n, int n_expert, int se0, int se1,
+                                                   int *__restrict__ ecount, int *__restrict__ eoffs, int *__restrict__ elist,
+                                                   int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan,
+                                                   int mt_gu, int mt_dn, int plan_tile_rows) {
+    // precondition: sm.cnt rows [0, (n + 31) / 32) are zero and a barrier separates that from this call
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int used_warps = (n + 31) / 32;          // only the warps that own entries contribute counts
+    if (tid >= n || e < 0 || e < se0 || e >= se1 || e >= n_expert) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && r_in_warp == 0) sm.cnt[warp][e] = (unsigned short)__popc(peers);
+    __syncthreads();
+    for (int x = tid; x < n_expert; x += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < used_warps; w++) {
+            const int c = sm.cnt[w][x];
+            sm.cnt[w][x] = (unsigned short)run;
+            run += c;
+        }
+        ecount[x] = run;
+        sm.s_eoffs[x] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {   // exclusive scan of the expert totals: lane owns a contiguous run
+        const int per = (n_expert + 31) / 32;
+        int sum = 0;
+        for (int j = 0; j < per; j++) { const int x = lane * per + j; if (x < n_expert) sum += sm.s_eoffs[x]; }
+        int incl = sum;
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+        int run = incl - sum;
+        for (int j = 0; j < per; j++) {
+            const int x = lane * per + j;
+            if (x < n_expert) { const int c = sm.s_eoffs[x]; sm.s_eoffs[x] = run; run += c; }
+        }
+        if (lane == 31) sm.s_eoffs[n_expert] = run;
+    }
+    __syncthreads();
+    for (int x = tid; x <= n_expert; x += blockDim.x) eoffs[x] = sm.s_eoffs[x];
+    if (tid == 0 && soffs) { soffs[0] = s0; soffs[1] = s1; }
+    if (tid < n) {
+        if (e >= 0) {
+            const int p = sm.s_eoffs[e] + sm.cnt[warp][e] + r_in_warp;
+            elist[p] = tid;
+            pos[tid] = p;
+        } else pos[tid] = -1;
+    }
+    // groups here hold at most a few token tiles: ranking by size would buy nothing
+    if (plan) tc_plan_block(sm.s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, sm.scratch, false, plan_tile_rows);
+}
+
 __global__ void __launch_bounds__(1024)
 k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale, int T, int row_stride, int se0, int se1,
               int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
               int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1,
-              TcPlan *plan, int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16,
-              uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0,
-              const uint8_t *__restrict__ ent, int ent_stride, int n_ent, int plan_tile_rows) {
-    // ent != nullptr: no routing, the n_ent entries' expert ids are the ints at ent + i * ent_stride (T, k unused)
+              TcPlan *plan, int mt_gu, int mt_dn, const void *__restrict__ X, int x_is_bf16,
+              uint8_t *__restrict__ Xq, uint8_t *__restrict__ Xs, int D, int shared_row0, int plan_tile_rows) {
     Q36_GDS();
-    __shared__ unsigned short cnt[FRONT_MAX_ENTRIES / 32][DISPATCH_MAX_E];   // 32 KB
-    __shared__ int s_eoffs[DISPATCH_MAX_E + 1];
-    __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
+    __shared__ SortSmem sm;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
-    const int n = ent ? n_ent : T * k;
-    const int used_warps = (n + 31) / 32;          // only the warps that own entries contribute counts
-    for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&cnt[0][0])[i] = 0;
-    for (int t = warp; t < T && !ent; t += nwarp) {
+    const int n = T * k;
+    const int used_warps = (n + 31) / 32;
+    for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&sm.cnt[0][0])[i] = 0;
+    for (int t = warp; t < T; t += nwarp) {
         const float *l = logits + (size_t)t * row_stride;
         int *ix = idx + (size_t)t * k;
         float *w = wt + (size_t)t * k;
@@ -333,51 +387,8 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
         else route_row<1>(l, k, ix, w, scale, 1, lane);
     }
     __syncthreads();   // idx written by this block is visible to it after the barrier
-    int e = -1;
-    if (tid < n) {
-        e = ent ? *reinterpret_cast<const int *>(ent + (size_t)tid * ent_stride) : idx[tid];
-        if (e < 0 || e < se0 || e >= se1 || e >= n_expert) e = -1;
-    }
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    const int r_in_warp = __popc(peers & ((1u << lane) - 1u));
-    if (e >= 0 && r_in_warp == 0) cnt[warp][e] = (unsigned short)__popc(peers);
-    __syncthreads();
-    for (int x = tid; x < n_expert; x += blockDim.x) {
-        int run = 0;
-        for (int w = 0; w < used_warps; w++) {
-            const int c = cnt[w][x];
-            cnt[w][x] = (unsigned short)run;
-            run += c;
-        }
-        ecount[x] = run;
-        s_eoffs[x] = run;
-    }
-    __syncthreads();
-    if (warp == 0) {   // exclusive scan of the expert totals: lane owns a contiguous run
-        const int per = (n_expert + 31) / 32;
-        int sum = 0;
-        for (int j = 0; j < per; j++) { const int x = lane * per + j; if (x < n_expert) sum += s_eoffs[x]; }
-        int incl = sum;
-        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
-        int run = incl - sum;
-        for (int j = 0; j < per; j++) {
-            const int x = lane * per + j;
-            if (x < n_expert) { const int c = s_eoffs[x]; s_eoffs[x] = run; run += c; }
-        }
-        if (lane == 31) s_eoffs[n_expert] = run;
-    }
-    __syncthreads();
-    for (int x = tid; x <= n_expert; x += blockDim.x) eoffs[x] = s_eoffs[x];
-    if (tid == 0 && soffs) { soffs[0] = s0; soffs[1] = s1; }
-    if (tid < n) {
-        if (e >= 0) {
-            const int p = s_eoffs[e] + cnt[warp][e] + r_in_warp;
-            elist[p] = tid;
-            pos[tid] = p;
-        } else pos[tid] = -1;
-    }
-    // groups here hold at most T <= 128 rows, one or two token tiles: ranking by size would buy nothing
-    if (plan) tc_plan_block(s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, scratch, false, plan_tile_rows);
+    sort_entries_block(sm, tid < n ? idx[tid] : -1, n, n_expert, se0, se1, ecount, eoffs, elist, pos, soffs, s0, s1, plan, mt_gu,
+                       mt_dn, plan_tile_rows);
     if (X) {   // decode: quantise and scatter the T rows here as well (pos[] of this block is visible after the barrier)
         __syncthreads();
         const int nbk = D / Q36_QK;
@@ -398,15 +409,63 @@ k_front_small(const float *__restrict__ logits, int n_expert, int k, float scale
     }
 }
 
-// dispatch (+ work plan) of entries whose expert ids sit in a strided buffer: k_front_small without the router
-int launch_dispatch_plan_small(const void *ent, int ent_stride, int n_ent, int n_expert, int se0, int se1, int *ecount,
-                               int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
-                               int *status, int plan_tile_rows, cudaStream_t st) {
-    if (n_ent > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || !ent) return Q36_MOE_EINVAL;
-    launch_k(k_front_small, dim3(1), dim3(1024), 0, st, (const float *)nullptr, n_expert, 1, 1.f, 0, 0, se0, se1, (int *)nullptr,
-             (float *)nullptr, ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status,
-             (const void *)nullptr, 0, (uint8_t *)nullptr, (uint8_t *)nullptr, D, -1, (const uint8_t *)ent, ent_stride, n_ent,
-             plan_tile_rows);
+// ---------------------------------------- expert-parallel: received slots -> local plan
+// The slots a rank received sit in its exchange window as [world sources][cap slots][row_bytes]; source s filled
+// the first count_s of its slots and then published (count_s, epoch) in hdr[s].  One block waits (bounded) for
+// every source's header of this call, then buckets the valid slots by local expert and writes the work plan:
+// the dispatch step of the layer applied to what arrived.  world * cap <= FRONT_MAX_ENTRIES.
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// hdr word = count | epoch << 32.  Returns the count, or -1 after `limit` polls (status receives `where`).
+__device__ __forceinline__ int ep_wait_hdr(const unsigned long long *hdr, unsigned epoch, unsigned limit, int *status, int where) {
+    for (unsigned i = 0; i < limit; i++) {
+        const unsigned long long v = ld_acquire_sys_u64(hdr);
+        if ((unsigned)(v >> 32) == epoch) return (int)(unsigned)v;
+        if (i > 64) __nanosleep(i < 4096 ? 32 : 256);
+    }
+    atomicCAS(status, 0, where);
+    return -1;
+}
+
+__global__ void __launch_bounds__(1024)
+k_ep_recv_plan(const uint8_t *__restrict__ win, uint64_t off_hdr0, uint64_t off_hdr1, uint64_t off_rows0, uint64_t off_rows1,
+               const int *__restrict__ ctr, int world, int cap, int row_bytes, int eid_off, unsigned limit, int *status,
+               int n_expert, int se0, int se1, int *__restrict__ ecount, int *__restrict__ eoffs, int *__restrict__ elist,
+               int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan, int mt_gu, int mt_dn,
+               int plan_tile_rows, int *__restrict__ counts_out) {
+    Q36_GDS();
+    __shared__ SortSmem sm;
+    __shared__ int s_cnt[64];
+    const int tid = threadIdx.x;
+    const int n = world * cap;
+    const unsigned epoch = (unsigned)(*ctr) + 1u;
+    const bool odd = epoch & 1u;
+    const int used_warps = (n + 31) / 32;
+    for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&sm.cnt[0][0])[i] = 0;
+    if (tid < world) {
+        const unsigned long long *hdr = reinterpret_cast<const unsigned long long *>(win + (odd ? off_hdr1 : off_hdr0)) + tid;
+        const int c = ep_wait_hdr(hdr, epoch, limit, status, 0xB00 + tid);
+        s_cnt[tid] = max(0, min(c, cap));
+        counts_out[tid] = s_cnt[tid];
+    }
+    __syncthreads();
+    int e = -1;
+    if (tid < n && (tid % cap) < s_cnt[tid / cap])
+        e = *reinterpret_cast<const int *>(win + (odd ? off_rows1 : off_rows0) + (size_t)tid * row_bytes + eid_off);
+    sort_entries_block(sm, e, n, n_expert, se0, se1, ecount, eoffs, elist, pos, soffs, s0, s1, plan, mt_gu, mt_dn, plan_tile_rows);
+}
+
+int launch_ep_recv_plan(const void *win, uint64_t off_hdr0, uint64_t off_hdr1, uint64_t off_rows0, uint64_t off_rows1, const int *ctr,
+                        int world, int cap, int row_bytes, int eid_off, unsigned limit, int *status, int n_expert, int se0, int se1,
+                        int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
+                        int plan_tile_rows, int *counts_out, cudaStream_t st) {
+    if (world * cap > FRONT_MAX_ENTRIES || world > 64 || n_expert > DISPATCH_MAX_E) return Q36_MOE_EINVAL;
+    launch_k(k_ep_recv_plan, dim3(1), dim3(1024), 0, st, (const uint8_t *)win, off_hdr0, off_hdr1, off_rows0, off_rows1, ctr, world, cap,
+             row_bytes, eid_off, limit, status, n_expert, se0, se1, ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan,
+             FF / TC_M, D / TC_M, plan_tile_rows, counts_out);
     return check_launch();
 }
 
@@ -415,9 +474,10 @@ int launch_front_small(const float *logits, int n_expert, int k, float scale, in
                        void *plan, int D, int FF, int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs,
                        int shared_row0, int plan_tile_rows, cudaStream_t st) {
     if (T * k > FRONT_MAX_ENTRIES || n_expert > DISPATCH_MAX_E) return Q36_MOE_EINVAL;
+    (void)status;   // (sticky status words: nothing to clear here)
     launch_k(k_front_small, dim3(1), dim3(1024), 0, st, logits, n_expert, k, scale, T, row_stride, se0, se1, idx, wt,
-             ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D,
-             shared_row0, (const uint8_t *)nullptr, 0, 0, plan_tile_rows);
+             ecount, eoffs, elist, pos, soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, X, x_is_bf16, Xq, Xs, D,
+             shared_row0, plan_tile_rows);
     return check_launch();
 }
 
@@ -650,8 +710,9 @@ static int *g_noalloc_ptr[64] = {nullptr};
 
 extern "C" int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entries, int n_expert, int se0, int se1,
                                         int *ecount, int *eoffs, int *elist, int *pos, void *stream) {
-    if (!expert_of_entry || !ecount || !eoffs || !elist || !pos) return Q36_MOE_EINVAL;
-    if (n_entries < 0 || n_expert <= 0 || se0 < 0 || se0 > se1 || se1 > n_expert) return Q36_MOE_EINVAL;
+    if (!ecount || !eoffs || n_entries < 0) return Q36_MOE_EINVAL;
+    if (n_entries > 0 && (!expert_of_entry || !elist || !pos)) return Q36_MOE_EINVAL;   // no entries: nothing to read or place
+    if (n_expert <= 0 || se0 < 0 || se0 > se1 || se1 > n_expert) return Q36_MOE_EINVAL;
     if (n_entries > NOALLOC_MAX_ENTRIES || n_expert > NOALLOC_MAX_EXPERTS) {
         fprintf(stderr,
                 "q36_moe_dispatch_noalloc: %d entries / %d experts exceed the built-in scratch (max %d entries, %d "

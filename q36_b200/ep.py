@@ -10,15 +10,16 @@ the experts, the grouped expert FFN runs on the local shard, one all-to-all
 brings the f32 result rows back, and the home rank does the weighted combine
 and adds its shared expert (replicated on every rank).
 
-Decode-sized steps use a FIXED capacity per peer (C = T*k rows, the worst
-case) so that no count ever has to reach the host: the exchange is two
-equal-split all-to-alls and the whole step stays launch-only.  Slot j of the
-block sent to rank r holds the j-th row (in expert order) routed to r, or is
-marked empty (expert id -1).
+The product path is the native one (`NativeEP`, `LocalEP` -> q36_moe_ep_layer):
+the library's own kernels store the routed rows and the result rows straight
+into the destination rank's exchange window over NVLink, with a capacity of
+rows per pair of ranks fixed when the window is opened, so that no count ever
+has to reach the host and the whole step stays launch-only.
 
-All device work goes through an `ops` object: `DeviceOps` binds the C-ABI
-kernels; the CPU tests substitute an oracle-backed stand-in to exercise the
-index arithmetic and the collectives with gloo.
+`ep_layer` below is the same step written with torch.distributed collectives
+over an `ops` object: `DeviceOps` binds the C-ABI kernels; the CPU tests
+substitute an oracle-backed stand-in to exercise the slot arithmetic and the
+exchange pattern on world-size-2 gloo ranks.
 """
 from __future__ import annotations
 
@@ -135,23 +136,35 @@ def _pad_index(llist: torch.Tensor, R: int) -> torch.Tensor:
     return out
 
 
-class NativeEP:
-    """The C entry point q36_moe_ep_layer: the whole step (kernels and NCCL send/recv) is issued from native
-    code on the current stream; torch.distributed only carries the 128-byte NCCL id at set-up."""
-    # front, quantise, pack, eids, dispatch x3, unpack, plan, gate/up, down, gather, combine (+2 exchanges);
-    # gate/up and down are one launch when no expert can receive more than 16 rows (world * T <= 16)
-    launches_per_layer = 14
+TRANSPORT_PEER, TRANSPORT_NCCL = 0, 1
 
-    def __init__(self, layers, world: int, rank: int, T: int):
+
+def _layer_args(m, ly, X, logits, out, ws):
+    stride = logits.shape[1]
+    return (ly.Wg.data_ptr(), ly.Wu.data_ptr(), ly.Wd.data_ptr(), m.ptr(ly.Sg), m.ptr(ly.Su), m.ptr(ly.Sd), ly.E, ly.k, ly.D,
+            ly.FF, X.data_ptr(), int(X.dtype == torch.bfloat16), logits.data_ptr(), stride, ly.E if stride > ly.E else -1, 1.0,
+            out.data_ptr(), X.shape[0], ws.data_ptr(), ws.numel(), m.stream_ptr())
+
+
+class NativeEP:
+    """One process per GPU.  The C entry point q36_moe_ep_layer issues the whole step from native code on the
+    current stream: the library's kernels store routed rows and result rows straight into the peer ranks'
+    exchange windows (CUDA IPC over NVLink).  torch.distributed only carries the 128-byte NCCL id at set-up; NCCL
+    itself only carries the IPC handles, unless `transport=TRANSPORT_NCCL` asks for the comparison transport."""
+
+    def __init__(self, layers, world: int, rank: int, T: int, transport: int = TRANSPORT_PEER, cap_rows: int = 0):
         import ctypes as C
         from . import moe
         self.moe, self.layers, self.world, self.rank, self.T = moe, layers, world, rank, T
-        # decode sizes: front cluster (route, dispatch, quantise), pack, sort + plan of the received slots, unpack,
-        # FFN (one launch when no expert can receive more than 16 rows, else two), gather, combine
-        small = T <= 16 and world * T * layers[0].k <= 1024
-        one_launch = world * T * layers[0].k + T <= 6300   # the library's switch to the two grouped-GEMM launches
-        self.launches_per_layer = (6 if one_launch else 8) if small else 14   # (one launch: no gather either)
-        dev = layers[0].device
+        ly = layers[0]
+        # kernels per layer step: front (cluster at decode sizes, else router + dispatch x3 + quantise), send, the
+        # received slots' plan, unpack, FFN (one launch up to 6300 rows, else plan + two), return, combine
+        small_front = T <= 16 and T * ly.k <= 128
+        S = world * (cap_rows or T * ly.k)
+        one_launch = S + T <= 6300
+        self.launches_per_layer = (1 if small_front else (2 if T * ly.k <= 1024 else 6)) + 1 + (1 if S <= 1024 else 5) + 1 + \
+            (1 if one_launch else 2) + 1 + 1
+        dev = ly.device
         idt = torch.zeros(128, dtype=torch.uint8)
         if rank == 0:
             buf = (C.c_uint8 * 128)()
@@ -163,20 +176,23 @@ class NativeEP:
         comm = C.c_void_p()
         moe.check(moe.lib.q36_moe_ep_init(idb, rank, world, C.byref(comm)), "ep_init")
         self.comm = comm
-        ly = layers[0]
-        n = int(moe.lib.q36_moe_ep_workspace_bytes(T, world, ly.E, ly.k, ly.D, ly.FF))
+        moe.check(moe.lib.q36_moe_ep_set_transport(comm, transport), "ep_set_transport")
+        moe.check(moe.lib.q36_moe_ep_open_window(comm, T, ly.k, ly.D, cap_rows), "ep_open_window")
+        n = int(moe.lib.q36_moe_ep_workspace_bytes(T, cap_rows, world, ly.E, ly.k, ly.D, ly.FF))
         self.ws = torch.empty(n, dtype=torch.uint8, device=dev)
         moe.check(moe.lib.q36_moe_ws_reset(self.ws.data_ptr(), moe.stream_ptr()), "ws_reset")
 
     def layer(self, ly, X, logits, out):
         m = self.moe
-        stride = logits.shape[1]
-        m.check(m.lib.q36_moe_ep_layer(self.comm, ly.Wg.data_ptr(), ly.Wu.data_ptr(), ly.Wd.data_ptr(), m.ptr(ly.Sg),
-                                       m.ptr(ly.Su), m.ptr(ly.Sd), ly.E, ly.k, ly.D, ly.FF, X.data_ptr(),
-                                       int(X.dtype == torch.bfloat16), logits.data_ptr(), stride,
-                                       ly.E if stride > ly.E else -1, 1.0, out.data_ptr(), X.shape[0], self.ws.data_ptr(),
-                                       self.ws.numel(), m.stream_ptr()), "ep_layer")
+        m.check(m.lib.q36_moe_ep_layer(self.comm, *_layer_args(m, ly, X, logits, out, self.ws)), "ep_layer")
         return out
+
+    def phase(self, p: int, ly, X, logits, out, stream=None):
+        m = self.moe
+        args = list(_layer_args(m, ly, X, logits, out, self.ws))
+        if stream is not None:
+            args[-1] = stream.cuda_stream
+        m.check(m.lib.q36_moe_ep_layer_phase(self.comm, p, *args), f"ep_layer_phase {p}")
 
     def step(self, Xs, Ls, outs):
         for l, ly in enumerate(self.layers):
@@ -189,6 +205,53 @@ class NativeEP:
         if self.comm:
             self.moe.lib.q36_moe_ep_destroy(self.comm)
             self.comm = None
+
+
+class LocalEP:
+    """One process, `world` ranks on the listed devices (q36_moe_ep_init_local), driven from one host thread
+    the way the engine's own multi-GPU driver works (q36_engine.cu:4261-4306).  Listing one device several
+    times makes its ranks take turns on it: the full 2/4/8-rank data path on a single GPU."""
+
+    def __init__(self, world: int, devices, T_max: int, E: int, k: int, D: int, FF: int, cap_rows: int = 0):
+        import ctypes as C
+        from . import moe
+        self.moe, self.world, self.devices = moe, world, list(devices)
+        comms = (C.c_void_p * world)()
+        moe.check(moe.lib.q36_moe_ep_init_local(world, (C.c_int * world)(*self.devices), comms), "ep_init_local")
+        self.comms = [C.c_void_p(c) for c in comms]
+        moe.check(moe.lib.q36_moe_ep_open_window(self.comms[0], T_max, k, D, cap_rows), "ep_open_window")
+        n = int(moe.lib.q36_moe_ep_workspace_bytes(T_max, cap_rows, world, E, k, D, FF))
+        self.ws = []
+        for r in range(world):
+            with torch.cuda.device(self.devices[r]):
+                w = torch.empty(n, dtype=torch.uint8, device=f"cuda:{self.devices[r]}")
+                moe.check(moe.lib.q36_moe_ws_reset(w.data_ptr(), moe.stream_ptr()), "ws_reset")
+            self.ws.append(w)
+
+    def phase(self, p: int, r: int, ly, X, logits, out):
+        m = self.moe
+        with torch.cuda.device(self.devices[r]):
+            return m.lib.q36_moe_ep_layer_phase(self.comms[r], p, *_layer_args(m, ly, X, logits, out, self.ws[r]))
+
+    def layer(self, shards, Xs, Ls, outs):
+        """One call on every rank: phase p of all ranks before phase p + 1 of any."""
+        for p in range(3):
+            for r in range(self.world):
+                self.moe.check(self.phase(p, r, shards[r], Xs[r], Ls[r], outs[r]), f"rank {r} phase {p}")
+        return outs
+
+    def status(self, r: int) -> int:
+        with torch.cuda.device(self.devices[r]):
+            return self.moe.lib.q36_moe_ws_status(self.ws[r].data_ptr(), self.moe.stream_ptr())
+
+    def reset_status(self, r: int):
+        with torch.cuda.device(self.devices[r]):
+            self.moe.check(self.moe.lib.q36_moe_ws_reset(self.ws[r].data_ptr(), self.moe.stream_ptr()), "ws_reset")
+
+    def close(self):
+        for c in reversed(self.comms):      # rank 0 last
+            self.moe.lib.q36_moe_ep_destroy(c)
+        self.comms = []
 
 
 class EPStack:

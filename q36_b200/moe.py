@@ -78,7 +78,11 @@ _SIGS = {
     "q36_moe_ep_unique_id": (i32, [vp]),
     "q36_moe_ep_init": (i32, [vp, i32, i32, C.POINTER(vp)]),
     "q36_moe_ep_destroy": (i32, [vp]),
-    "q36_moe_ep_workspace_bytes": (u64, [i32, i32, i32, i32, i32, i32]),
+    "q36_moe_ep_init_local": (i32, [i32, C.POINTER(i32), C.POINTER(vp)]),
+    "q36_moe_ep_open_window": (i32, [vp, i32, i32, i32, i32]),
+    "q36_moe_ep_set_transport": (i32, [vp, i32]),
+    "q36_moe_ep_workspace_bytes": (u64, [i32, i32, i32, i32, i32, i32, i32]),
+    "q36_moe_ep_layer_phase": (i32, [vp, i32] + [vp] * 6 + [i32] * 4 + [vp, i32, vp, i32, i32, f32, vp, i32, vp, u64, vp]),
     "q36_moe_ep_layer": (i32, [vp] * 7 + [i32] * 4 + [vp, i32, vp, i32, i32, f32, vp, i32, vp, u64, vp]),
     "q36_moe_tc_selftest": (i32, [vp, vp, vp, vp, i32, i32, vp, u64, vp]),
 }

@@ -318,6 +318,18 @@ int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const voi
                        float *host_out, int T, int path, void *dev_io, void *ws, uint64_t ws_bytes,
                        void *stream);
 
+/* A stack of n_layers layers from HOST buffers in one call: host_X [L][T][D], host_logits [L][T][stride] in,
+ * host_out [L][T][D] out (pinned or pageable); Wg..Sd are arrays of n_layers device pointers (Sg/Su/Sd may be
+ * NULL).  Three copies per call (all X, all logits, all outputs) around the layer launches on `stream`, which is
+ * synchronised before returning; reports the device status like q36_moe_layer_host.
+ * dev_io: q36_moe_stack_host_io_bytes(...) bytes of device staging. */
+uint64_t q36_moe_stack_host_io_bytes(int n_layers, int T, int D, int logit_stride, int x_is_bf16);
+int q36_moe_stack_host(int n_layers, const void *const *Wg, const void *const *Wu, const void *const *Wd,
+                       const void *const *Sg, const void *const *Su, const void *const *Sd, int n_expert, int se0,
+                       int se1, int k, int D, int FF, const void *host_X, int x_is_bf16, const float *host_logits,
+                       int logit_stride, int shgate_col, float route_scale, int inc_shared, float *host_out, int T,
+                       int path, void *dev_io, void *ws, uint64_t ws_bytes, void *stream);
+
 /* ---- expert-parallel helpers ----------------------------------------------
  * Row permutation used either side of the all-to-all: dst[i] = src[index[i]]
  * for rows of row_bytes bytes (row_bytes % 16 == 0); index[i] < 0 zero-fills. */
@@ -366,6 +378,14 @@ int q36_moe_ep_layer_phase(void *comm, int phase, const void *Wg, const void *Wu
                            const void *Su, const void *Sd, int n_expert, int k, int D, int FF, const void *X,
                            int x_is_bf16, const float *logits, int logit_stride, int shgate_col,
                            float route_scale, float *out, int T, void *ws, uint64_t ws_bytes, void *stream);
+
+/* q36_moe_stack_host for an expert-parallel stack: this rank's tokens of every layer in, its outputs out. */
+int q36_moe_ep_stack_host(void *comm, int n_layers, const void *const *Wg, const void *const *Wu,
+                          const void *const *Wd, const void *const *Sg, const void *const *Su,
+                          const void *const *Sd, int n_expert, int k, int D, int FF, const void *host_X,
+                          int x_is_bf16, const float *host_logits, int logit_stride, int shgate_col,
+                          float route_scale, float *host_out, int T, void *dev_io, void *ws, uint64_t ws_bytes,
+                          void *stream);
 
 /* ---- tensor-core self-check (the role of test_mma_bs.cu:45-175) ----------
  * Runs 128 x N x K block-scaled tcgen05 tiles on caller data and returns the

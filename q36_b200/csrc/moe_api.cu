@@ -428,6 +428,36 @@ int q36_moe_layer_host(const void *Wg, const void *Wu, const void *Wd, const voi
     return Q36_MOE_OK;
 }
 
+// A stack of layers from host buffers: what a serving loop that keeps activations on the host would call per step.
+int q36_moe_stack_host(int n_layers, const void *const *Wg, const void *const *Wu, const void *const *Wd, const void *const *Sg,
+                       const void *const *Su, const void *const *Sd, int n_expert, int se0, int se1, int k, int D, int FF,
+                       const void *host_X, int x_is_bf16, const float *host_logits, int logit_stride, int shgate_col,
+                       float route_scale, int inc_shared, float *host_out, int T, int path, void *dev_io, void *ws,
+                       uint64_t ws_bytes, void *stream) {
+    if (n_layers <= 0 || !Wg || !Wu || !Wd || !host_X || !host_logits || !host_out || !dev_io || T <= 0) return Q36_MOE_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint64_t xb = (uint64_t)T * D * (x_is_bf16 ? 2 : 4), lb = (uint64_t)T * logit_stride * 4, ob = (uint64_t)T * D * 4;
+    // device staging: all layers' X, then all logits, then all outputs: three copies per step
+    uint8_t *dX = (uint8_t *)dev_io, *dL = dX + al(xb * n_layers), *dO = dL + al(lb * n_layers);
+    int rc;
+    if ((rc = ck(cudaMemcpyAsync(dX, host_X, xb * n_layers, cudaMemcpyHostToDevice, st)))) return rc;
+    if ((rc = ck(cudaMemcpyAsync(dL, host_logits, lb * n_layers, cudaMemcpyHostToDevice, st)))) return rc;
+    for (int l = 0; l < n_layers; l++)
+        if ((rc = layer_impl(Wg[l], Wu[l], Wd[l], Sg ? Sg[l] : nullptr, Su ? Su[l] : nullptr, Sd ? Sd[l] : nullptr, n_expert, se0, se1,
+                             k, D, FF, dX + xb * l, x_is_bf16, (const float *)(dL + lb * l), logit_stride, shgate_col, route_scale,
+                             inc_shared, (float *)(dO + ob * l), nullptr, nullptr, T, path, ws, ws_bytes, st)))
+            return rc;
+    if ((rc = ck(cudaMemcpyAsync(host_out, dO, ob * n_layers, cudaMemcpyDeviceToHost, st)))) return rc;
+    if ((rc = ck(cudaStreamSynchronize(st)))) return rc;
+    if (pick_path(path, T) == Q36_MOE_PATH_TC) return q36_moe_ws_status(ws, stream);
+    return Q36_MOE_OK;
+}
+uint64_t q36_moe_stack_host_io_bytes(int n_layers, int T, int D, int logit_stride, int x_is_bf16) {
+    if (n_layers <= 0 || T <= 0) return 0;
+    return al((uint64_t)n_layers * T * D * (x_is_bf16 ? 2 : 4)) + al((uint64_t)n_layers * T * logit_stride * 4) +
+           al((uint64_t)n_layers * T * D * 4);
+}
+
 int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes, void *stream) {
     if (!src || !index || !dst || row_bytes % 16 || n_rows < 0) return Q36_MOE_EINVAL;
     return launch_gather_rows(src, index, dst, n_rows, row_bytes, (cudaStream_t)stream);

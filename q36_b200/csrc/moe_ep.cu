@@ -680,4 +680,30 @@ int q36_moe_ep_layer(void *comm, const void *Wg, const void *Wu, const void *Wd,
     return Q36_MOE_OK;
 }
 
+// The expert-parallel stack from host buffers (this rank's tokens of every layer): three copies per step around
+// n_layers calls of the layer step.  dev_io: q36_moe_stack_host_io_bytes(...) bytes.
+int q36_moe_ep_stack_host(void *comm, int n_layers, const void *const *Wg, const void *const *Wu, const void *const *Wd,
+                          const void *const *Sg, const void *const *Su, const void *const *Sd, int n_expert, int k, int D, int FF,
+                          const void *host_X, int x_is_bf16, const float *host_logits, int logit_stride, int shgate_col,
+                          float route_scale, float *host_out, int T, void *dev_io, void *ws, uint64_t ws_bytes, void *stream) {
+    EpComm *c = (EpComm *)comm;
+    if (!c || n_layers <= 0 || !Wg || !Wu || !Wd || !host_X || !host_logits || !host_out || !dev_io || T <= 0) return Q36_MOE_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const uint64_t xb = (uint64_t)T * D * (x_is_bf16 ? 2 : 4), lb = (uint64_t)T * logit_stride * 4, ob = (uint64_t)T * D * 4;
+    uint8_t *dX = (uint8_t *)dev_io, *dL = dX + al256(xb * n_layers), *dO = dL + al256(lb * n_layers);
+    int rc;
+    if ((rc = ckc(cudaMemcpyAsync(dX, host_X, xb * n_layers, cudaMemcpyHostToDevice, st)))) return rc;
+    if ((rc = ckc(cudaMemcpyAsync(dL, host_logits, lb * n_layers, cudaMemcpyHostToDevice, st)))) return rc;
+    for (int l = 0; l < n_layers; l++) {
+        const LayerArgs a{Wg[l], Wu[l], Wd[l], Sg ? Sg[l] : nullptr, Su ? Su[l] : nullptr, Sd ? Sd[l] : nullptr, n_expert, k, D, FF,
+                          dX + xb * l, x_is_bf16, (const float *)(dL + lb * l), logit_stride, shgate_col, route_scale,
+                          (float *)(dO + ob * l), T, ws, ws_bytes};
+        for (int phase = 0; phase < 3; phase++)
+            if ((rc = ep_phase(c, phase, a, st))) return rc;
+    }
+    if ((rc = ckc(cudaMemcpyAsync(host_out, dO, ob * n_layers, cudaMemcpyDeviceToHost, st)))) return rc;
+    if ((rc = ckc(cudaStreamSynchronize(st)))) return rc;
+    return q36_moe_ws_status(ws, stream);
+}
+
 }  // extern "C"

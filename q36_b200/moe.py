@@ -74,6 +74,9 @@ _SIGS = {
     "q36_moe_block": (i32, [vp] * 6 + [i32] * 6 + [vp, vp, vp, f32, f32, i32, vp, vp, vp, vp, i32, vp, u64, vp]),
     "q36_moe_host_io_bytes": (u64, [i32, i32, i32, i32]),
     "q36_moe_layer_host": (i32, [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, i32, vp, vp, u64, vp]),
+    "q36_moe_stack_host_io_bytes": (u64, [i32, i32, i32, i32, i32]),
+    "q36_moe_stack_host": (i32, [i32] + [vp] * 6 + [i32] * 6 + [vp, i32, vp, i32, i32, f32, i32, vp, i32, i32, vp, vp, u64, vp]),
+    "q36_moe_ep_stack_host": (i32, [vp, i32] + [vp] * 6 + [i32] * 4 + [vp, i32, vp, i32, i32, f32, vp, i32, vp, vp, u64, vp]),
     "q36_moe_gather_rows": (i32, [vp, vp, vp, i32, i32, vp]),
     "q36_moe_ep_unique_id": (i32, [vp]),
     "q36_moe_ep_init": (i32, [vp, i32, i32, C.POINTER(vp)]),
@@ -449,3 +452,40 @@ class MoELayer:
                                      int(inc_shared), out.data_ptr(), T, path, self._io.data_ptr(), ws.data_ptr(),
                                      ws.numel(), stream_ptr(stream)), "moe_layer_host")
         return out
+
+
+class HostStack:
+    """q36_moe_stack_host / q36_moe_ep_stack_host: a stack of layers driven from pinned host buffers, one call
+    per step (inputs copied in, results copied out, stream synchronised)."""
+
+    def __init__(self, layers, T: int, x_is_bf16: bool = True, logit_stride: int | None = None, ep=None):
+        self.layers, self.T, self.ep = layers, T, ep
+        ly = layers[0]
+        self.stride = (ly.E + 1) if logit_stride is None else logit_stride
+        self.bf16 = x_is_bf16
+        n = len(layers)
+        arr = lambda ts: (vp * n)(*[ptr(t) for t in ts])
+        self.planes = [arr([l.Wg for l in layers]), arr([l.Wu for l in layers]), arr([l.Wd for l in layers]),
+                       arr([l.Sg for l in layers]), arr([l.Su for l in layers]), arr([l.Sd for l in layers])]
+        self.has_shared = ly.Sg is not None
+        io = int(lib.q36_moe_stack_host_io_bytes(n, T, ly.D, self.stride, int(x_is_bf16)))
+        self.io = torch.empty(io, dtype=torch.uint8, device=ly.device)
+        self.ws = ep.ws if ep is not None else ly.workspace(T)
+
+    def step(self, hX: torch.Tensor, hL: torch.Tensor, hO: torch.Tensor, path: int = PATH_AUTO):
+        """hX [L,T,D], hL [L,T,stride], hO [L,T,D]: CPU tensors (pinned for speed).  Synchronous."""
+        ly, n = self.layers[0], len(self.layers)
+        P = self.planes
+        sh = P[3:] if self.has_shared else [None, None, None]
+        gate_col = ly.E if self.stride > ly.E else -1
+        if self.ep is None:
+            check(lib.q36_moe_stack_host(n, P[0], P[1], P[2], sh[0], sh[1], sh[2], ly.E, ly.se0, ly.se1, ly.k, ly.D, ly.FF,
+                                         hX.data_ptr(), int(self.bf16), hL.data_ptr(), self.stride, gate_col, 1.0, 1,
+                                         hO.data_ptr(), self.T, path, self.io.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
+                                         stream_ptr()), "stack_host")
+        else:
+            check(lib.q36_moe_ep_stack_host(self.ep.comm, n, P[0], P[1], P[2], sh[0], sh[1], sh[2], ly.E, ly.k, ly.D, ly.FF,
+                                            hX.data_ptr(), int(self.bf16), hL.data_ptr(), self.stride, gate_col, 1.0,
+                                            hO.data_ptr(), self.T, self.io.data_ptr(), self.ws.data_ptr(), self.ws.numel(),
+                                            stream_ptr()), "ep_stack_host")
+        return hO

@@ -91,5 +91,5 @@ def test_ep_layer_across_gpus(world):
     for rank, worst in res:
         for case, err in worst.items():
             # same quantised rows, same kernels; only the summation grouping differs from the single-GPU layer
-            tol = 5e-4 if "T=448" in case else 1e-5     # (448 tokens: other FFN kernels than the single-GPU layer takes)
+            tol = 2e-3 if "T=448" in case else 1e-5     # (448 tokens: other FFN kernels than the single-GPU layer takes)
             assert err < tol, f"world {world} rank {rank} {case}: rel-L2 vs single-GPU layer {err}"

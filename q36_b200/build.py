@@ -30,7 +30,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, "-ccbin", "g++", *[os.path.join(CSRC, s) for s in SOURCES], "-o", LIB]
+    extra = os.environ.get("Q36_NVCC_EXTRA", "").split()      # e.g. -DQ36_TRACE for the kernels' timing trace
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-ccbin", "g++", *[os.path.join(CSRC, s) for s in SOURCES], "-o", LIB]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode:
         sys.stderr.write(r.stdout + r.stderr)

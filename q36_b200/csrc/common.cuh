@@ -20,6 +20,35 @@
         cudaGridDependencySynchronize();         \
     } while (0)
 
+// Optional timing trace (compile with -DQ36_TRACE): thread 0 of block 0 of an instrumented kernel adds its own
+// duration and the gap since the previous instrumented kernel ended to counters kept behind the status words of the
+// workspace (u64 slots from byte 64: [0] last end, [1 + id] duration, [9 + id] gap before, [17 + id] launches).
+#ifdef Q36_TRACE
+__device__ __forceinline__ unsigned long long q36_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define Q36_TR_BEGIN(st, kid)                                                                  \
+    unsigned long long tr_t0 = 0;                                                              \
+    if ((st) && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {                      \
+        tr_t0 = q36_globaltimer();                                                             \
+        unsigned long long *tr = reinterpret_cast<unsigned long long *>((st) + 16);            \
+        if (tr[0]) tr[9 + (kid)] += tr_t0 - tr[0];                                             \
+    }
+#define Q36_TR_END(st, kid)                                                                    \
+    if ((st) && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {                      \
+        const unsigned long long tr_t1 = q36_globaltimer();                                    \
+        unsigned long long *tr = reinterpret_cast<unsigned long long *>((st) + 16);            \
+        tr[1 + (kid)] += tr_t1 - tr_t0;                                                        \
+        tr[0] = tr_t1;                                                                         \
+        tr[17 + (kid)] += 1;                                                                   \
+    }
+#else
+#define Q36_TR_BEGIN(st, kid)
+#define Q36_TR_END(st, kid)
+#endif
+
 namespace q36 {
 
 // Last CUDA error seen by an entry point of this thread (0 = none).

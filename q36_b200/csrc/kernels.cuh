@@ -6,6 +6,24 @@
 
 namespace q36 {
 
+// Expert-parallel hooks of the two decode-sized kernels (all pointers device memory; peers == nullptr: not used).
+// Windows: peers[r] is rank r's exchange window as mapped on this device; offsets are the same on every rank and
+// come in pairs indexed by the parity of the call number ctl[0] + 1.  slot_major: index the slot blocks by the
+// OTHER rank instead of this one (local staging for the NCCL transport).
+struct EpSendArgs {     // front end: quantised rows straight into the destination ranks' windows
+    uint8_t *const *peers;
+    uint64_t rows0, rows1, hdr0, hdr1;
+    int *ctl, *ypos;
+    int me, world, per, cap, slot_major;
+};
+struct EpReturnArgs {   // FFN: result rows of the sorted rows [0, n_map) straight into their home ranks' windows
+    uint8_t *const *peers;
+    uint64_t ret0, ret1, rhdr0, rhdr1;
+    int *ctl;
+    const int *rowmap;  // sorted row -> received slot (source rank * cap + j)
+    int n_map, me, world, cap, slot_major;
+};
+
 constexpr int DISPATCH_MAX_GROUPS = 512;  // upper bound on expert groups per call
 
 bool router_supports(int n_expert);   // moe_api.cu: expert counts the router kernels are built for
@@ -27,7 +45,7 @@ int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K
 int launch_front_decode(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int *idx, float *wt,
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
                         int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0, int put_k,
-                        cudaStream_t st);
+                        cudaStream_t st, const EpSendArgs *ep = nullptr);
 // expert-parallel: wait (bounded) for every source rank's header of this call in the exchange window, bucket the
 // received slots by local expert, write the work plan; counts_out[world] receives the per-source slot counts
 int launch_ep_recv_plan(const void *win, uint64_t off_hdr0, uint64_t off_hdr1, uint64_t off_rows0, uint64_t off_rows1, const int *ctr,
@@ -91,10 +109,10 @@ int ensure_smem_attr(const void *kernel, int bytes, bool *done);
 
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
 bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF);   // does launch_ffn_fused_small take this call?
+int ffn_fused_small_grid(int R_max, int n_group, int D, int FF);   // CTAs of that launch
 int fused_rows_limit();            // policy: rows up to which that kernel is preferred when groups may exceed 16 rows   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
-                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const int *rowmap, float *Ymap,
-                           int n_map, cudaStream_t st);
+                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const EpReturnArgs *ep, cudaStream_t st);
 
 }  // namespace q36

@@ -147,7 +147,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
             return rc;
         if (decode_kernel) {
             if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
-                                             ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, nullptr, nullptr, 0, st)))
+                                             ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, nullptr, st)))
                 return rc;
         } else {
         if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, ng, R, T, w.Xq, w.Xs, w.Hq, w.Hs,
@@ -296,7 +296,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : 0, st))) return rc;
     if (one_launch)
         return launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, n_group,
-                                      R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, nullptr, nullptr, 0, st);
+                                      R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, nullptr, st);
     const int mgr = max_group_rows > 0 ? max_group_rows : R_max;
     if ((stages & 1) && (rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, n_group, R_max,
                                                mgr, Xq_rows, Xs_rows, Hq_rows, Hs_rows, D, FF, plan, status, st)))

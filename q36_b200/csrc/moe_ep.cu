@@ -87,7 +87,7 @@ static WinLayout win_layout(int world, int cap, int D) {
     uint64_t o = 0;
     auto take = [&](uint64_t b) { const uint64_t r = o; o += (b + 255) & ~(uint64_t)255; return r; };
     for (int p = 0; p < 2; p++) { L.hdr[p] = take(8 * EP_MAX_WORLD); L.rhdr[p] = take(8 * EP_MAX_WORLD); }
-    L.ctl = take(256);   // [0] call counter, [1..3] tickets of the three "last block" patterns
+    L.ctl = take(256);   // ints: [0] call counter, [3] ticket of the combine, [8 + r] / [8 + 16 + s] tickets per destination / source
     for (int p = 0; p < 2; p++) L.rows[p] = take((uint64_t)world * cap * L.row_bytes);
     for (int p = 0; p < 2; p++) L.ret[p] = take((uint64_t)world * cap * D * 4);
     L.bytes = o;
@@ -132,51 +132,74 @@ __device__ __forceinline__ int wait_hdr(const unsigned long long *hdr, unsigned 
 }
 
 // ------------------------------------------------------------------ kernels
-// One block per sorted row s (entry elist[s], expert e, destination rank r = e / per, j-th row for r): the
-// quantised row of its token + the expert id go to slot (me, j) of r's window.  The last block to finish
-// publishes (count_r, epoch) in every destination.  ypos[entry] = r * cap + j: where the result comes back.
-// slot_major_dst: NCCL transport, the "peers" are local staging blocks indexed by DESTINATION instead.
-__global__ void __launch_bounds__(128)
+// Blocks (r, b), b < nb: block b of destination rank r copies the rows j = b, b + nb, ... that this rank routed to r
+// (sorted rows eoffs[r * per] + j: entry elist[.], expert e) -- the quantised row of the entry's token + the expert
+// id -- into slot (me, j) of r's window, then publishes (count_r, epoch) there: thread 0 after the block barrier
+// with one system-scope fence (the barrier orders the other threads' stores before it).  With several blocks
+// per destination the last one to arrive at the destination's ticket publishes.  ypos[entry] = r * cap + j: where
+// the result row comes back.  slot_major_dst: NCCL transport, "peers" are local staging blocks indexed by
+// DESTINATION instead.
+__global__ void __launch_bounds__(1024)
 k_ep_send(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const int *__restrict__ idx,
           const int *__restrict__ eoffs, const int *__restrict__ elist, int world, int per, int k, int cap, int D,
           uint8_t *const *__restrict__ peers, int me, uint64_t rows0, uint64_t rows1, uint64_t hdr0, uint64_t hdr1, int *ctl,
-          int *__restrict__ ypos, int slot_major_dst, int *status) {
+          int *__restrict__ ypos, int slot_major_dst, int *status, int nb) {
     Q36_GDS();
-    const int s = blockIdx.x;
+    Q36_TR_BEGIN(status, 1)
+    const int r = blockIdx.x / nb, b = blockIdx.x % nb;
     const unsigned epoch = (unsigned)ctl[0] + 1u;
     const bool odd = epoch & 1u;
     const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_TAIL;
-    const int entry = elist[s], t = entry / k, e = idx[entry], r = e / per;
-    const int j = s - eoffs[r * per];
-    if (j < cap) {
-        uint8_t *dst = peers[r] + (odd ? rows1 : rows0) + ((size_t)(slot_major_dst ? r : me) * cap + j) * row_bytes;
-        const uint4 *sq = reinterpret_cast<const uint4 *>(Xq + (size_t)t * D);
-        for (int i = threadIdx.x; i < D / 16; i += blockDim.x) reinterpret_cast<uint4 *>(dst)[i] = sq[i];
-        const uint4 *ss = reinterpret_cast<const uint4 *>(Xs + (size_t)t * nbs);
-        for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) reinterpret_cast<uint4 *>(dst + D)[i] = ss[i];
-        if (threadIdx.x == 0) {
-            *reinterpret_cast<int4 *>(dst + D + nbs) = make_int4(e, 0, 0, 0);
-            ypos[entry] = r * cap + j;
+    const int base = eoffs[r * per], cnt_all = eoffs[(r + 1) * per] - base, cnt = min(cap, cnt_all);
+    uint8_t *dst0 = peers[r] + (odd ? rows1 : rows0) + (size_t)(slot_major_dst ? r : me) * cap * row_bytes;
+    const int u4_row = D / 16, u4_all = u4_row + nbs / 16;
+    // flat over the 16-byte units of this block's rows (codes, then scale bytes; the tail separately), four loads
+    // in flight per thread before the (remote) stores
+    const int my_rows = cnt > b ? (cnt - b + nb - 1) / nb : 0;      // rows j = b + nb * q, q < my_rows
+    const int total = my_rows * u4_all;
+    for (int x0 = threadIdx.x; x0 < total; x0 += 4 * blockDim.x) {
+        uint4 v[4];
+        uint4 *dptr[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int x = x0 + u * blockDim.x;
+            dptr[u] = nullptr;
+            if (x < total) {
+                const int q = x / u4_all, i = x - q * u4_all, j = b + nb * q;
+                const int t = elist[base + j] / k;
+                v[u] = (i < u4_row) ? reinterpret_cast<const uint4 *>(Xq + (size_t)t * D)[i]
+                                    : reinterpret_cast<const uint4 *>(Xs + (size_t)t * nbs)[i - u4_row];
+                dptr[u] = reinterpret_cast<uint4 *>(dst0 + (size_t)j * row_bytes) + i;
+            }
         }
-    } else if (threadIdx.x == 0) {
-        ypos[entry] = -1;                       // beyond the window's capacity: dropped, and reported
-        atomicCAS(status, 0, 0xD00);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (dptr[u]) *dptr[u] = v[u];
     }
-    __threadfence_system();
+    for (int q = threadIdx.x; q * nb + b < cnt_all; q += blockDim.x) {   // per row: the tail and the return position
+        const int j = b + nb * q, entry = elist[base + j];
+        if (j < cnt) {
+            *reinterpret_cast<int4 *>(dst0 + (size_t)j * row_bytes + D + nbs) = make_int4(idx[entry], 0, 0, 0);
+            ypos[entry] = r * cap + j;
+        } else {                                 // beyond the window's capacity: dropped, and reported
+            ypos[entry] = -1;
+            atomicCAS(status, 0, 0xD00);
+        }
+    }
     __syncthreads();
-    __shared__ int s_last;
-    if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 1, 1) == (int)gridDim.x - 1);
-    __syncthreads();
-    if (s_last) {
-        __threadfence_system();
-        if (threadIdx.x < world) {
-            const int rr = threadIdx.x;
-            const int cnt = min(cap, eoffs[(rr + 1) * per] - eoffs[rr * per]);
-            unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[rr] + (odd ? hdr1 : hdr0)) + (slot_major_dst ? rr : me);
+    if (threadIdx.x == 0) {
+        bool publish = true;
+        if (nb > 1) {
+            __threadfence_system();
+            publish = atomicAdd(ctl + 8 + r, 1) == nb - 1;
+            if (publish) ctl[8 + r] = 0;
+        }
+        if (publish) {   // (a release store: one system-scope fence, ordered after the whole block's stores by the barrier)
+            unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[r] + (odd ? hdr1 : hdr0)) + (slot_major_dst ? r : me);
             st_release_sys_u64(h, (unsigned long long)(unsigned)cnt | ((unsigned long long)epoch << 32));
         }
-        if (threadIdx.x == 0) ctl[1] = 0;
     }
+    Q36_TR_END(status, 1)
 }
 
 // Received slots beyond FRONT_MAX_ENTRIES: wait for the headers in every block, then list each slot's expert id
@@ -206,8 +229,9 @@ k_ep_wait_eids(const uint8_t *__restrict__ win, uint64_t hdr0, uint64_t hdr1, ui
 __global__ void __launch_bounds__(128)
 k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, const int *ctl, const int *__restrict__ llist,
             const int *__restrict__ loffs_end, const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, int R, int T, int D,
-            uint8_t *__restrict__ rows_q, uint8_t *__restrict__ rows_s) {
+            uint8_t *__restrict__ rows_q, uint8_t *__restrict__ rows_s, int *status) {
     Q36_GDS();
+    Q36_TR_BEGIN(status, 3)
     const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_TAIL;
     const bool odd = ((unsigned)ctl[0] + 1u) & 1u;
     const uint8_t *recv = win + (odd ? rows1 : rows0);
@@ -226,41 +250,51 @@ k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, con
         for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dq[i] = reinterpret_cast<const uint4 *>(sq)[i];
         for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) ds[i] = reinterpret_cast<const uint4 *>(ss)[i];
     }
+    Q36_TR_END(status, 3)
 }
 
-// One block per received slot (source rank s, j): its result row Y[lpos[slot]] goes to slot (me, j) of the
-// result area in s's window; the last block publishes the epoch in every source rank.
-__global__ void __launch_bounds__(256)
+// Blocks (s, b), b < nb: block b of source rank s copies the result rows of the slots j = b, b + nb, ... that s
+// filled (Y[lpos[s * cap + j]]) into slot (me, j) of the result area in s's window, then publishes the epoch there
+// (same pattern as k_ep_send).
+__global__ void __launch_bounds__(1024)
 k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int *__restrict__ counts, int world, int cap, int D,
             uint8_t *const *__restrict__ peers, int me, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1, int *ctl,
-            int slot_major_dst) {
+            int slot_major_dst, int nb, int *status) {
     Q36_GDS();
+    Q36_TR_BEGIN(status, 5)
+    const int s = blockIdx.x / nb, b = blockIdx.x % nb;
     const unsigned epoch = (unsigned)ctl[0] + 1u;
     const bool odd = epoch & 1u;
-    // work items: the filled slots of every source, (s, j) with j < counts[s], numbered source by source
-    int total = 0;
-    for (int s = 0; s < world; s++) total += counts[s];
-    for (int x = blockIdx.x; x < total; x += gridDim.x) {
-        int s = 0, j = x;
-        while (j >= counts[s]) { j -= counts[s]; s++; }
-        const int p = lpos[s * cap + j];
-        float4 *dst = reinterpret_cast<float4 *>(peers[s] + (odd ? ret1 : ret0) + ((size_t)(slot_major_dst ? s : me) * cap + j) * D * 4);
-        const float4 *src = reinterpret_cast<const float4 *>(Y + (size_t)(p < 0 ? 0 : p) * D);
-        for (int i = threadIdx.x; i < D / 4; i += blockDim.x) dst[i] = (p >= 0) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    __threadfence_system();
-    __syncthreads();
-    __shared__ int s_last;
-    if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 2, 1) == (int)gridDim.x - 1);
-    __syncthreads();
-    if (s_last) {
-        __threadfence_system();
-        if (threadIdx.x < world) {
-            unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[threadIdx.x] + (odd ? rhdr1 : rhdr0)) + (slot_major_dst ? threadIdx.x : me);
-            st_release_sys_u64(h, (unsigned long long)epoch << 32);
+    const int cnt = counts[s];
+    float4 *dst0 = reinterpret_cast<float4 *>(peers[s] + (odd ? ret1 : ret0) + (size_t)(slot_major_dst ? s : me) * cap * D * 4);
+    const int f4 = D / 4;
+    const int my_rows = cnt > b ? (cnt - b + nb - 1) / nb : 0;
+    const int total = my_rows * f4;
+    for (int x0 = threadIdx.x; x0 < total; x0 += 4 * blockDim.x) {
+        float4 v[4];
+        float4 *dptr[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int x = x0 + u * blockDim.x;
+            dptr[u] = nullptr;
+            if (x < total) {
+                const int q = x / f4, i = x - q * f4, j = b + nb * q;
+                const int p = lpos[s * cap + j];
+                v[u] = (p >= 0) ? reinterpret_cast<const float4 *>(Y + (size_t)p * D)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                dptr[u] = dst0 + (size_t)j * f4 + i;
+            }
         }
-        if (threadIdx.x == 0) ctl[2] = 0;
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (dptr[u]) *dptr[u] = v[u];
     }
+    __syncthreads();
+    if (threadIdx.x == 0) {   // one system-scope fence (the barrier ordered the block's stores before it), then count this block in at s
+        __threadfence_system();
+        unsigned *h = reinterpret_cast<unsigned *>(peers[s] + (odd ? rhdr1 : rhdr0) + 8 * (slot_major_dst ? s : me));
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(h) : "memory");
+    }
+    Q36_TR_END(status, 5)
 }
 
 // k_moe_combine_pf (q36_engine.cu:3393-3401) on the home rank: waits (bounded) for every expert rank's results of
@@ -269,13 +303,24 @@ k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int
 __global__ void __launch_bounds__(256)
 k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1,
              int *ctl, int world, unsigned limit, int *status, const int *__restrict__ ypos, const float *__restrict__ wt,
-             const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k) {
+             const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k, unsigned expected) {
+    // expected: arrivals every expert rank counts in at this rank's result header per call (the CTAs of its FFN
+    // launch, or the blocks per source of its return kernel: the same on every rank for equal sizes)
     Q36_GDS();
+    Q36_TR_BEGIN(status, 6)
     const unsigned epoch = (unsigned)ctl[0] + 1u;
     const bool odd = epoch & 1u;
-    if (threadIdx.x < world)
-        wait_hdr(reinterpret_cast<const unsigned long long *>(win + (odd ? rhdr1 : rhdr0)) + threadIdx.x, epoch, limit, status,
-                 0xC00 + threadIdx.x);
+    if (threadIdx.x < world) {
+        const unsigned *h = reinterpret_cast<const unsigned *>(win + (odd ? rhdr1 : rhdr0) + 8 * threadIdx.x);
+        bool ok = false;
+        for (unsigned i = 0; i < limit && !ok; i++) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(h) : "memory");
+            ok = v >= expected;
+            if (!ok && i > 64) __nanosleep(i < 4096 ? 32 : 256);
+        }
+        if (!ok) atomicCAS(status, 0, 0xC00 + threadIdx.x);
+    }
     __syncthreads();
     const float *Y = reinterpret_cast<const float *>(win + (odd ? ret1 : ret0));
     const int t = blockIdx.y;
@@ -313,7 +358,12 @@ k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t 
     __shared__ int s_last;
     if (threadIdx.x == 0) s_last = (atomicAdd(ctl + 3, 1) == (int)(gridDim.x * gridDim.y) - 1);
     __syncthreads();
-    if (s_last && threadIdx.x == 0) { ctl[3] = 0; ctl[0] = (int)epoch; }   // the call is over: next call, other parity
+    if (s_last) {   // the call is over: clear this parity's arrival counts (their next use is two calls away), next call
+        if (threadIdx.x < world) *reinterpret_cast<unsigned long long *>(const_cast<uint8_t *>(win) + (odd ? rhdr1 : rhdr0) + 8 * threadIdx.x) = 0ull;
+        __syncthreads();
+        if (threadIdx.x == 0) { ctl[3] = 0; ctl[0] = (int)epoch; }
+    }
+    Q36_TR_END(status, 6)
 }
 
 static inline uint64_t al256(uint64_t x) { return (x + 255) & ~(uint64_t)255; }
@@ -429,8 +479,10 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         // once, in token order (hw order inside the blocks): one cluster launch at decode sizes
         const bool cluster_front = T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
         if (cluster_front) {
+            // ... and the rows go straight from the quantising warps into the destination ranks' windows
+            const EpSendArgs sa{(uint8_t *const *)c->d_peer, L.rows[0], L.rows[1], L.hdr[0], L.hdr[1], ctl, w.ypos, rank, world, per, C, use_nccl ? 1 : 0};
             if ((rc = launch_front_decode(a.logits, E, k, a.route_scale, T, a.logit_stride, w.idx, w.wt, w.ecount, w.eoffs, w.elist,
-                                          w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, a.X, a.x_is_bf16, w.Xq, w.Xs, 0, 0, st)))
+                                          w.pos, nullptr, 0, 0, nullptr, D, FF, w.status, a.X, a.x_is_bf16, w.Xq, w.Xs, 0, 0, st, &sa)))
                 return rc;
         } else if (n <= 1024) {
             if ((rc = launch_front_small(a.logits, E, k, a.route_scale, T, a.logit_stride, 0, E, w.idx, w.wt, w.ecount, w.eoffs,
@@ -441,9 +493,11 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             if ((rc = launch_dispatch(w.idx, n, E, 0, E, w.ecount, w.eoffs, w.elist, w.pos, w.disp, nullptr, 0, 0, st))) return rc;
         }
         if (!cluster_front && (rc = launch_quant(a.X, a.x_is_bf16, w.Xq, w.Xs, T, D, nullptr, 0, 0, true, st))) return rc;
-        launch_k(k_ep_send, dim3(n), dim3(128), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
+        // (larger calls: a kernel of its own.)  Blocks per destination: one up to 256 rows, then one per 256 (at most 32)
+        const int nb_send = max(1, min(32, (min(n, C) + 255) / 256));
+        if (!cluster_front) launch_k(k_ep_send, dim3(world * nb_send), dim3(1024), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
                  (const int *)w.eoffs, (const int *)w.elist, world, per, k, C, D, (uint8_t *const *)c->d_peer, rank, L.rows[0], L.rows[1],
-                 L.hdr[0], L.hdr[1], ctl, w.ypos, use_nccl ? 1 : 0, w.status);
+                 L.hdr[0], L.hdr[1], ctl, w.ypos, use_nccl ? 1 : 0, w.status, nb_send);
         if ((rc = check_launch())) return rc;
         if (use_nccl) {   // staging blocks (indexed by destination) -> the destinations' windows (indexed by source)
             if ((rc = all_to_all(api, c, c->stage + L.rows[par], c->win + L.rows[par], (size_t)C * rowb, st))) return rc;
@@ -468,15 +522,18 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
                 return rc;
         }
         launch_k(k_ep_unpack, dim3(min(R + T, 8 * sm_count())), dim3(128), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,
-                 (const int *)w.llist, (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s);
+                 (const int *)w.llist, (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s, w.status);
         if ((rc = check_launch())) return rc;
         // grouped expert FFN on the local shard (+ shared expert on the own tokens)
         const int *goffs = w.loffs + se0;
         if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, one_launch ? 16 : 0, st)))
             return rc;
         if (one_launch) {
+            // its down epilogue stores the routed result rows straight into their home ranks' windows and its last CTA
+            // publishes; the shared expert's rows stay in Y for the combine
+            const EpReturnArgs ra{(uint8_t *const *)c->d_peer, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, w.llist, R, rank, world, C, use_nccl ? 1 : 0};
             if ((rc = launch_ffn_fused_small(a.Wg, a.Wu, a.Wd, shared ? a.Sg : nullptr, shared ? a.Su : nullptr, shared ? a.Sd : nullptr,
-                                             per, R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, nullptr, nullptr, 0, st)))
+                                             per, R + T, w.rows_q, w.rows_s, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status, &ra, st)))
                 return rc;
         } else {
             if ((rc = launch_gateup_tc(a.Wg, a.Wu, shared ? a.Sg : nullptr, shared ? a.Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
@@ -485,21 +542,28 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             if ((rc = launch_down_tc(a.Wd, shared ? a.Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
                 return rc;
         }
-        // result rows straight into their home ranks' windows
-        launch_k(k_ep_return, dim3(min(S, 8 * sm_count())), dim3(256), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
-                 (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0);
+        // (two launches: a kernel of its own puts the result rows into their home ranks' windows)
+        // blocks per source: one while a pair of ranks exchanges at most 64 rows (a single fence on the way), else one per 64
+        const int nb_ret = max(1, min(32, (min(c->T_max * k, C) + 63) / 64));
+        if (!one_launch) launch_k(k_ep_return, dim3(world * nb_ret), dim3(1024), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
+                 (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0, nb_ret, w.status);
         if ((rc = check_launch())) return rc;
         if (use_nccl) {
             if ((rc = all_to_all(api, c, c->stage + L.ret[par], c->win + L.ret[par], (size_t)C * D * 4, st))) return rc;
             if ((rc = all_to_all(api, c, c->stage + L.rhdr[par], c->win + L.rhdr[par], 8, st))) return rc;
+            if ((rc = ckc(cudaMemsetAsync(c->stage + L.rhdr[par], 0, 8 * EP_MAX_WORLD, st)))) return rc;   // the staged arrival counts start at zero next time
         }
         return Q36_MOE_OK;
     }
     if (phase == 2) {
+        // what every expert rank counts in at this rank per call: the CTAs of its one-launch FFN, else its return blocks
+        const bool peers_one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
+        const unsigned expected = peers_one_launch ? (unsigned)ffn_fused_small_grid(R + T, per, D, FF)
+                                                   : (unsigned)max(1, min(32, (min(c->T_max * k, C) + 63) / 64));
         const float *shg = (shared && a.shgate_col >= 0) ? a.logits + a.shgate_col : nullptr;
         launch_k(k_ep_combine, dim3((D / 4 + 255) / 256, T), dim3(256), 0, st, a.out, (const uint8_t *)c->win, L.ret[0], L.ret[1],
                  L.rhdr[0], L.rhdr[1], ctl, world, c->spin_limit, w.status, (const int *)w.ypos, (const float *)w.wt,
-                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k);
+                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k, expected);
         c->calls++;
         return check_launch();
     }

@@ -437,6 +437,7 @@ k_ep_recv_plan(const uint8_t *__restrict__ win, uint64_t off_hdr0, uint64_t off_
                int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan, int mt_gu, int mt_dn,
                int plan_tile_rows, int *__restrict__ counts_out) {
     Q36_GDS();
+    Q36_TR_BEGIN(status, 2)
     __shared__ SortSmem sm;
     __shared__ int s_cnt[64];
     const int tid = threadIdx.x;
@@ -456,6 +457,7 @@ k_ep_recv_plan(const uint8_t *__restrict__ win, uint64_t off_hdr0, uint64_t off_
     if (tid < n && (tid % cap) < s_cnt[tid / cap])
         e = *reinterpret_cast<const int *>(win + (odd ? off_rows1 : off_rows0) + (size_t)tid * row_bytes + eid_off);
     sort_entries_block(sm, e, n, n_expert, se0, se1, ecount, eoffs, elist, pos, soffs, s0, s1, plan, mt_gu, mt_dn, plan_tile_rows);
+    Q36_TR_END(status, 2)
 }
 
 int launch_ep_recv_plan(const void *win, uint64_t off_hdr0, uint64_t off_hdr1, uint64_t off_rows0, uint64_t off_rows1, const int *ctr,
@@ -499,15 +501,19 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
                int *__restrict__ idx, float *__restrict__ wt, int *__restrict__ ecount, int *__restrict__ eoffs,
                int *__restrict__ elist, int *__restrict__ pos, int *__restrict__ soffs, int s0, int s1, TcPlan *plan,
                int mt_gu, int mt_dn, int *status, const void *__restrict__ X, int x_is_bf16, uint8_t *__restrict__ Xq,
-               uint8_t *__restrict__ Xs, int D, int shared_row0, int put_k) {
+               uint8_t *__restrict__ Xs, int D, int shared_row0, int put_k, const EpSendArgs ep) {
     // put_k: k for the sorted row space of a single-GPU layer; 0 when only the token-order rows (shared_row0 + t)
     // are wanted, as in the expert-parallel step
     Q36_GDS();
+    Q36_TR_BEGIN(status, 0)
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n = T * k;
     __shared__ int s_pos[FD_MAX_ENTRIES];          // row of every entry; CTA 0 writes it into every CTA of the cluster
+    // expert-parallel: where every entry's row goes, (destination rank << 20) | slot, or -1 (beyond the capacity)
+    __shared__ int s_slot[FD_MAX_ENTRIES];
+    const unsigned ep_epoch = ep.peers ? (unsigned)ep.ctl[0] + 1u : 0u;
     if (cluster.block_rank() != 0) {
         // ---- quantise now (warp = token x run of 32 blocks, lane = block), place after the barrier
         // (units are dealt across the CTAs first: one SM's store path would take microseconds for all rows)
@@ -529,7 +535,19 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
                 if (row >= 0) quant_block_put(qs, q.e2, Xq, Xs, row, blk0, lane, D);
             }
             if (shared_row0 >= 0) quant_block_put(qs, q.e2, Xq, Xs, shared_row0 + t, blk0, lane, D);
+            if (ep.peers) {   // the same blocks straight into the windows of the ranks that own the token's experts
+                const int row_bytes = D + D / Q36_QK + 16;
+                for (int d = 0; d < k; d++) {
+                    const int code = s_slot[t * k + d];
+                    if (code < 0) continue;
+                    const int r = code >> 20, j = code & 0xfffff;
+                    uint8_t *rowbase = ep.peers[r] + ((ep_epoch & 1u) ? ep.rows1 : ep.rows0) +
+                                       ((size_t)(ep.slot_major ? r : ep.me) * ep.cap + j) * row_bytes;
+                    quant_block_put(qs, q.e2, rowbase, rowbase + D, 0, blk0, lane, D);
+                }
+            }
         }
+        if (ep.peers) cluster.sync();   // every CTA's remote stores before CTA 0 publishes the headers
         return;
     }
     // ---- CTA 0: route, sort, plan
@@ -593,6 +611,7 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
         if (tid == n_expert - 1) {
             const int total = (excl + val) & 0xffff, ne_all = (excl + val) >> 16;
             eoffs[n_expert] = total;
+            s_eoffs[n_expert] = total;
             if (soffs) { soffs[0] = s0; soffs[1] = s1; }
             if (plan) {
                 const bool extra = s1 > s0;
@@ -618,15 +637,44 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
         }
         pos[tid] = p;
         for (int r = 1; r < FD_CLUSTER; r++) *cluster.map_shared_rank(&s_pos[tid], r) = p;   // no L2 round trip for the scatter
+        if (ep.peers) {
+            int code = -1;
+            if (e >= 0) {
+                const int dr = e / ep.per, j = p - s_eoffs[dr * ep.per];
+                if (j < ep.cap) {
+                    code = (dr << 20) | j;
+                    const int row_bytes = D + D / Q36_QK + 16;
+                    uint8_t *rowbase = ep.peers[dr] + ((ep_epoch & 1u) ? ep.rows1 : ep.rows0) +
+                                       ((size_t)(ep.slot_major ? dr : ep.me) * ep.cap + j) * row_bytes;
+                    *reinterpret_cast<int4 *>(rowbase + D + D / Q36_QK) = make_int4(e, 0, 0, 0);     // the row's tail: its expert
+                    ep.ypos[tid] = dr * ep.cap + j;
+                } else {
+                    ep.ypos[tid] = -1;                       // beyond the window's capacity: dropped, and reported
+                    if (status) atomicCAS(status, 0, 0xD00);
+                }
+            } else ep.ypos[tid] = -1;
+            for (int r = 1; r < FD_CLUSTER; r++) *cluster.map_shared_rank(&s_slot[tid], r) = code;
+        }
     }
     cluster.sync();   // (release/acquire at cluster scope: the remote stores above are visible to their CTAs)
+    if (ep.peers) {
+        cluster.sync();   // the quantising CTAs have stored their blocks into the peers' windows
+        if (tid < ep.world) {
+            const int cnt = min(ep.cap, s_eoffs[(tid + 1) * ep.per] - s_eoffs[tid * ep.per]);
+            unsigned long long *h = reinterpret_cast<unsigned long long *>(ep.peers[tid] + ((ep_epoch & 1u) ? ep.hdr1 : ep.hdr0)) +
+                                    (ep.slot_major ? tid : ep.me);
+            const unsigned long long v = (unsigned long long)(unsigned)cnt | ((unsigned long long)ep_epoch << 32);
+            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(h), "l"(v) : "memory");
+        }
+    }
+    Q36_TR_END(status, 0)
 }
 
 // 0 when this front end applies, else the caller takes the general kernels
 int launch_front_decode(const float *logits, int n_expert, int k, float scale, int T, int row_stride, int *idx, float *wt,
                         int *ecount, int *eoffs, int *elist, int *pos, int *soffs, int s0, int s1, void *plan, int D, int FF,
                         int *status, const void *X, int x_is_bf16, uint8_t *Xq, uint8_t *Xs, int shared_row0, int put_k,
-                        cudaStream_t st) {
+                        cudaStream_t st, const EpSendArgs *ep) {
     if (T > 16 || T * k > FD_MAX_ENTRIES || n_expert > DISPATCH_MAX_E || n_expert > FD_THREADS || D % (32 * Q36_QK) ||
         T * (D / (32 * Q36_QK)) > FD_QWARPS || s1 - s0 > 16)
         return Q36_MOE_EINVAL;
@@ -644,7 +692,8 @@ int launch_front_decode(const float *logits, int n_expert, int k, float scale, i
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&cfg, k_front_decode, logits, n_expert, k, scale, T, row_stride, idx, wt, ecount, eoffs, elist, pos,
-                       soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D, shared_row0, put_k);
+                       soffs, s0, s1, (TcPlan *)plan, FF / TC_M, D / TC_M, status, X, x_is_bf16, Xq, Xs, D, shared_row0, put_k,
+                       ep ? *ep : EpSendArgs{nullptr, 0, 0, 0, 0, nullptr, nullptr, 0, 0, 1, 0, 0});
     return check_launch();
 }
 

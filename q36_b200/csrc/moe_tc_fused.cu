@@ -85,9 +85,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                   const uint8_t *__restrict__ sfSU, const uint8_t *__restrict__ sfSD, int n_routed,
                   const uint8_t *__restrict__ Xs, TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
                   uint8_t *__restrict__ Hs, float *__restrict__ Y, int D, int FF, int *__restrict__ status,
-                  const int *__restrict__ rowmap, float *__restrict__ Ymap, int n_map) {
-    // rowmap != nullptr: the result row of sorted row r < n_map goes to row rowmap[r] of Ymap instead of row r of Y
-    // (the expert-parallel step: straight into the slots of the return exchange)
+                  const EpReturnArgs ep) {
+    // ep.peers != nullptr (the expert-parallel step): the result row of sorted row r < ep.n_map is the answer to the
+    // received slot ep.rowmap[r] and goes straight into the result area of that slot's source rank, over NVLink,
+    // instead of row r of Y; the last CTA to finish publishes the call's epoch in every source's header
     using Cfg = FusedCfg;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -133,6 +134,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
     // everything before it (the front end's routing results) being complete as soon as it runs at all.
     cudaGridDependencySynchronize();
     cudaTriggerProgrammaticLaunchCompletion();
+    Q36_TR_BEGIN(status, 4)
     // from here on: global memory written by earlier kernels (the plan, Xq/Xs)
 
     const int G = plan->n_groups;
@@ -366,15 +368,23 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 // lane 0's CTA-scope release orders them before the publisher's device-scope one
                 __syncwarp();
                 if (lane == 0) asm volatile("red.release.cta.shared.add.s32 [%0], 1;" ::"r"(smem_u32(&s_pub)) : "memory");
-            } else if (rowmap && t.row0 < n_map) {
-                int dst[16];
-#pragma unroll
-                for (int c = 0; c < 16; c++) dst[c] = (c < t.nrows && t.row0 + c < n_map) ? rowmap[t.row0 + c] : -1;
+            } else if (ep.peers && t.row0 < ep.n_map) {
+                const bool odd = ((unsigned)ep.ctl[0] + 1u) & 1u;
+                const uint64_t roff = odd ? ep.ret1 : ep.ret0;
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
                     if (c >= t.nrows) continue;
-                    if (dst[c] >= 0) Ymap[(size_t)dst[c] * D + mrow] = g[c];
-                    else if (t.row0 + c >= n_map) Y[(size_t)(t.row0 + c) * D + mrow] = g[c];
+                    const int row = t.row0 + c;
+                    if (row < ep.n_map) {
+                        const int sl = ep.rowmap[row];
+                        if (sl >= 0) {
+                            const int src = sl / ep.cap, j = sl - src * ep.cap;
+                            float *dst = reinterpret_cast<float *>(ep.peers[src] + roff) + ((size_t)(ep.slot_major ? src : ep.me) * ep.cap + j) * D;
+                            dst[mrow] = g[c];
+                        }
+                    } else {
+                        Y[(size_t)row * D + mrow] = g[c];
+                    }
                 }
             } else {
 #pragma unroll
@@ -483,6 +493,17 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(Cfg::TMEM_COLS) : "memory");
     }
+    if (ep.peers && threadIdx.x == 0) {
+        // every CTA orders its remote stores (the barrier above gathered the epilogue warps') with one system-scope
+        // fence, then counts itself in at every source rank: a home rank's combine waits for gridDim.x arrivals
+        __threadfence_system();
+        const bool odd = ((unsigned)ep.ctl[0] + 1u) & 1u;
+        for (int src = 0; src < ep.world; src++) {
+            unsigned *h = reinterpret_cast<unsigned *>(ep.peers[src] + (odd ? ep.rhdr1 : ep.rhdr0) + 8 * (ep.slot_major ? src : ep.me));
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(h) : "memory");
+        }
+    }
+    Q36_TR_END(status, 4)
 }
 
 // every non-empty group has at least one row and one token tile, so the row count bounds the tiles of a CTA
@@ -497,10 +518,15 @@ bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF) {
     return n_group + 1 <= Cfg::MAX_GROUPS && (n0 + grid - 1) / grid + (n1 + grid - 1) / grid + Cfg::EXTRA_DOWN + 1 <= Cfg::MAX_TILES;
 }
 
+// CTAs the launch below uses for a call of these sizes
+int ffn_fused_small_grid(int R_max, int n_group, int D, int FF) {
+    const long max_tiles = (long)(R_max + n_group + 1) * (FF / TC_M + D / TC_M);
+    return (int)min((long)sm_count(), max_tiles);
+}
+
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,
-                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const int *rowmap, float *Ymap,
-                           int n_map, cudaStream_t st) {
+                           uint8_t *Hs, float *Y, int D, int FF, void *plan, int *status, const EpReturnArgs *ep, cudaStream_t st) {
     using Cfg = FusedCfg;
     if (D % (4 * TC_KSTEP) || FF % (4 * TC_KSTEP) || !ffn_fused_small_fits(R_max, n_group, D, FF)) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)FF * (D / 2) + (uint64_t)FF * (D / Q36_QK);   // same for [FF][D] and [D][FF]
@@ -518,11 +544,11 @@ int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const
     if ((rc = make_map_rows_ksteps(&maps.h, Hq, R_max, FF, 16, Cfg::KS))) return rc;
     static bool attr_done[MAX_DEVICES] = {false};
     if ((rc = ensure_smem_attr((const void *)k_ffn_fused_small, Cfg::SMEM_BYTES, attr_done))) return rc;
-    const long max_tiles = (long)(R_max + n_group + 1) * (FF / TC_M + D / TC_M);
-    const int grid = (int)min((long)sm_count(), max_tiles);
+    const int grid = ffn_fused_small_grid(R_max, n_group, D, FF);
     launch_k(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
              (const uint8_t *)Wu + plane, (const uint8_t *)Wd + plane, estride, (const uint8_t *)Sg + plane,
-             (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status, rowmap, Ymap, n_map);
+             (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status,
+             ep ? *ep : EpReturnArgs{nullptr, 0, 0, 0, 0, nullptr, nullptr, 0, 0, 0, 0, 0});
     return check_launch();
 }
 

@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--prefill-tokens", type=int, default=4096)
     ap.add_argument("--zipf", action="store_true", help="Zipf-skewed router logits for the decode stack too")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--prefill-only", action="store_true", help="only the prefill configuration (for profiling): prints {prefill: ...}")
+    ap.add_argument("--prefill-graph-layers", type=int, default=8)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-config3", action="store_true", help="skip the fixed-batch line (64 tokens in all, split over the ranks)")
     ap.add_argument("--no-roofline", action="store_true")
@@ -347,6 +349,10 @@ def run_ours(args):
     path = {"auto": moe.PATH_AUTO, "gemv": moe.PATH_GEMV, "tc": moe.PATH_TC}[args.path]
     transport = ep.TRANSPORT_PEER if args.transport == "peer" else ep.TRANSPORT_NCCL
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    if args.prefill_only:
+        layers, _ = make_layers(torch, moe, 1, 0, dev, min(NL, args.prefill_graph_layers))
+        print(json.dumps({"prefill": bench_prefill(torch, moe, synth, layers, args.prefill_tokens, bf16_peak, peak_kind, dev, args.min_seconds)}))
+        return
     layers, full0 = make_layers(torch, moe, world, rank, dev, NL)
     st = Stack(torch, dist, moe, synth, ep, layers, world, rank, dev, T, path, transport, args.zipf)
     st.capture(allow=(world == 1 or transport == ep.TRANSPORT_PEER))

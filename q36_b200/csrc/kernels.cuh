@@ -33,8 +33,11 @@ int launch_router_topk(const float *logits, int n_expert, int k, int *idx, float
                        int renorm, int T, int row_stride, cudaStream_t st);
 uint64_t dispatch_ws_bytes(int n_entries, int n_expert);
 // soffs (optional): receives {s0, s1}, the row range of the shared expert's group
+// plan (optional): the tensor-core work plan of the groups [se0, se1) (+ the group [s0, s1) when s1 > s0) is written by
+// the scan kernel as well, for the launches of D x FF matrices with token tiles of plan_tile_rows (0: 112 / 128)
 int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *ecount, int *eoffs,
-                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st);
+                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st, void *plan = nullptr, int D = 0,
+                    int FF = 0, int plan_tile_rows = 0);
 int launch_quant(const void *X, int bf16, uint8_t *Xq, uint8_t *Xs, int T, int K, const int *pos,
                  int k, int shared_row0, bool scatter, cudaStream_t st);
 

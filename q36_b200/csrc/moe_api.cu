@@ -130,7 +130,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     } else {
         if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
         if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
-                                  shared ? n + T : n, st)))
+                                  shared ? n + T : n, st, use_tc ? w.plan : nullptr, D, FF, decode_kernel ? 16 : 0)))   // (+ the work plan)
             return rc;
     }
     if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
@@ -143,8 +143,6 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_down_gemv(Wd, ng, goffs, shared ? Sd : nullptr, w.soffs, w.Hq, w.Hs, w.Y, D, FF, st)))
             return rc;
     } else {
-        if (!fused_front && (rc = launch_tc_plan(goffs, ng, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, decode_kernel ? 16 : 0, st)))
-            return rc;
         if (decode_kernel) {
             if ((rc = launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr,
                                              ng, R, w.Xq, w.Xs, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 0, nullptr, st)))

@@ -518,16 +518,14 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         } else {
             launch_k(k_ep_wait_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)c->win, L.hdr[0], L.hdr[1], L.rows[0],
                      L.rows[1], (const int *)ctl, world, C, rowb, D + nbs, c->spin_limit, w.status, w.reid, w.counts);
-            if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st)))
+            if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st,
+                                      w.plan, D, FF, one_launch ? 16 : 0)))   // (+ the work plan)
                 return rc;
         }
         launch_k(k_ep_unpack, dim3(min(R + T, 8 * sm_count())), dim3(128), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,
                  (const int *)w.llist, (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s, w.status);
         if ((rc = check_launch())) return rc;
         // grouped expert FFN on the local shard (+ shared expert on the own tokens)
-        const int *goffs = w.loffs + se0;
-        if (!small_plan && (rc = launch_tc_plan(goffs, per, shared ? w.soffs : nullptr, D, FF, w.plan, w.status, one_launch ? 16 : 0, st)))
-            return rc;
         if (one_launch) {
             // its down epilogue stores the routed result rows straight into their home ranks' windows and its last CTA
             // publishes; the shared expert's rows stay in Y for the combine

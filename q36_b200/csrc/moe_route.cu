@@ -109,28 +109,47 @@ k_dispatch_count(const int *__restrict__ eid, int n, int n_expert, int se0, int 
     if (i < n) lrank[i] = (e >= 0) ? (cnt[warp][e] + r_in_warp) : -1;
 }
 
-__global__ void k_dispatch_scan(int *__restrict__ chunk_cnt, int n_chunk, int n_expert,
-                                int *__restrict__ ecount, int *__restrict__ eoffs,
-                                int *__restrict__ soffs, int s0, int s1) {
+// One block of 1024 threads: a warp per expert at a time scans that expert's per-chunk counts across its lanes
+// (chunks beyond 32 in further passes), then warp 0 scans the expert totals, and -- when a plan is wanted --
+// the same block writes the tensor-core work plan of the grouped launches, which depends on nothing else.
+__global__ void __launch_bounds__(1024)
+k_dispatch_scan(int *__restrict__ chunk_cnt, int n_chunk, int n_expert, int *__restrict__ ecount, int *__restrict__ eoffs,
+                int *__restrict__ soffs, int s0, int s1, TcPlan *plan, int se0, int se1, int mt_gu, int mt_dn, int plan_tile_rows) {
     Q36_GDS();
-    __shared__ int tot[DISPATCH_MAX_E];
-    for (int x = threadIdx.x; x < n_expert; x += blockDim.x) {
+    __shared__ int s_eoffs[DISPATCH_MAX_E + 1];
+    __shared__ int scratch[4 * (DISPATCH_MAX_GROUPS + 1)];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarp = blockDim.x >> 5;
+    for (int x = warp; x < n_expert; x += nwarp) {
         int run = 0;
-        for (int c = 0; c < n_chunk; c++) {
-            const int v = chunk_cnt[(size_t)c * n_expert + x];
-            chunk_cnt[(size_t)c * n_expert + x] = run;
-            run += v;
+        for (int c0 = 0; c0 < n_chunk; c0 += 32) {
+            const int c = c0 + lane;
+            const int v = (c < n_chunk) ? chunk_cnt[(size_t)c * n_expert + x] : 0;
+            int incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+            if (c < n_chunk) chunk_cnt[(size_t)c * n_expert + x] = run + incl - v;
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        tot[x] = run;
-        ecount[x] = run;
+        if (lane == 0) { s_eoffs[x] = run; ecount[x] = run; }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int x = 0; x < n_expert; x++) { eoffs[x] = run; run += tot[x]; }
-        eoffs[n_expert] = run;
-        if (soffs) { soffs[0] = s0; soffs[1] = s1; }
+    if (warp == 0) {   // exclusive scan of the expert totals: lane owns a contiguous run
+        const int per = (n_expert + 31) / 32;
+        int sum = 0;
+        for (int j = 0; j < per; j++) { const int x = lane * per + j; if (x < n_expert) sum += s_eoffs[x]; }
+        int incl = sum;
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+        int run = incl - sum;
+        for (int j = 0; j < per; j++) {
+            const int x = lane * per + j;
+            if (x < n_expert) { const int c = s_eoffs[x]; s_eoffs[x] = run; run += c; }
+        }
+        if (lane == 31) s_eoffs[n_expert] = run;
     }
+    __syncthreads();
+    for (int x = tid; x <= n_expert; x += blockDim.x) eoffs[x] = s_eoffs[x];
+    if (tid == 0 && soffs) { soffs[0] = s0; soffs[1] = s1; }
+    if (plan) tc_plan_block(s_eoffs + se0, se1 - se0, s1 > s0, s0, s1, plan, mt_gu, mt_dn, scratch, true, plan_tile_rows);
 }
 
 __global__ void k_dispatch_place(const int *__restrict__ eid, int n, int n_expert,
@@ -711,12 +730,14 @@ uint64_t dispatch_ws_bytes(int n_entries, int n_expert) {
 }
 
 int launch_dispatch(const int *eid, int n, int n_expert, int se0, int se1, int *ecount, int *eoffs,
-                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st) {
+                    int *elist, int *pos, void *ws, int *soffs, int s0, int s1, cudaStream_t st, void *plan, int D, int FF,
+                    int plan_tile_rows) {
     const int n_chunk = (n + DISPATCH_CHUNK - 1) / DISPATCH_CHUNK;
     int *chunk_cnt = (int *)ws;
     int *lrank = chunk_cnt + (size_t)n_chunk * n_expert;
     if (n > 0) launch_k(k_dispatch_count, dim3(n_chunk), dim3(DISPATCH_CHUNK), 0, st, eid, n, n_expert, se0, se1, chunk_cnt, lrank);
-    launch_k(k_dispatch_scan, dim3(1), dim3(256), 0, st, chunk_cnt, n_chunk, n_expert, ecount, eoffs, soffs, s0, s1);
+    launch_k(k_dispatch_scan, dim3(1), dim3(1024), 0, st, chunk_cnt, n_chunk, n_expert, ecount, eoffs, soffs, s0, s1, (TcPlan *)plan,
+             se0, se1, plan ? FF / TC_M : 0, plan ? D / TC_M : 0, plan_tile_rows);
     if (n > 0) launch_k(k_dispatch_place, dim3((n + 255) / 256), dim3(256), 0, st, eid, n, n_expert, chunk_cnt, lrank, eoffs, elist, pos);
     return check_launch();
 }
@@ -785,5 +806,5 @@ extern "C" int q36_moe_dispatch_noalloc(const int *expert_of_entry, int n_entrie
     // Nothing in the scratch has to start at zero: k_dispatch_count writes every counter of every chunk it
     // covers and the rank of every entry before the later kernels read them.
     return q36::launch_dispatch(expert_of_entry, n_entries, n_expert, se0, se1, ecount, eoffs, elist, pos,
-                                g_noalloc_ptr[dev], nullptr, 0, 0, (cudaStream_t)stream);
+                                g_noalloc_ptr[dev], nullptr, 0, 0, (cudaStream_t)stream, nullptr, 0, 0, 0);
 }

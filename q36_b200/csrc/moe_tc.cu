@@ -26,6 +26,7 @@
 // groups first).  Every mbarrier wait is bounded; a wait that gives up raises
 // a status word that the host entry point reports as Q36_MOE_EDEVICE.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -194,7 +195,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                 for (int ks = 0; ks < k_steps; ks++, it++) {
                     if ((ks & 3) == 0) {   // the scale bytes of the next four K steps
                         const uint32_t sl = item % Cfg::SFR_SLOTS;
-                        if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / Cfg::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl))) break;
+                        if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / Cfg::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
                         const uint32_t dst = smem_u32(sfr + sl * Cfg::SFR_BYTES);
                         mbar_expect_tx(sfr_full0 + 8 * sl, NA * Cfg::SFR_PART + Cfg::N * 16);
                         tma_load_3d(dst, fa0, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
@@ -204,7 +205,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                     }
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, tx);
                     tma_load_3d(sb, ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
@@ -265,7 +266,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
             const TcTile t = get_tile(ti);
             const uint32_t buf = tcount & 1;
             const uint32_t tq = tmem + buf * Cfg::ACC_STRIDE + ((uint32_t)(q * 32) << 16);
-            if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf))) break;
+            if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;   // weight row (output feature) of this thread
             for (int c0 = 32 * half; c0 < t.nrows; c0 += 64) {
@@ -310,7 +311,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
             const bool bvalid = i < t.nrows;
             for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
                 const uint32_t sl = item % Cfg::SFR_SLOTS;
-                if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl))) break;
+                if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
                 const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + i * 16;
                 const uint4 a0 = *reinterpret_cast<const uint4 *>(src);
                 const uint4 a1 = (NA == 2) ? *reinterpret_cast<const uint4 *>(src + Cfg::SFR_PART) : make_uint4(0, 0, 0, 0);
@@ -322,7 +323,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                 for (int j = 0; j < 4; j++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s))) break;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
                     uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
                     *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
                     if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
@@ -354,6 +355,277 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ----------------------------------------------- down projection, token tile resident
+// The down projection of prefill-sized groups has K = FF = 512: a token tile's whole B operand (128 rows x 512 B
+// = 64 KB) fits in shared memory.  k_grouped_mma<1> re-fetches it for every one of the D / 128 weight-row tiles
+// (64 KB of tokens against 32 KB of weights per tile) from one producer thread and issues from one thread (N = 128
+// needs an MMA per 64 cycles, one thread manages one per ~92).  Here a work item is (group, token tile, chunk of
+// DR_MC consecutive weight-row tiles): the token rows and their scale images are loaded once per item and stay,
+// weights stream through a ring of two-K-step stages (one 4-D copy each), two warps issue alternate row tiles into
+// their own accumulators (which is also what lets the epilogue of one tile overlap the MMAs of the next), and the
+// weight copies, the token copies and the scale images each have their own thread(s).
+struct DownRes {
+    static constexpr int N = TC_N_DOWN;                 // token rows per item
+    static constexpr int KSTEPS = 4;                    // K = 512 in steps of 128
+    static constexpr int KS = 2;                        // K steps per weight stage
+    static constexpr int STAGES = 4;
+    static constexpr int A_BYTES = TC_M * 128;          // one K step of weights in shared memory (padded 4-bit)
+    static constexpr int A_TX = TC_M * 64;              // ... and what the copy signals (packed bytes)
+    static constexpr int SF_BYTES = 512;
+    static constexpr int STAGE_BYTES = KS * A_BYTES + KS * SF_BYTES + 1024 - KS * SF_BYTES;   // 33 KB: [A k0][A k1][SFA k0][SFA k1][pad]
+    static constexpr int B_STEP = N * 128;              // one K step of the token tile
+    static constexpr int B_BYTES = KSTEPS * B_STEP;     // 64 KB
+    static constexpr int BIMG_BYTES = KSTEPS * SF_BYTES;   // token scale images, one per K step
+    static constexpr int SFR_SLOTS = 2, SFR_BYTES = TC_M * 16;   // staged weight scale bytes of a row tile: 128 rows x 16 B
+    static constexpr int BS_BYTES = N * 16;             // staged token scale bytes of an item
+    static constexpr int OFF_B = STAGES * STAGE_BYTES, OFF_BIMG = OFF_B + B_BYTES, OFF_SFR = OFF_BIMG + BIMG_BYTES,
+                         OFF_BS = OFF_SFR + SFR_SLOTS * SFR_BYTES, OFF_BARS = OFF_BS + BS_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;
+    static constexpr int W_PROD_A = 0, W_PROD_B = 1, W_ISSUE0 = 2, W_EPI0 = 4, EPI_WARPS = 8, W_LOAD0 = W_EPI0 + EPI_WARPS;
+    static constexpr int THREADS = 32 * (W_LOAD0 + 4);
+    static constexpr int ACC_BUFS = 3, ACC_STRIDE = 128, SF_COL0 = ACC_BUFS * ACC_STRIDE, TMEM_COLS = 512;
+};
+static_assert(DownRes::STAGE_BYTES % 1024 == 0 && DownRes::OFF_B % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+constexpr int DR_MC = 8;   // weight-row tiles per work item
+
+struct DownMaps { CUtensorMap a, s, b, fa, fs, fb; };   // routed / shared code planes (2 K steps per box), token rows, scale planes
+
+__global__ void __launch_bounds__(DownRes::THREADS, 1)
+k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPlan *__restrict__ plan, float *__restrict__ Y,
+                int M_total, int *__restrict__ status) {
+    using C = DownRes;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::OFF_BARS);
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+    __shared__ int s_row0[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1], s_base[DISPATCH_MAX_GROUPS + 2];
+    __shared__ unsigned short s_order[DISPATCH_MAX_GROUPS + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // barriers: full[4] empty[4] | sfr_full[2] sfr_empty[2] | bq_full[4] | bimg_full b_empty bs_full bs_empty | acc_full[3] acc_empty[3]
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * C::STAGES, sfr_full0 = empty0 + 8 * C::STAGES,
+                   sfr_empty0 = sfr_full0 + 8 * C::SFR_SLOTS, bq_full0 = sfr_empty0 + 8 * C::SFR_SLOTS,
+                   bimg_full = bq_full0 + 8 * C::KSTEPS, b_empty = bimg_full + 8, bs_full = b_empty + 8, bs_empty = bs_full + 8,
+                   acc_full0 = bs_empty + 8, acc_empty0 = acc_full0 + 8 * C::ACC_BUFS;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < C::STAGES; i++) { mbar_init(full0 + 8 * i, 1 + 4); mbar_init(empty0 + 8 * i, 1); }
+        for (int i = 0; i < C::SFR_SLOTS; i++) { mbar_init(sfr_full0 + 8 * i, 1); mbar_init(sfr_empty0 + 8 * i, 4); }
+        for (int i = 0; i < C::KSTEPS; i++) mbar_init(bq_full0 + 8 * i, 1);
+        mbar_init(bimg_full, 4); mbar_init(b_empty, 2); mbar_init(bs_full, 1); mbar_init(bs_empty, 4);
+        for (int i = 0; i < C::ACC_BUFS; i++) { mbar_init(acc_full0 + 8 * i, 1); mbar_init(acc_empty0 + 8 * i, C::EPI_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == C::W_ISSUE0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    Q36_GDS();
+    const int G = plan->n_groups, m_tiles = M_total / TC_M;
+    const int n_items = plan->n_tiles[1] / DR_MC;          // every group's tile count is a multiple of m_tiles, and m_tiles of DR_MC
+    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
+        s_base[i] = plan->base[1][i];
+        if (i < G) { s_order[i] = (unsigned short)plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = plan->cnt[i]; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    // item -> (group, first weight-row tile of its chunk, first token row, token rows)
+    auto get_item = [&](int ii) {
+        const int ti = ii * DR_MC;
+        int lo = 0, hi = G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_base[mid] <= ti) lo = mid; else hi = mid - 1;
+        }
+        const int g = s_order[lo], local = ti - s_base[lo];
+        const int nt = local / m_tiles, mt = local - nt * m_tiles;
+        return TcTile{g, mt, s_row0[g] + nt * C::N, min(C::N, s_cnt[g] - nt * C::N)};
+    };
+
+    if (warp == C::W_PROD_A) {
+        // ------------------------------ weights: per row tile its scale bytes (one box) and two 2-K-step code boxes
+        if (lane == 0) {
+            uint32_t q = 0;
+            bool ok = true;
+            for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x) {
+                const TcTile t = get_item(ii);
+                const bool sh = t.g >= n_routed;
+                const CUtensorMap *ma = sh ? &maps.s : &maps.a, *mf = sh ? &maps.fs : &maps.fa;
+                const int ge = sh ? 0 : t.g;
+                for (int j = 0; j < DR_MC && ok; j++, q++) {
+                    const int mrow0 = (t.mt + j) * TC_M;
+                    const uint32_t sl = q % C::SFR_SLOTS;
+                    if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((q / C::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                    mbar_expect_tx(sfr_full0 + 8 * sl, C::SFR_BYTES);
+                    tma_load_3d(smem_u32(smem + C::OFF_SFR + sl * C::SFR_BYTES), mf, 0, mrow0, ge, sfr_full0 + 8 * sl);
+                    for (int h = 0; h < C::KSTEPS / C::KS; h++) {
+                        const uint32_t it = q * (C::KSTEPS / C::KS) + h, s = it % C::STAGES;
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        mbar_expect_tx(full0 + 8 * s, C::KS * C::A_TX);
+                        tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES), ma, 0, mrow0, h * C::KS, ge, full0 + 8 * s);
+                    }
+                }
+            }
+        }
+    } else if (warp == C::W_PROD_B) {
+        // ------------------------------ token rows of the item (one box per K step) and their scale bytes
+        if (lane == 0) {
+            uint32_t n = 0;
+            bool ok = true;
+            for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
+                const TcTile t = get_item(ii);
+                // the scale bytes first (their staging is free as soon as the loader warps have read the previous item's):
+                // the images can then be written the moment the issuers let go of the previous item
+                if (!(ok = mbar_wait(bs_empty, (n & 1) ^ 1, &abort_flag, status, 0x190, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                mbar_expect_tx(bs_full, C::BS_BYTES);
+                tma_load_2d(smem_u32(smem + C::OFF_BS), &maps.fb, 0, t.row0, bs_full);
+                if (!(ok = mbar_wait(b_empty, (n & 1) ^ 1, &abort_flag, status, 0x180, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;      // both issuers are done with the previous item's rows
+                for (int ks = 0; ks < C::KSTEPS; ks++) {
+                    mbar_expect_tx(bq_full0 + 8 * ks, C::B_STEP);
+                    tma_load_2d(smem_u32(smem + C::OFF_B + ks * C::B_STEP), &maps.b, ks * TC_KSTEP, t.row0, bq_full0 + 8 * ks);
+                }
+            }
+        }
+    } else if (warp < C::W_EPI0) {
+        // ------------------------------ MMA issuers: warp w takes the row tiles with sequence number q = w (mod 2)
+        if (lane == 0) {
+            const uint32_t w = warp - C::W_ISSUE0;
+            const uint32_t t_sfa = tmem + C::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
+            uint32_t n = 0;
+            bool ok = true;
+            for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
+                const TcTile t = get_item(ii);
+                const int n_mma = max(16, (t.nrows + 15) & ~15);
+                bool first = true;
+                for (int j = 0; j < DR_MC && ok; j++) {
+                    const uint32_t q = n * DR_MC + j;
+                    if ((q & 1u) != w) continue;
+                    // accumulator q % 3: a third buffer lets the issuers run a row tile ahead of the epilogue, which is
+                    // the slower side (64 KB of f32 rows to store per row tile)
+                    const uint32_t buf = q % C::ACC_BUFS, use = q / C::ACC_BUFS;
+                    const uint32_t d_tmem = tmem + buf * C::ACC_STRIDE;
+                    if (!(ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
+                    if (first) {                                   // the item's token scale images
+                        if (!(ok = mbar_wait(bimg_full, n & 1, &abort_flag, status, 0x210))) break;
+                    }
+                    tc_fence_after();
+                    for (int h = 0; h < C::KSTEPS / C::KS && ok; h++) {
+                        const uint32_t it = q * (C::KSTEPS / C::KS) + h, s = it % C::STAGES;
+                        if (!(ok = mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, &abort_flag, status, 0x300 + s))) break;
+                        const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES);
+#pragma unroll
+                        for (int x = 0; x < C::KS; x++) {
+                            const int ks = h * C::KS + x;
+                            if (first && !(ok = mbar_wait(bq_full0 + 8 * ks, n & 1, &abort_flag, status, 0x220 + ks))) break;
+                            tc_fence_after();
+                            tc_cp_sf(t_sfa, desc_sf(sb + C::KS * C::A_BYTES + x * C::SF_BYTES));
+                            tc_cp_sf(t_sfb, desc_sf(smem_u32(smem + C::OFF_BIMG + ks * C::SF_BYTES)));
+                            const uint32_t sa = sb + x * C::A_BYTES, sbb = smem_u32(smem + C::OFF_B + ks * C::B_STEP);
+#pragma unroll
+                            for (int kb = 0; kb < 4; kb++) {
+                                const uint32_t sfid = (uint32_t)kb << 30;
+                                tc_mma(d_tmem, desc_sw128(sa + kb * 32), desc_sw128(sbb + kb * 32), idesc_mx(n_mma, kb), t_sfa | sfid,
+                                       t_sfb | sfid, (ks | kb) ? 1u : 0u);
+                            }
+                        }
+                        if (!ok) break;
+                        tc_commit(empty0 + 8 * s);
+                    }
+                    if (!ok) break;
+                    first = false;
+                    tc_commit(acc_full0 + 8 * buf);
+                }
+                if (ok) tc_commit(b_empty);     // (arrives when all of this warp's MMAs on the item have read the token rows)
+            }
+        }
+    } else if (warp < C::W_LOAD0) {
+        // ------------------------------ epilogue: accumulators -> f32 rows
+        const int qd = warp & 3;                              // TMEM lane quarter this warp may read
+        const int half = (warp - C::W_EPI0) >> 2;             // even or odd 32-column chunks
+        uint32_t n = 0;
+        bool ok = true;
+        for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
+            const TcTile t = get_item(ii);
+            for (int j = 0; j < DR_MC && ok; j++) {
+                const uint32_t q = n * DR_MC + j, buf = q % C::ACC_BUFS;
+                if (!(ok = mbar_wait(acc_full0 + 8 * buf, (q / C::ACC_BUFS) & 1, &abort_flag, status, 0x400 + buf, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                tc_fence_after();
+                const uint32_t tq = tmem + buf * C::ACC_STRIDE + ((uint32_t)(qd * 32) << 16);
+                const int mrow = (t.mt + j) * TC_M + qd * 32 + lane;
+                for (int c0 = 32 * half; c0 < t.nrows; c0 += 64) {
+                    uint32_t v[32];
+                    tc_ld32(tq + c0, v);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; c++)
+                        if (c0 + c < t.nrows) Y[(size_t)(t.row0 + c0 + c) * M_total + mrow] = __uint_as_float(v[c]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+            }
+        }
+    } else {
+        // ------------------------------ scale images: thread i owns row i of the token tile and of every weight-row tile
+        const int i = threadIdx.x - 32 * C::W_LOAD0;
+        const uint32_t my_off = (i & 31) * 16 + (i >> 5) * 4;
+        uint32_t n = 0;
+        bool ok = true;
+        for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
+            const TcTile t = get_item(ii);
+            // token scale images, once per item: wait for the staged bytes and for the previous item's images to be unused
+            if (!(ok = mbar_wait(bs_full, n & 1, &abort_flag, status, 0x700, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+            uint4 b = *reinterpret_cast<const uint4 *>(smem + C::OFF_BS + i * 16);
+            if (i >= t.nrows) b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+            if (!(ok = mbar_wait(b_empty, (n & 1) ^ 1, &abort_flag, status, 0x710, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+            {
+                uint8_t *img = smem + C::OFF_BIMG + my_off;
+                *reinterpret_cast<uint32_t *>(img) = b.x;
+                *reinterpret_cast<uint32_t *>(img + C::SF_BYTES) = b.y;
+                *reinterpret_cast<uint32_t *>(img + 2 * C::SF_BYTES) = b.z;
+                *reinterpret_cast<uint32_t *>(img + 3 * C::SF_BYTES) = b.w;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(bimg_full); mbar_arrive(bs_empty); }
+            // weight scale images, per row tile: 4 bytes per K step from the staged 16
+            for (int j = 0; j < DR_MC && ok; j++) {
+                const uint32_t q = n * DR_MC + j, sl = q % C::SFR_SLOTS;
+                if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (q / C::SFR_SLOTS) & 1, &abort_flag, status, 0x720 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                const uint4 a = *reinterpret_cast<const uint4 *>(smem + C::OFF_SFR + sl * C::SFR_BYTES + i * 16);
+                const uint32_t wa[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int h = 0; h < C::KSTEPS / C::KS; h++) {
+                    const uint32_t it = q * (C::KSTEPS / C::KS) + h, s = it % C::STAGES;
+                    if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                    uint8_t *sf = smem + s * C::STAGE_BYTES + C::KS * C::A_BYTES + my_off;
+                    *reinterpret_cast<uint32_t *>(sf) = wa[2 * h];
+                    *reinterpret_cast<uint32_t *>(sf + C::SF_BYTES) = wa[2 * h + 1];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full0 + 8 * s);
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);   // leave copies in flight time to land before the block retires
+        if (threadIdx.x == 0) atomicCAS(status, 0, 1);
+    }
+    if (warp == C::W_ISSUE0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
     }
 }
 
@@ -534,9 +806,35 @@ int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void 
     (void)max_group_rows;
     return run_grouped<2>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
 }
+// K = 512 and D a multiple of DR_MC row tiles: the token-tile-resident kernel
+static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs, float *Y,
+                             int M, int K, const void *plan, int *status, cudaStream_t st) {
+    using C = DownRes;
+    const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK), plane = (uint64_t)M * (K / 2);
+    const int nb = K / Q36_QK;
+    if (!Sd) Sd = Wd;
+    DownMaps maps;
+    int rc;
+    if ((rc = make_map_codes_ksteps(&maps.a, Wd, M, K, n_group, estride, C::KS))) return rc;
+    if ((rc = make_map_codes_ksteps(&maps.s, Sd, M, K, 1, estride, C::KS))) return rc;
+    if ((rc = make_map_rows(&maps.b, Hq, R_max, K, C::N))) return rc;
+    if ((rc = make_map_scales(&maps.fa, (const uint8_t *)Wd + plane, M, nb, n_group, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fs, (const uint8_t *)Sd + plane, M, nb, 1, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fb, Hs, R_max, nb, 0, 0, C::N))) return rc;
+    static bool attr_done[MAX_DEVICES] = {false};
+    if ((rc = ensure_smem_attr((const void *)k_down_resident, C::SMEM_BYTES, attr_done))) return rc;
+    const long max_items = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * (M / TC_M / DR_MC);
+    const int grid = (int)min((long)sm_count(), max_items);
+    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status);
+    return check_launch();
+}
+
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq,
                    const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
     (void)max_group_rows;
+    static const bool old_down = getenv("Q36_OLD_DOWN") != nullptr;
+    if (!old_down && FF == DownRes::KSTEPS * TC_KSTEP && D % (TC_M * DR_MC) == 0 && n_group + 1 <= DISPATCH_MAX_GROUPS)
+        return run_down_resident(Wd, Sd, n_group, R_max, Hq, Hs, Y, D, FF, plan, status, st);
     return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
 }
 

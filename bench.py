@@ -52,6 +52,11 @@ def parse():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--prefill-only", action="store_true", help="only the prefill configuration (for profiling): prints {prefill: ...}")
     ap.add_argument("--prefill-graph-layers", type=int, default=8)
+    ap.add_argument("--prefill-stack", action="store_true",
+                    help="benchmark configuration 4 instead: the 40-layer prefill stack, --stack-tokens tokens in all, expert-parallel over "
+                         "the ranks with the dispatch of layer l + 1 overlapped with the expert work of layer l")
+    ap.add_argument("--stack-tokens", type=int, default=32768)
+    ap.add_argument("--no-overlap", action="store_true", help="--prefill-stack: every phase on one stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-config3", action="store_true", help="skip the fixed-batch line (64 tokens in all, split over the ranks)")
     ap.add_argument("--no-roofline", action="store_true")
@@ -642,8 +647,142 @@ def bench_prefill(torch, moe, synth, layers, Tp, bf16_peak, peak_kind, dev, min_
             "frac_of_nominal": tf / 4500.0, "frac_of_2x_bf16": tf / (2 * bf16_peak), "peak_kind": peak_kind}
 
 
+def run_prefill_stack(args):
+    """Benchmark configuration 4: NL layers x stack-tokens tokens (uniform N(0,1) router logits, top-8), expert-parallel
+    over the ranks; two streams: phase 0 (route, quantise, store rows into the peers' windows) of layer l + 1 runs beside
+    phases 1 and 2 (expert FFN, results back, combine) of layer l.  One rank: the same layers on one GPU."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from q36_b200 import build as qb
+    qb.build()
+    from q36_b200 import moe, synth, ep
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    NL, T = args.layers, args.stack_tokens // world
+    _, bf16_peak, peak_kind = measured_peaks()
+    layers, full0 = make_layers(torch, moe, world, rank, dev, NL)
+    NIN = 4                                                    # distinct input sets, cycled over the layers
+    rng = np.random.default_rng(99 + rank)
+    X = [torch.from_numpy(synth.activations(rng, T)).to(dev).to(torch.bfloat16) for _ in range(NIN)]
+    L = [torch.from_numpy(synth.router_logits(rng, T)).to(dev) for _ in range(NIN)]
+    out = [torch.empty((T, D), dtype=torch.float32, device=dev) for _ in range(2)]
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    ep_check = None
+    if world == 1:
+        ws = layers[0].workspace(T)
+
+        def one_pass():
+            for l in range(NL):
+                layers[l].forward(X[l % NIN], L[l % NIN], out=out[l & 1], path=moe.PATH_TC, ws=ws)
+        launch = "stream launches, one stream"
+    else:
+        cap = min(T * K8, int(1.5 * T * K8 / world) + 256)      # rows per pair of ranks: 1.5 x the mean of uniform routing
+        nat = ep.NativeEP(layers, world, rank, T, cap_rows=cap)
+        wss = [nat.ws, nat.second_workspace()]
+        e0 = [torch.cuda.Event() for _ in range(NL)]
+        e2 = [torch.cuda.Event() for _ in range(NL)]
+
+        def one_pass():
+            if args.no_overlap:
+                for l in range(NL):
+                    for p in range(3):
+                        nat.phase(p, layers[l], X[l % NIN], L[l % NIN], out[l & 1], ws=wss[l & 1])
+                return
+            cur = torch.cuda.current_stream()
+            s1.wait_stream(cur)
+            s2.wait_stream(cur)
+            with torch.cuda.stream(s2):
+                nat.phase(0, layers[0], X[0], L[0], out[0], ws=wss[0])
+                e0[0].record(s2)
+            for l in range(NL):
+                if l + 1 < NL:
+                    with torch.cuda.stream(s2):
+                        if l >= 1:
+                            s2.wait_event(e2[l - 1])       # its windows' and workspace's previous user (layer l - 1) is done
+                        nat.phase(0, layers[l + 1], X[(l + 1) % NIN], L[(l + 1) % NIN], out[(l + 1) & 1], ws=wss[(l + 1) & 1])
+                        e0[l + 1].record(s2)
+                with torch.cuda.stream(s1):
+                    s1.wait_event(e0[l])
+                    nat.phase(1, layers[l], X[l % NIN], L[l % NIN], out[l & 1], ws=wss[l & 1])
+                    nat.phase(2, layers[l], X[l % NIN], L[l % NIN], out[l & 1], ws=wss[l & 1])
+                    e2[l].record(s1)
+            cur.wait_stream(s1)
+            cur.wait_stream(s2)
+        launch = "stream launches, one stream" if args.no_overlap else "stream launches, two streams (dispatch of layer l + 1 beside the expert work of layer l)"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    one_pass()
+    barrier()
+    if world > 1:
+        # layer NL - 1's output of this rank (out[(NL - 1) & 1]) against the single-GPU layer over all experts
+        lchk = NL - 1
+        fullL = moe.MoELayer(device=dev).random_planes(seed=1000 + lchk)
+        ref = fullL.forward(X[lchk % NIN], L[lchk % NIN], path=moe.PATH_TC)
+        torch.cuda.synchronize()
+        err = float((out[lchk & 1] - ref).norm() / ref.norm())
+        t = torch.tensor([err], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        st_rc = 0
+        for w in wss:
+            st_rc = st_rc or moe.lib.q36_moe_ws_status(w.data_ptr(), moe.stream_ptr())
+        ts = torch.tensor([abs(st_rc)], device=dev)
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        ep_check = {"max_rel_l2": float(t.item()), "tolerance": 1e-4, "status": int(ts.item()), "layer_checked": lchk}
+        del fullL, ref
+        torch.cuda.empty_cache()
+    else:
+        layers[0].check_device_status()
+    for _ in range(max(1, args.warmup - 1)):
+        one_pass()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per = []
+    for _ in range(max(3, args.steps)):
+        barrier()
+        ev0.record()
+        one_pass()
+        ev1.record()
+        barrier()
+        per.append(ev0.elapsed_time(ev1))
+    t = torch.tensor(per, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    per = t.tolist()
+    ms = statistics.median(per)
+    tokens = T * world
+    flop = tokens * (K8 + 1) * FLOP_PER_ASSIGNMENT * NL
+    line = {"metric": "moe_prefill_stack_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s (through all layers)",
+            "token_layers_per_s": tokens * NL / (ms * 1e-3), "n_gpus": world, "steps": len(per), "ms_per_pass": ms,
+            "ms_per_pass_std": statistics.pstdev(per), "ms_per_layer": ms / NL, "tflops_per_gpu": flop / (ms * 1e-3) / 1e12 / world,
+            "frac_of_nominal_mxf8f6f4_per_gpu": flop / (ms * 1e-3) / 1e12 / world / 4500.0, "scaling": "strong", "data": "synthetic",
+            "config": {"workload": f"prefill stack: {NL} distinct MoE layers, {tokens} tokens in all ({T} per rank), uniform routing, top-8",
+                       "layers": NL, "tokens": tokens, "parallelism": f"ep{world}" if world > 1 else "single"},
+            "launch": launch, "ep_check": ep_check, "peaks": peak_kind}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        ok = ep_check["status"] == 0 and ep_check["max_rel_l2"] < ep_check["tolerance"]
+        nat.close()
+        dist.destroy_process_group()
+        if not ok:
+            sys.exit(3)
+
+
 def main():
     args = parse()
+    if args.prefill_stack:
+        run_prefill_stack(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -17,7 +17,8 @@
 // ranks with CUDA IPC or, for ranks of one process, by peer access): [2 parities] x { headers, rows of every
 // source, result rows of every expert rank }.  A call uses parity (call number & 1); a rank can run at most one
 // call ahead of a peer because its combine needs that peer's results, so two parities suffice.  The call
-// number lives on the device, which makes a stack of calls capturable in a CUDA graph.
+// numbers live on the device (one counter per phase, advanced by the phase's last kernel), which makes a stack of
+// calls capturable in a CUDA graph and lets phase 0 of the next call run beside phases 1 and 2 of this one.
 //
 // Every wait is bounded; a wait that gives up records 0xB00 + source (dispatch) or 0xC00 + source (results) in
 // the status words and the step goes on (with garbage, but it ends and the host can see why).
@@ -87,7 +88,7 @@ static WinLayout win_layout(int world, int cap, int D) {
     uint64_t o = 0;
     auto take = [&](uint64_t b) { const uint64_t r = o; o += (b + 255) & ~(uint64_t)255; return r; };
     for (int p = 0; p < 2; p++) { L.hdr[p] = take(8 * EP_MAX_WORLD); L.rhdr[p] = take(8 * EP_MAX_WORLD); }
-    L.ctl = take(256);   // ints: [0] call counter, [3] ticket of the combine, [8 + r] / [8 + 16 + s] tickets per destination / source
+    L.ctl = take(256);   // ints: [0..2] calls whose phase 0 / 1 / 2 has finished on this rank, [3..6] tickets of the "last block" patterns, [8 + r] per destination
     for (int p = 0; p < 2; p++) L.rows[p] = take((uint64_t)world * cap * L.row_bytes);
     for (int p = 0; p < 2; p++) L.ret[p] = take((uint64_t)world * cap * D * 4);
     L.bytes = o;
@@ -110,7 +111,7 @@ struct EpComm {
     uint8_t **d_peer = nullptr;          // device copy of peer[] (or of stage pointers for the NCCL transport)
     uint8_t *stage = nullptr;            // NCCL transport: local staging laid out like a window
     unsigned spin_limit = EP_SPIN_LIMIT;
-    unsigned long long calls = 0;        // host mirror of the device call counter (NCCL transport only)
+    unsigned long long calls[3] = {0, 0, 0};   // host mirror of the device's per-phase call counters (NCCL transport only)
 };
 
 __device__ __forceinline__ void st_release_sys_u64(unsigned long long *p, unsigned long long v) {
@@ -198,6 +199,8 @@ k_ep_send(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const 
             unsigned long long *h = reinterpret_cast<unsigned long long *>(peers[r] + (odd ? hdr1 : hdr0)) + (slot_major_dst ? r : me);
             st_release_sys_u64(h, (unsigned long long)(unsigned)cnt | ((unsigned long long)epoch << 32));
         }
+        // the last block of the launch (every block has read the counter by then) ends phase 0 of this call
+        if (atomicAdd(ctl + 5, 1) == (int)gridDim.x - 1) { ctl[5] = 0; ctl[0] = (int)epoch; }
     }
     Q36_TR_END(status, 1)
 }
@@ -210,7 +213,7 @@ k_ep_wait_eids(const uint8_t *__restrict__ win, uint64_t hdr0, uint64_t hdr1, ui
                int *__restrict__ counts_out) {
     Q36_GDS();
     __shared__ int s_cnt[EP_MAX_WORLD];
-    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const unsigned epoch = (unsigned)ctl[1] + 1u;
     const bool odd = epoch & 1u;
     if (threadIdx.x < world) {
         const int c = wait_hdr(reinterpret_cast<const unsigned long long *>(win + (odd ? hdr1 : hdr0)) + threadIdx.x, epoch, limit,
@@ -233,7 +236,7 @@ k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, con
     Q36_GDS();
     Q36_TR_BEGIN(status, 3)
     const int nbs = D / Q36_QK, row_bytes = D + nbs + EP_TAIL;
-    const bool odd = ((unsigned)ctl[0] + 1u) & 1u;
+    const bool odd = ((unsigned)ctl[1] + 1u) & 1u;
     const uint8_t *recv = win + (odd ? rows1 : rows0);
     const int n_res = *loffs_end;          // rows that arrived; rows [n_res, R) belong to no group and are never used
     for (int x = blockIdx.x; x < n_res + T; x += gridDim.x) {
@@ -263,7 +266,7 @@ k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int
     Q36_GDS();
     Q36_TR_BEGIN(status, 5)
     const int s = blockIdx.x / nb, b = blockIdx.x % nb;
-    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const unsigned epoch = (unsigned)ctl[1] + 1u;
     const bool odd = epoch & 1u;
     const int cnt = counts[s];
     float4 *dst0 = reinterpret_cast<float4 *>(peers[s] + (odd ? ret1 : ret0) + (size_t)(slot_major_dst ? s : me) * cap * D * 4);
@@ -293,6 +296,7 @@ k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int
         __threadfence_system();
         unsigned *h = reinterpret_cast<unsigned *>(peers[s] + (odd ? rhdr1 : rhdr0) + 8 * (slot_major_dst ? s : me));
         asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(h) : "memory");
+        if (atomicAdd(ctl + 6, 1) == (int)gridDim.x - 1) { ctl[6] = 0; ctl[1] = (int)epoch; }   // the last block ends phase 1 of this call
     }
     Q36_TR_END(status, 5)
 }
@@ -308,7 +312,7 @@ k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t 
     // launch, or the blocks per source of its return kernel: the same on every rank for equal sizes)
     Q36_GDS();
     Q36_TR_BEGIN(status, 6)
-    const unsigned epoch = (unsigned)ctl[0] + 1u;
+    const unsigned epoch = (unsigned)ctl[2] + 1u;
     const bool odd = epoch & 1u;
     if (threadIdx.x < world) {
         const unsigned *h = reinterpret_cast<const unsigned *>(win + (odd ? rhdr1 : rhdr0) + 8 * threadIdx.x);
@@ -361,7 +365,7 @@ k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t 
     if (s_last) {   // the call is over: clear this parity's arrival counts (their next use is two calls away), next call
         if (threadIdx.x < world) *reinterpret_cast<unsigned long long *>(const_cast<uint8_t *>(win) + (odd ? rhdr1 : rhdr0) + 8 * threadIdx.x) = 0ull;
         __syncthreads();
-        if (threadIdx.x == 0) { ctl[3] = 0; ctl[0] = (int)epoch; }
+        if (threadIdx.x == 0) { ctl[3] = 0; ctl[2] = (int)epoch; }
     }
     Q36_TR_END(status, 6)
 }
@@ -472,7 +476,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     const bool use_nccl = c->transport == EP_TRANSPORT_NCCL;
     NcclApi *api = use_nccl ? nccl() : nullptr;
     if (use_nccl && (!api || c->kind != EP_KIND_PROCS)) return Q36_MOE_EINVAL;
-    const int par = (int)((c->calls + 1) & 1);                    // NCCL transport only (host mirror of the call counter)
+    const int par = (int)((c->calls[phase < 3 && phase >= 0 ? phase : 0] + 1) & 1);   // NCCL transport only (host mirror of the phase's call counter)
     int rc;
     if (phase == 0) {
         // route + dispatch over ALL experts (their order is the destination-rank order); quantise the rank's tokens
@@ -503,6 +507,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             if ((rc = all_to_all(api, c, c->stage + L.rows[par], c->win + L.rows[par], (size_t)C * rowb, st))) return rc;
             if ((rc = all_to_all(api, c, c->stage + L.hdr[par], c->win + L.hdr[par], 8, st))) return rc;
         }
+        c->calls[0]++;
         return Q36_MOE_OK;
     }
     if (phase == 1) {
@@ -551,6 +556,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             if ((rc = all_to_all(api, c, c->stage + L.rhdr[par], c->win + L.rhdr[par], 8, st))) return rc;
             if ((rc = ckc(cudaMemsetAsync(c->stage + L.rhdr[par], 0, 8 * EP_MAX_WORLD, st)))) return rc;   // the staged arrival counts start at zero next time
         }
+        c->calls[1]++;
         return Q36_MOE_OK;
     }
     if (phase == 2) {
@@ -562,7 +568,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         launch_k(k_ep_combine, dim3((D / 4 + 255) / 256, T), dim3(256), 0, st, a.out, (const uint8_t *)c->win, L.ret[0], L.ret[1],
                  L.rhdr[0], L.rhdr[1], ctl, world, c->spin_limit, w.status, (const int *)w.ypos, (const float *)w.wt,
                  shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k, expected);
-        c->calls++;
+        c->calls[2]++;
         return check_launch();
     }
     return Q36_MOE_EINVAL;
@@ -657,7 +663,7 @@ int q36_moe_ep_open_window(void *comm, int T_max, int k, int D, int cap_rows) {
         if ((r = ckc(cudaMalloc((void **)&c->win, L.bytes)))) return r;
         if ((r = ckc(cudaMemset(c->win, 0, L.bytes)))) return r;
         if ((r = ckc(cudaMalloc((void **)&c->d_peer, sizeof(uint8_t *) * EP_MAX_WORLD)))) return r;
-        c->calls = 0;
+        c->calls[0] = c->calls[1] = c->calls[2] = 0;
         c->open = true;
         return Q36_MOE_OK;
     };

@@ -461,7 +461,7 @@ k_ep_recv_plan(const uint8_t *__restrict__ win, uint64_t off_hdr0, uint64_t off_
     __shared__ int s_cnt[64];
     const int tid = threadIdx.x;
     const int n = world * cap;
-    const unsigned epoch = (unsigned)(*ctr) + 1u;
+    const unsigned epoch = (unsigned)ctr[1] + 1u;   // (this rank's phase-1 call counter)
     const bool odd = epoch & 1u;
     const int used_warps = (n + 31) / 32;
     for (int i = tid; i < used_warps * DISPATCH_MAX_E; i += blockDim.x) (&sm.cnt[0][0])[i] = 0;
@@ -685,6 +685,8 @@ k_front_decode(const float *__restrict__ logits, int n_expert, int k, float scal
             const unsigned long long v = (unsigned long long)(unsigned)cnt | ((unsigned long long)ep_epoch << 32);
             asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(h), "l"(v) : "memory");
         }
+        __syncthreads();
+        if (tid == 0) ep.ctl[0] = (int)ep_epoch;      // phase 0 of this call is over (every CTA read the counter before the barriers above)
     }
     Q36_TR_END(status, 0)
 }

@@ -369,7 +369,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 __syncwarp();
                 if (lane == 0) asm volatile("red.release.cta.shared.add.s32 [%0], 1;" ::"r"(smem_u32(&s_pub)) : "memory");
             } else if (ep.peers && t.row0 < ep.n_map) {
-                const bool odd = ((unsigned)ep.ctl[0] + 1u) & 1u;
+                const bool odd = ((unsigned)ep.ctl[1] + 1u) & 1u;
                 const uint64_t roff = odd ? ep.ret1 : ep.ret0;
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
@@ -497,11 +497,13 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         // every CTA orders its remote stores (the barrier above gathered the epilogue warps') with one system-scope
         // fence, then counts itself in at every source rank: a home rank's combine waits for gridDim.x arrivals
         __threadfence_system();
-        const bool odd = ((unsigned)ep.ctl[0] + 1u) & 1u;
+        const unsigned epoch = (unsigned)ep.ctl[1] + 1u;
+        const bool odd = epoch & 1u;
         for (int src = 0; src < ep.world; src++) {
             unsigned *h = reinterpret_cast<unsigned *>(ep.peers[src] + (odd ? ep.rhdr1 : ep.rhdr0) + 8 * (ep.slot_major ? src : ep.me));
             asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(h) : "memory");
         }
+        if (atomicAdd(ep.ctl + 4, 1) == (int)gridDim.x - 1) { ep.ctl[4] = 0; ep.ctl[1] = (int)epoch; }   // the last CTA ends phase 1 of this call
     }
     Q36_TR_END(status, 4)
 }

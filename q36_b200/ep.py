@@ -187,9 +187,16 @@ class NativeEP:
         m.check(m.lib.q36_moe_ep_layer(self.comm, *_layer_args(m, ly, X, logits, out, self.ws)), "ep_layer")
         return out
 
-    def phase(self, p: int, ly, X, logits, out, stream=None):
+    def second_workspace(self):
+        """A second private workspace: calls whose phases overlap (phase 0 of the next call issued before phases 1 and
+        2 of this one) must alternate between two."""
+        w = torch.empty_like(self.ws)
+        self.moe.check(self.moe.lib.q36_moe_ws_reset(w.data_ptr(), self.moe.stream_ptr()), "ws_reset")
+        return w
+
+    def phase(self, p: int, ly, X, logits, out, stream=None, ws=None):
         m = self.moe
-        args = list(_layer_args(m, ly, X, logits, out, self.ws))
+        args = list(_layer_args(m, ly, X, logits, out, self.ws if ws is None else ws))
         if stream is not None:
             args[-1] = stream.cuda_stream
         m.check(m.lib.q36_moe_ep_layer_phase(self.comm, p, *args), f"ep_layer_phase {p}")
@@ -228,10 +235,10 @@ class LocalEP:
                 moe.check(moe.lib.q36_moe_ws_reset(w.data_ptr(), moe.stream_ptr()), "ws_reset")
             self.ws.append(w)
 
-    def phase(self, p: int, r: int, ly, X, logits, out):
+    def phase(self, p: int, r: int, ly, X, logits, out, ws=None):
         m = self.moe
         with torch.cuda.device(self.devices[r]):
-            return m.lib.q36_moe_ep_layer_phase(self.comms[r], p, *_layer_args(m, ly, X, logits, out, self.ws[r]))
+            return m.lib.q36_moe_ep_layer_phase(self.comms[r], p, *_layer_args(m, ly, X, logits, out, self.ws[r] if ws is None else ws))
 
     def layer(self, shards, Xs, Ls, outs):
         """One call on every rank: phase p of all ranks before phase p + 1 of any."""

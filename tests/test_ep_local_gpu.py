@@ -77,6 +77,45 @@ def test_local_ranks_match_the_single_gpu_layer(moe, full, world, T, same):
         loc.close()
 
 
+def test_phase_0_of_the_next_call_may_run_ahead(moe, full):
+    """Overlap: phase 0 (route + send) of call n + 1 is issued BEFORE phases 1 and 2 of call n, as a caller does to
+    hide the dispatch behind the previous call's expert work.  Each phase keeps its own call counter on the device
+    and the calls alternate between two private workspaces; the results must not change."""
+    import torch
+    from q36_b200 import ep
+    world, T, calls = 4, 8, 5
+    shards = _shards(moe, full, world)
+    loc = ep.LocalEP(world, [0] * world, T, E, K8, D, FF)
+    ws2 = [torch.zeros_like(w) for w in loc.ws]
+    try:
+        ins = [_inputs(world, T, 1200 + 10 * c) for c in range(calls)]
+        outs = [[torch.full((T, D), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)] for _ in range(calls)]
+        wsel = lambda c, r: None if c % 2 == 0 else ws2[r]
+
+        def phase(p, c):
+            for r in range(world):
+                moe.check(loc.phase(p, r, shards[r], ins[c][0][r], ins[c][1][r], outs[c][r], ws=wsel(c, r)), f"call {c} rank {r} phase {p}")
+
+        phase(0, 0)
+        for c in range(calls):
+            if c + 1 < calls:
+                phase(0, c + 1)           # ahead of this call's expert work and combine
+            phase(1, c)
+            phase(2, c)
+        torch.cuda.synchronize()
+        for c in range(calls):
+            for r in range(world):
+                ref = full.forward(ins[c][0][r], ins[c][1][r], path=moe.PATH_TC)
+                torch.cuda.synchronize()
+                err = float((outs[c][r] - ref).norm() / ref.norm())
+                assert err < 1e-5, f"call {c} rank {r}: rel-L2 {err}"
+        for r in range(world):
+            assert loc.status(r) == moe.OK
+            assert moe.lib.q36_moe_ws_status(ws2[r].data_ptr(), moe.stream_ptr()) == moe.OK
+    finally:
+        loc.close()
+
+
 def test_a_smaller_capacity_drops_rows_and_says_so(moe, full):
     """cap_rows below the worst case: rows beyond it are dropped (their term is missing from the sum), the status
     words say 0xD00, nothing hangs or overruns."""

@@ -187,7 +187,7 @@ def test_ffn_gemv_vs_oracle(moe, oracle, torch_cuda, layer, weights, T):
     _check_ffn(moe, oracle, torch_cuda, layer, weights, T, moe.PATH_GEMV, np.random.default_rng(20 + T))
 
 
-def _check_layer(moe, oracle, torch, layer, weights, T, path, rng, zipf=False, sample=6, bf16=True, **kw):
+def _check_layer(moe, oracle, torch, layer, weights, T, path, rng, zipf=False, sample=6, bf16=True, spread=False, **kw):
     X = synth.activations(rng, T, D)
     L = synth.router_logits(rng, T, E, zipf=zipf)
     xt = torch.from_numpy(X).cuda()
@@ -201,6 +201,12 @@ def _check_layer(moe, oracle, torch, layer, weights, T, path, rng, zipf=False, s
     widx, wwt = oracle.router_topk(L, K8, n_expert=E)
     np.testing.assert_array_equal(idx, widx)
     toks = rng.choice(T, size=min(sample, T), replace=False)
+    if spread and T > sample:
+        # half of the sample from the tokens whose rarest chosen expert is rarest overall (the tail of a skewed load:
+        # groups of a few rows), half at random (mostly the head: groups of thousands of rows)
+        load = np.bincount(widx.reshape(-1), minlength=E)
+        rare = np.argsort(load[widx].min(axis=1), kind="stable")[:sample // 2]
+        toks = np.unique(np.concatenate([rare, toks[:sample - rare.size]]))
     w = weights
     want = oracle.moe_layer(w["gate"], w["up"], w["down"], w["sgate"][0], w["sup"][0], w["sdown"][0], D, FF, X, widx,
                             wwt, L[:, E], tokens=toks, se0=layer.se0, se1=layer.se1,
@@ -476,7 +482,7 @@ def test_prefill_layer_full_size_zipf(moe, oracle, torch_cuda, layer, weights):
     torch = torch_cuda
     rng = np.random.default_rng(71)
     T = 4096
-    out = _check_layer(moe, oracle, torch, layer, weights, T, moe.PATH_TC, rng, zipf=True, sample=8)
+    out = _check_layer(moe, oracle, torch, layer, weights, T, moe.PATH_TC, rng, zipf=True, sample=64, spread=True)
     # permutation invariance: the same tokens in another order give the same rows
     rng = np.random.default_rng(71)
     X = synth.activations(rng, T, D)

@@ -78,12 +78,14 @@ constexpr unsigned EP_SPIN_LIMIT = 1u << 22;
 
 // Byte offsets inside a window, the same on every rank.
 struct WinLayout {
-    uint64_t hdr[2], rhdr[2], rows[2], ret[2], ctl, bytes;
-    int cap, D, world, row_bytes;
+    uint64_t hdr[2], rhdr[2], rows[2], ret[2], tslot[2], twt[2], ctl, bytes;
+    int cap, D, world, row_bytes, n_max, tstride;
 };
-static WinLayout win_layout(int world, int cap, int D) {
+// n_max: entries (tokens x k) one rank routes per call at most
+static WinLayout win_layout(int world, int cap, int D, int n_max) {
     WinLayout L;
-    L.cap = cap; L.D = D; L.world = world;
+    L.cap = cap; L.D = D; L.world = world; L.n_max = n_max;
+    L.tstride = n_max + 4;               // ints per source in a token table: [n_max] = the source's token count of the call
     L.row_bytes = D + D / Q36_QK + EP_TAIL;
     uint64_t o = 0;
     auto take = [&](uint64_t b) { const uint64_t r = o; o += (b + 255) & ~(uint64_t)255; return r; };
@@ -91,6 +93,9 @@ static WinLayout win_layout(int world, int cap, int D) {
     L.ctl = take(256);   // ints: [0..2] calls whose phase 0 / 1 / 2 has finished on this rank, [3..6] tickets of the "last block" patterns, [8 + r] per destination
     for (int p = 0; p < 2; p++) L.rows[p] = take((uint64_t)world * cap * L.row_bytes);
     for (int p = 0; p < 2; p++) L.ret[p] = take((uint64_t)world * cap * D * 4);
+    // token tables (reduced return): per source and entry (t, s) the slot its row went to on this rank (-1: another
+    // rank, or dropped) and its combine weight
+    for (int p = 0; p < 2; p++) { L.tslot[p] = take((uint64_t)world * L.tstride * 4); L.twt[p] = take((uint64_t)world * L.tstride * 4); }
     L.bytes = o;
     return L;
 }
@@ -144,7 +149,8 @@ __global__ void __launch_bounds__(1024)
 k_ep_send(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const int *__restrict__ idx,
           const int *__restrict__ eoffs, const int *__restrict__ elist, int world, int per, int k, int cap, int D,
           uint8_t *const *__restrict__ peers, int me, uint64_t rows0, uint64_t rows1, uint64_t hdr0, uint64_t hdr1, int *ctl,
-          int *__restrict__ ypos, int slot_major_dst, int *status, int nb) {
+          int *__restrict__ ypos, int slot_major_dst, int *status, int nb, const int *__restrict__ pos, const float *__restrict__ wt,
+          int n, int T, uint64_t tslot0, uint64_t tslot1, uint64_t twt0, uint64_t twt1, int tstride, int tables) {
     Q36_GDS();
     Q36_TR_BEGIN(status, 1)
     const int r = blockIdx.x / nb, b = blockIdx.x % nb;
@@ -186,6 +192,17 @@ k_ep_send(const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, const 
             ypos[entry] = -1;
             atomicCAS(status, 0, 0xD00);
         }
+    }
+    if (tables) {   // reduced return: entry i -> its slot on r (or -1) and its weight, + this rank's token count
+        int *ts = reinterpret_cast<int *>(peers[r] + (odd ? tslot1 : tslot0)) + (size_t)me * tstride;
+        float *tw = reinterpret_cast<float *>(peers[r] + (odd ? twt1 : twt0)) + (size_t)me * tstride;
+        for (int i = b * blockDim.x + threadIdx.x; i < n; i += nb * blockDim.x) {
+            const int j = pos[i] - base;
+            const bool mine = idx[i] / per == r && j < cap;
+            ts[i] = mine ? j : -1;
+            tw[i] = wt[i];
+        }
+        if (b == 0 && threadIdx.x == 0) ts[tstride - 4] = T;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -301,13 +318,73 @@ k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int
     Q36_TR_END(status, 5)
 }
 
+// Reduced return.  Blocks (s, b), b < nb: for the tokens t = b, b + nb, ... of source rank s, the weighted sum over
+// the token's entries that ran on this rank, in entry order (sum_s' wt * Y[lpos[slot]], slots and weights from the
+// token table s wrote with its rows), goes into row t of this rank's block of the result area in s's window: one
+// row per (token, expert rank) pair crosses the link instead of one per (token, expert).  Tokens without an entry
+// here are skipped; the home rank knows which those are.  Then the block counts itself in at s (as k_ep_return).
+__global__ void __launch_bounds__(512)
+k_ep_reduce_return(const float *__restrict__ Y, const int *__restrict__ lpos, const uint8_t *__restrict__ win, uint64_t tslot0,
+                   uint64_t tslot1, uint64_t twt0, uint64_t twt1, int tstride, int k, int world, int cap, int D,
+                   uint8_t *const *__restrict__ peers, int me, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1, int *ctl,
+                   int nb, int *status) {
+    Q36_GDS();
+    Q36_TR_BEGIN(status, 5)
+    const int s = blockIdx.x / nb, b = blockIdx.x % nb;
+    const unsigned epoch = (unsigned)ctl[1] + 1u;
+    const bool odd = epoch & 1u;
+    const int *ts = reinterpret_cast<const int *>(win + (odd ? tslot1 : tslot0)) + (size_t)s * tstride;
+    const float *tw = reinterpret_cast<const float *>(win + (odd ? twt1 : twt0)) + (size_t)s * tstride;
+    const int Ts = min(ts[tstride - 4], cap);
+    float *dst0 = reinterpret_cast<float *>(peers[s] + (odd ? ret1 : ret0) + (size_t)me * cap * D * 4);
+    constexpr int KMAX = 8;
+    for (int t = b; t < Ts; t += nb) {
+        int p[KMAX];
+        float w[KMAX];
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < KMAX; q++) {
+            const int j = (q < k) ? ts[(size_t)t * k + q] : -1;
+            any |= j >= 0;
+            p[q] = (j >= 0) ? lpos[s * cap + j] : -1;
+            w[q] = (q < k) ? tw[(size_t)t * k + q] : 0.f;
+        }
+        if (!any) continue;
+        for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+            float4 y[KMAX];
+#pragma unroll
+            for (int q = 0; q < KMAX; q++)
+                y[q] = (p[q] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[q] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < KMAX; q++) {
+                if (p[q] < 0) continue;
+                acc.x = fmaf(w[q], y[q].x, acc.x); acc.y = fmaf(w[q], y[q].y, acc.y);
+                acc.z = fmaf(w[q], y[q].z, acc.z); acc.w = fmaf(w[q], y[q].w, acc.w);
+            }
+            *reinterpret_cast<float4 *>(dst0 + (size_t)t * D + i) = acc;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        unsigned *h = reinterpret_cast<unsigned *>(peers[s] + (odd ? rhdr1 : rhdr0) + 8 * me);
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(h) : "memory");
+        if (atomicAdd(ctl + 6, 1) == (int)gridDim.x - 1) { ctl[6] = 0; ctl[1] = (int)epoch; }
+    }
+    Q36_TR_END(status, 5)
+}
+
 // k_moe_combine_pf (q36_engine.cu:3393-3401) on the home rank: waits (bounded) for every expert rank's results of
 // this call, then out[t] = sum_s wt[t][s] * ret[ypos[t*k+s]] + sigmoid(gate) * SH[t] in slot order.  The last
 // block to finish advances the call counter.  grid (D / 1024, T).
 __global__ void __launch_bounds__(256)
 k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1,
              int *ctl, int world, unsigned limit, int *status, const int *__restrict__ ypos, const float *__restrict__ wt,
-             const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k, unsigned expected) {
+             const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k, unsigned expected,
+             int reduced, int cap) {
+    // reduced: the expert ranks sent one weighted partial row per token (row r * cap + t for rank r): add those of
+    // the ranks that ran an entry of the token, in rank order
     // expected: arrivals every expert rank counts in at this rank's result header per call (the CTAs of its FFN
     // launch, or the blocks per source of its return kernel: the same on every rank for equal sizes)
     Q36_GDS();
@@ -338,6 +415,17 @@ k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t 
         for (int s = 0; s < KMAX; s++) {
             p[s] = (s < k) ? ypos[(size_t)t * k + s] : -1;
             w[s] = (s < k) ? wt[(size_t)t * k + s] : 0.f;
+        }
+        if (reduced) {
+            unsigned mask = 0;
+#pragma unroll
+            for (int s = 0; s < KMAX; s++)
+                if (p[s] >= 0) mask |= 1u << (p[s] / cap);
+#pragma unroll
+            for (int s = 0; s < KMAX; s++) {   // (world <= KMAX on this path: one candidate row per rank)
+                p[s] = (s < world && ((mask >> s) & 1u)) ? s * cap + t : -1;
+                w[s] = 1.f;
+            }
         }
         const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
         float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -458,6 +546,13 @@ struct LayerArgs {
     uint64_t ws_bytes;
 };
 
+// Two-launch (prefill-sized) calls over the peer transport return one weighted partial row per (token, expert rank)
+// instead of one row per (token, expert); the rows use the first T_max rows of each rank's block of the result area.
+static bool ep_reduced_return(const EpComm *c, bool one_launch) {
+    return !one_launch && c->transport != EP_TRANSPORT_NCCL && c->world <= 8 && c->T_max <= c->L.cap;
+}
+static int ep_reduce_blocks(const EpComm *c) { return max(1, min(512 / c->world, (c->T_max + 15) / 16)); }
+
 static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     const int world = c->world, rank = c->rank, E = a.E, k = a.k, D = a.D, FF = a.FF, T = a.T;
     if (!c->open) return Q36_MOE_EINVAL;
@@ -477,11 +572,15 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     NcclApi *api = use_nccl ? nccl() : nullptr;
     if (use_nccl && (!api || c->kind != EP_KIND_PROCS)) return Q36_MOE_EINVAL;
     const int par = (int)((c->calls[phase < 3 && phase >= 0 ? phase : 0] + 1) & 1);   // NCCL transport only (host mirror of the phase's call counter)
+    // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count (every
+    // rank takes the same decision for equal T)
+    const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
+    const bool reduced = ep_reduced_return(c, one_launch);
     int rc;
     if (phase == 0) {
         // route + dispatch over ALL experts (their order is the destination-rank order); quantise the rank's tokens
         // once, in token order (hw order inside the blocks): one cluster launch at decode sizes
-        const bool cluster_front = T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
+        const bool cluster_front = !reduced && T <= 16 && n <= 128 && D % 1024 == 0 && D * T <= 32 * 1024;
         if (cluster_front) {
             // ... and the rows go straight from the quantising warps into the destination ranks' windows
             const EpSendArgs sa{(uint8_t *const *)c->d_peer, L.rows[0], L.rows[1], L.hdr[0], L.hdr[1], ctl, w.ypos, rank, world, per, C, use_nccl ? 1 : 0};
@@ -501,7 +600,8 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         const int nb_send = max(1, min(32, (min(n, C) + 255) / 256));
         if (!cluster_front) launch_k(k_ep_send, dim3(world * nb_send), dim3(1024), 0, st, (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, (const int *)w.idx,
                  (const int *)w.eoffs, (const int *)w.elist, world, per, k, C, D, (uint8_t *const *)c->d_peer, rank, L.rows[0], L.rows[1],
-                 L.hdr[0], L.hdr[1], ctl, w.ypos, use_nccl ? 1 : 0, w.status, nb_send);
+                 L.hdr[0], L.hdr[1], ctl, w.ypos, use_nccl ? 1 : 0, w.status, nb_send, (const int *)w.pos, (const float *)w.wt, n, T,
+                 L.tslot[0], L.tslot[1], L.twt[0], L.twt[1], L.tstride, reduced ? 1 : 0);
         if ((rc = check_launch())) return rc;
         if (use_nccl) {   // staging blocks (indexed by destination) -> the destinations' windows (indexed by source)
             if ((rc = all_to_all(api, c, c->stage + L.rows[par], c->win + L.rows[par], (size_t)C * rowb, st))) return rc;
@@ -513,8 +613,6 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     if (phase == 1) {
         // local plan over the received slots
         const bool small_plan = S <= 1024;   // one block waits, sorts the slots and writes the work plan
-        // the one-launch decode kernel: always when no expert can receive more than 16 rows, else up to a row count
-        const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
         if (small_plan) {
             if ((rc = launch_ep_recv_plan(c->win, L.hdr[0], L.hdr[1], L.rows[0], L.rows[1], ctl, world, C, rowb, D + nbs, c->spin_limit,
                                           w.status, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs, R, shared ? R + T : R,
@@ -548,7 +646,12 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         // (two launches: a kernel of its own puts the result rows into their home ranks' windows)
         // blocks per source: one while a pair of ranks exchanges at most 64 rows (a single fence on the way), else one per 64
         const int nb_ret = max(1, min(32, (min(c->T_max * k, C) + 63) / 64));
-        if (!one_launch) launch_k(k_ep_return, dim3(world * nb_ret), dim3(1024), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
+        if (reduced) {
+            const int nb = ep_reduce_blocks(c);
+            launch_k(k_ep_reduce_return, dim3(world * nb), dim3(512), 0, st, (const float *)w.Y, (const int *)w.lpos, (const uint8_t *)c->win,
+                     L.tslot[0], L.tslot[1], L.twt[0], L.twt[1], L.tstride, k, world, C, D, (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1],
+                     L.rhdr[0], L.rhdr[1], ctl, nb, w.status);
+        } else if (!one_launch) launch_k(k_ep_return, dim3(world * nb_ret), dim3(1024), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
                  (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0, nb_ret, w.status);
         if ((rc = check_launch())) return rc;
         if (use_nccl) {
@@ -561,13 +664,13 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     }
     if (phase == 2) {
         // what every expert rank counts in at this rank per call: the CTAs of its one-launch FFN, else its return blocks
-        const bool peers_one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
-        const unsigned expected = peers_one_launch ? (unsigned)ffn_fused_small_grid(R + T, per, D, FF)
+        const unsigned expected = one_launch ? (unsigned)ffn_fused_small_grid(R + T, per, D, FF)
+                                  : reduced        ? (unsigned)ep_reduce_blocks(c)
                                                    : (unsigned)max(1, min(32, (min(c->T_max * k, C) + 63) / 64));
         const float *shg = (shared && a.shgate_col >= 0) ? a.logits + a.shgate_col : nullptr;
         launch_k(k_ep_combine, dim3((D / 4 + 255) / 256, T), dim3(256), 0, st, a.out, (const uint8_t *)c->win, L.ret[0], L.ret[1],
                  L.rhdr[0], L.rhdr[1], ctl, world, c->spin_limit, w.status, (const int *)w.ypos, (const float *)w.wt,
-                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k, expected);
+                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k, expected, reduced ? 1 : 0, C);
         c->calls[2]++;
         return check_launch();
     }
@@ -653,7 +756,7 @@ int q36_moe_ep_open_window(void *comm, int T_max, int k, int D, int cap_rows) {
     int dev0 = 0;
     cudaGetDevice(&dev0);
     const int world = c0->world;
-    const WinLayout L = win_layout(world, cap_rows ? cap_rows : T_max * k, D);
+    const WinLayout L = win_layout(world, cap_rows ? cap_rows : T_max * k, D, T_max * k);
     int rc = Q36_MOE_OK;
     auto alloc_one = [&](EpComm *c) -> int {
         close_window(c);

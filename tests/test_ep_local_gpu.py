@@ -77,6 +77,31 @@ def test_local_ranks_match_the_single_gpu_layer(moe, full, world, T, same):
         loc.close()
 
 
+def test_prefill_sized_calls_return_one_partial_row_per_token_and_rank(moe, full):
+    """Two-launch calls over the peer transport: the expert ranks sum a token's rows with the combine weights and
+    return one row per (token, rank).  Window capacity 1.5 x the mean, as the prefill stack uses; the second call
+    has fewer tokens than the window was opened for."""
+    import torch
+    from q36_b200 import ep
+    world, T_max = 4, 1024
+    shards = _shards(moe, full, world)
+    loc = ep.LocalEP(world, [0] * world, T_max, E, K8, D, FF, cap_rows=T_max * K8 * 3 // (2 * world))
+    try:
+        for call, T in enumerate((T_max, 900, T_max)):
+            Xs, Ls = _inputs(world, T, 700 + 10 * call)
+            outs = [torch.full((T, D), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+            loc.layer(shards, Xs, Ls, outs)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert loc.status(r) == moe.OK, f"rank {r}: device status {moe.lib.q36_moe_last_cuda_error()}"
+                ref = full.forward(Xs[r], Ls[r], path=moe.PATH_TC)
+                torch.cuda.synchronize()
+                err = float((outs[r] - ref).norm() / ref.norm())
+                assert err < 1e-5, f"call {call} rank {r}: rel-L2 vs single-GPU layer {err}"
+    finally:
+        loc.close()
+
+
 def test_phase_0_of_the_next_call_may_run_ahead(moe, full):
     """Overlap: phase 0 (route + send) of call n + 1 is issued BEFORE phases 1 and 2 of call n, as a caller does to
     hide the dispatch behind the previous call's expert work.  Each phase keeps its own call counter on the device

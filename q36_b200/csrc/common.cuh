@@ -73,6 +73,34 @@ inline void launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
     cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// The same for a kernel whose blocks wait for one another: the cooperative attribute makes the runtime refuse the
+// launch unless every block can be resident at once (instead of that being true by construction only).  Measured:
+// no cost (1.450 against 1.445 ms per 40-layer step), and it combines with the programmatic-launch attribute inside a
+// captured graph.  Q36_COOP=0 in the environment turns it off; 2 = cooperative without the programmatic attribute.
+inline int coop_mode() {
+    static int mode = -1;
+    if (mode < 0) { const char *e = getenv("Q36_COOP"); mode = e ? atoi(e) : 1; }
+    return mode;
+}
+template <typename... KArgs, typename... Args>
+inline void launch_k_resident(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    const int mode = coop_mode();
+    if (mode == 0) { launch_k(kern, grid, block, smem, st, args...); return; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (mode == 1 && pdl_enabled()) ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Smallest e2 with amax <= 448 * 2^e2, clamped to [-127,127]; 0 -> -127.
 // Integer form of ceil(log2(amax/448)) (q36_engine.cu:2421); 448 = 1.75 * 2^8.
 __device__ __forceinline__ int e2_of_amax(float amax) {

@@ -67,7 +67,10 @@ struct TcCfg {
     static constexpr int SFR_BYTES = (NA + 1) * SFR_PART;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFR_SLOTS * SFR_BYTES + 1024 /* alignment */ + 512 /* barriers */;
     static constexpr int ACC_STRIDE = (NA == 2) ? 256 : 128; // TMEM columns between the two accumulator sets
-    static constexpr int SF_COL0 = (NA == 2) ? 224 : 256;    // per issuer: A (4), B (4)
+    // scale columns of stage s: one 4-column image per A operand, then the token rows' (gate/up: the columns the two
+    // accumulator sets of 2 x 112 leave free in each half of the 512)
+    static constexpr int SF_COLS = 4 * (NA + 1);
+    __host__ __device__ static constexpr int sf_col(int s) { return (NA == 2) ? ((s < 2 ? 224 : 456) + SF_COLS * s) : 256 + SF_COLS * s; }
     static constexpr int TMEM_COLS = 512;
     static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
     static constexpr int EPI_WARPS = 8;                      // two per TMEM lane quarter, alternating 32-column chunks
@@ -221,11 +224,11 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         }
     } else if (warp <= Cfg::ISSUERS) {
         // ----------------------------------------------------- MMA issuers
-        // NA = 2: issuer 0 drives the gate matrix, issuer 1 the up matrix of the SAME stage; each copies its own
-        // weight-scale image and its own copy of the token-scale image into its own TMEM columns.
+        // NA = 2: issuer 0 drives the gate matrix, issuer 1 the up matrix of the SAME stage.  The scale images are in
+        // TMEM already when the stage is full: the loader warps store them there (tcgen05.st), so that no
+        // tcgen05.cp sits between the MMAs in the tensor pipe (four of them cost as much as the eight MMAs of a K step).
         if (lane == 0) {
             const int w = warp - 1;
-            const uint32_t t_sfa = tmem + Cfg::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
@@ -242,9 +245,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                     if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
                     tc_fence_after();
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t sf = sb + NA * Cfg::A_BYTES + Cfg::B_BYTES;
-                    tc_cp_sf(t_sfa, desc_sf(sf + w * Cfg::SF_BYTES));
-                    tc_cp_sf(t_sfb, desc_sf(sf + NA * Cfg::SF_BYTES));
+                    const uint32_t t_sfa = tmem + Cfg::sf_col(s) + 4 * w, t_sfb = tmem + Cfg::sf_col(s) + 4 * NA;
 #pragma unroll
                     for (int kb = 0; kb < 4; kb++) {
                         const uint32_t sfid = (uint32_t)kb << 30;
@@ -299,45 +300,49 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         }
     } else {
         // --------------------------------------------------- scale loaders
-        // Thread i owns row i of the tile: per stage it moves the row's 4 scale bytes of that K step from the
-        // staged item into the 32 x 16 B image tcgen05.cp broadcasts (row m at (m % 32) * 16 + (m / 32) * 4).
-        const int i = threadIdx.x - 32 * (1 + Cfg::ISSUERS + Cfg::EPI_WARPS);
-        const int w4 = i >> 5, m0 = i & 31;
-        const uint32_t my_off = m0 * 16 + w4 * 4;
+        // The scale image of an operand for one K step is 32 lanes x 4 columns in each TMEM lane quarter: lane l,
+        // column j, byte kb = scale of row l + 32 * j for K block kb -- one aligned word of the row's 16 staged
+        // bytes.  Each of the four warps writes the image into its own lane quarter (the four copies the MMA
+        // reads), lane = thread: four rows' words per operand per K step, straight from the staged item.
+        const int q = warp & 3;
         uint32_t it = 0, item = 0;
         bool ok = true;
         for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
             const TcTile t = get_tile(ti);
-            const bool bvalid = i < t.nrows;
             for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
                 const uint32_t sl = item % Cfg::SFR_SLOTS;
                 if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + i * 16;
-                const uint4 a0 = *reinterpret_cast<const uint4 *>(src);
-                const uint4 a1 = (NA == 2) ? *reinterpret_cast<const uint4 *>(src + Cfg::SFR_PART) : make_uint4(0, 0, 0, 0);
-                uint4 b = *reinterpret_cast<const uint4 *>(src + NA * Cfg::SFR_PART);
-                if (!bvalid) b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-                const uint32_t wa0[4] = {a0.x, a0.y, a0.z, a0.w}, wa1[4] = {a1.x, a1.y, a1.z, a1.w}, wb[4] = {b.x, b.y, b.z, b.w};
-                const uint32_t it0 = it;
+                const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + lane * 16;
+                uint32_t wa0[4][4], wa1[4][4], wb[4][4];      // [row l + 32 j][K step of the item]
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
+                    const uint4 a0 = *reinterpret_cast<const uint4 *>(src + j * 512);
+                    wa0[j][0] = a0.x; wa0[j][1] = a0.y; wa0[j][2] = a0.z; wa0[j][3] = a0.w;
+                    if (NA == 2) {
+                        const uint4 a1 = *reinterpret_cast<const uint4 *>(src + Cfg::SFR_PART + j * 512);
+                        wa1[j][0] = a1.x; wa1[j][1] = a1.y; wa1[j][2] = a1.z; wa1[j][3] = a1.w;
+                    }
+                    uint4 b = *reinterpret_cast<const uint4 *>(src + NA * Cfg::SFR_PART + j * 512);
+                    if (lane + 32 * j >= t.nrows) b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
+                    wb[j][0] = b.x; wb[j][1] = b.y; wb[j][2] = b.z; wb[j][3] = b.w;
+                }
+#pragma unroll
+                for (int x = 0; x < 4; x++) {
                     const int s = it % Cfg::STAGES;
                     const uint32_t ph = (it / Cfg::STAGES) & 1;
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                    uint8_t *sf = smem + s * Cfg::STAGE_BYTES + NA * Cfg::A_BYTES + Cfg::B_BYTES;
-                    *reinterpret_cast<uint32_t *>(sf + my_off) = wa0[j];
-                    if (NA == 2) *reinterpret_cast<uint32_t *>(sf + Cfg::SF_BYTES + my_off) = wa1[j];
-                    *reinterpret_cast<uint32_t *>(sf + NA * Cfg::SF_BYTES + my_off) = wb[j];
+                    tc_fence_after();
+                    const uint32_t tq = tmem + Cfg::sf_col(s) + ((uint32_t)(q * 32) << 16);
+                    tc_st4(tq, wa0[0][x], wa0[1][x], wa0[2][x], wa0[3][x]);
+                    if (NA == 2) tc_st4(tq + 4, wa1[0][x], wa1[1][x], wa1[2][x], wa1[3][x]);
+                    tc_st4(tq + 4 * NA, wb[0][x], wb[1][x], wb[2][x], wb[3][x]);
+                    tc_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full0 + 8 * s);
                     it++;
-                    if (Cfg::STAGES < 6 || j == 3) {   // few stages: hand each over at once; else one fence per item
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(full0 + 8 * s);
-                    }
                 }
                 if (!ok) break;
-                if (Cfg::STAGES >= 6 && lane == 0)
-                    for (uint32_t x = it0; x + 1 < it; x++) mbar_arrive(full0 + 8 * (x % Cfg::STAGES));
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
             }

@@ -547,7 +547,7 @@ int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const
     static bool attr_done[MAX_DEVICES] = {false};
     if ((rc = ensure_smem_attr((const void *)k_ffn_fused_small, Cfg::SMEM_BYTES, attr_done))) return rc;
     const int grid = ffn_fused_small_grid(R_max, n_group, D, FF);
-    launch_k(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
+    launch_k_resident(k_ffn_fused_small, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, (const uint8_t *)Wg + plane,
              (const uint8_t *)Wu + plane, (const uint8_t *)Wd + plane, estride, (const uint8_t *)Sg + plane,
              (const uint8_t *)Su + plane, (const uint8_t *)Sd + plane, n_group, Xs, (TcPlan *)plan, Hq, Hs, Y, D, FF, status,
              ep ? *ep : EpReturnArgs{nullptr, 0, 0, 0, 0, nullptr, nullptr, 0, 0, 0, 0, 0});

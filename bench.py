@@ -57,6 +57,11 @@ def parse():
                          "the ranks with the dispatch of layer l + 1 overlapped with the expert work of layer l")
     ap.add_argument("--stack-tokens", type=int, default=32768)
     ap.add_argument("--no-overlap", action="store_true", help="--prefill-stack: every phase on one stream")
+    ap.add_argument("--table", action="store_true",
+                    help="one GPU: a pp / tg / batch-width table over the layer stack, mean and std over -r repetitions (wall clock)")
+    ap.add_argument("-p", dest="pp", default="512,2048,4096", help="--table: prefill sizes")
+    ap.add_argument("-n", dest="tg", type=int, default=128, help="--table: decode steps per repetition")
+    ap.add_argument("-r", dest="reps", type=int, default=3, help="--table: repetitions")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-config3", action="store_true", help="skip the fixed-batch line (64 tokens in all, split over the ranks)")
     ap.add_argument("--no-roofline", action="store_true")
@@ -778,8 +783,69 @@ def run_prefill_stack(args):
             sys.exit(3)
 
 
+def run_table(args):
+    """The caller loop around the layer stack, reported the way the engine's own harness reports a model
+    (bench.c:306-335: `pp<N>` = N prompt tokens through the stack once, `tg<N>` = N single-token steps, each mean
+    and sample standard deviation of tokens/s over -r repetitions timed by the wall clock around a synchronised
+    region; bench.c:283-305: a step at batch width B against B = 1).  Every size runs as one CUDA graph of the whole
+    stack with the path q36_moe_layer picks for it."""
+    import torch
+    from q36_b200 import ep, moe, synth
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    NL = args.layers
+    layers, _ = make_layers(torch, moe, 1, 0, dev, NL)
+    path = {"auto": moe.PATH_AUTO, "gemv": moe.PATH_GEMV, "tc": moe.PATH_TC}[args.path]
+
+    def stack_for(T):
+        st = Stack(torch, None, moe, synth, ep, layers, 1, 0, dev, T, path, ep.TRANSPORT_PEER, False)
+        st.capture(True)
+        for _ in range(3):
+            st.run()
+        torch.cuda.synchronize()
+        return st
+
+    def rates(st, calls, tokens):
+        out = []
+        for _ in range(max(1, args.reps)):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                st.run()
+            torch.cuda.synchronize()
+            out.append(tokens / (time.perf_counter() - t0))
+        st.check()
+        return statistics.fmean(out), (statistics.stdev(out) if len(out) > 1 else 0.0)
+
+    name = f"moe-stack-{NL}x({E}+1)xMXFP4"
+    print("| model | test | t/s |\n|---|---|---:|")
+    for T in [int(x) for x in args.pp.split(",") if x]:
+        st = stack_for(T)
+        m, sd = rates(st, 1, T)
+        print(f"| {name} | pp{T} | {m:.1f} \u00b1 {sd:.1f} |", flush=True)
+        st.close()
+        del st
+    st = stack_for(1)
+    m, sd = rates(st, args.tg, args.tg)
+    print(f"| {name} | tg{args.tg} | {m:.1f} \u00b1 {sd:.1f} |", flush=True)
+    print("\n| batch B | step ms | vs B=1 |\n|---|---:|---:|")
+    t1 = None
+    for B in (1, 2, 4, 8, 16, 32):
+        if B > 1:
+            st.close()
+            st = stack_for(B)
+        m, _ = rates(st, 20, 20)          # steps per second
+        ms = 1e3 / m
+        t1 = ms if t1 is None else t1
+        print(f"| {B} | {ms:.3f} | {t1 * B / ms:.2f}x |", flush=True)
+    st.close()
+
+
 def main():
     args = parse()
+    if args.table:
+        run_table(args)
+        return
     if args.prefill_stack:
         run_prefill_stack(args)
         return

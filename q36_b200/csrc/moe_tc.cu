@@ -31,6 +31,7 @@
 #include "common.cuh"
 #include "kernels.cuh"
 #include "tc_plan.cuh"
+#include <cstdio>
 #include "tc_ptx.cuh"
 
 namespace q36 {
@@ -73,8 +74,14 @@ struct TcCfg {
     __host__ __device__ static constexpr int sf_col(int s) { return (NA == 2) ? ((s < 2 ? 224 : 456) + SF_COLS * s) : 256 + SF_COLS * s; }
     static constexpr int TMEM_COLS = 512;
     static constexpr int B_FULL_MIN = 49;                    // token tiles of at least this many rows use one big box
-    static constexpr int EPI_WARPS = 8;                      // two per TMEM lane quarter, alternating 32-column chunks
-    static constexpr int THREADS = 32 * (1 + ISSUERS + EPI_WARPS + 4);
+    // Warps: 0 weight producer, 1 token-row + scale-item producer, 2..3 MMA issuers (3 idle for NA = 1), 4..7 scale
+    // loaders, 8.. epilogue: every role group is a whole, aligned group of four warps so that the gate/up kernel can
+    // move registers from the first eight warps to its epilogue warps (setmaxnreg works on such groups).
+    static constexpr int EPI_WARP0 = 8;
+    static constexpr int EPI_WARPS = (NA == 2) ? 16 : 8;     // EPI_WARPS / 4 per TMEM lane quarter, taking 16-column batches in turn
+    static constexpr int THREADS = 32 * (EPI_WARP0 + EPI_WARPS);
+    static constexpr bool REBALANCE = (NA == 2);             // 768 threads x 80 registers at launch -> 256 x 40 + 512 x 96
+    static constexpr int REGS_LOW = 40, REGS_EPI = 96;
 };
 
 // ------------------------------------------------------------- tile plan
@@ -137,7 +144,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < Cfg::STAGES; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4);               // producer's expect_tx arrive + one arrive per scale warp
+            mbar_init(full0 + 8 * s, 2 + 4);               // each producer's expect_tx arrive + one arrive per scale warp
             mbar_init(empty0 + 8 * s, Cfg::ISSUERS);       // one tcgen05.commit per issuing warp
         }
         for (int b = 0; b < 2; b++) {
@@ -150,7 +157,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 2) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -181,113 +188,212 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         return TcTile{g, mt, s_row0[g] + nt * Cfg::N, min(Cfg::N, s_cnt[g] - nt * Cfg::N)};
     };
 
-    if (warp == 0) {
-        // ---------------------------------------------------- TMA producer
-        if (lane == 0) {
+    if (warp < Cfg::EPI_WARP0) {
+        if (Cfg::REBALANCE) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_LOW));
+        if (warp == 0) {
+            // ------------------------------------------- TMA producer: weights
+            // (One thread needs ~140 cycles to issue a copy whatever its size, ~300 with the wait and the expect_tx: all
+            // of a K step's copies from one thread took longer than the step's MMAs.  Two threads share them.)
+            if (lane == 0) {
+                uint32_t it = 0;
+                bool ok = true;
+                for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
+                    const TcTile t = get_tile(ti);
+                    const bool sh = t.g >= n_routed;
+                    const CUtensorMap *ma0 = sh ? &maps.s0 : &maps.a0, *ma1 = sh ? &maps.s1 : &maps.a1;
+                    const int ge = sh ? 0 : t.g;
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        const int s = it % Cfg::STAGES;
+                        const uint32_t ph = (it / Cfg::STAGES) & 1;
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                        mbar_expect_tx(full0 + 8 * s, NA * Cfg::A_TX_BYTES);
+                        tma_load_3d(sb, ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                        if (NA == 2) tma_load_3d(sb + Cfg::A_BYTES, ma1, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // --------------------------- TMA producer: token rows and scale items
+            if (lane == 0) {
+                uint32_t it = 0, item = 0;
+                bool ok = true;
+                for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
+                    const TcTile t = get_tile(ti);
+                    const bool sh = t.g >= n_routed;
+                    const CUtensorMap *fa0 = sh ? &maps.fs0 : &maps.fa0, *fa1 = sh ? &maps.fs1 : &maps.fa1;
+                    const int ge = sh ? 0 : t.g;
+                    const bool full_box = t.nrows >= Cfg::B_FULL_MIN;
+                    const int slabs = (t.nrows + 15) / 16;
+                    const uint32_t tx = full_box ? Cfg::N * 128 : slabs * 2048;
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        if ((ks & 3) == 0) {   // the scale bytes of the next four K steps
+                            const uint32_t sl = item % Cfg::SFR_SLOTS;
+                            if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / Cfg::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                            const uint32_t dst = smem_u32(sfr + sl * Cfg::SFR_BYTES);
+                            mbar_expect_tx(sfr_full0 + 8 * sl, NA * Cfg::SFR_PART + Cfg::N * 16);
+                            tma_load_3d(dst, fa0, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                            if (NA == 2) tma_load_3d(dst + Cfg::SFR_PART, fa1, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                            tma_load_2d(dst + NA * Cfg::SFR_PART, &maps.fb, 4 * ks, t.row0, sfr_full0 + 8 * sl);
+                            item++;
+                        }
+                        const int s = it % Cfg::STAGES;
+                        const uint32_t ph = (it / Cfg::STAGES) & 1;
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x900 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                        mbar_expect_tx(full0 + 8 * s, tx);
+                        if (full_box) {
+                            tma_load_2d(sb + NA * Cfg::A_BYTES, &maps.bfull, ks * TC_KSTEP, t.row0, full0 + 8 * s);
+                        } else {
+                            for (int i = 0; i < slabs; i++)
+                                tma_load_2d(sb + NA * Cfg::A_BYTES + i * 2048, &maps.b16, ks * TC_KSTEP, t.row0 + 16 * i, full0 + 8 * s);
+                        }
+                    }
+                }
+            }
+        } else if (warp < 4) {
+            // ----------------------------------------------------- MMA issuers
+            // NA = 2: issuer 0 drives the gate matrix, issuer 1 the up matrix of the SAME stage.  The scale images are in
+            // TMEM already when the stage is full: the loader warps store them there (tcgen05.st), so that no
+            // tcgen05.cp sits between the MMAs in the tensor pipe (four of them cost as much as the eight MMAs of a K step).
+            if (lane == 0 && warp - 2 < Cfg::ISSUERS) {
+                const int w = warp - 2;
+                uint32_t it = 0, tcount = 0;
+                bool ok = true;
+#ifdef Q36_TCPROF
+                long long pf_full = 0, pf_acc = 0, pf_t0 = clock64();
+#endif
+                for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
+                    const TcTile t = get_tile(ti);
+                    const int n_mma = (t.nrows >= Cfg::B_FULL_MIN) ? Cfg::N : max(16, (t.nrows + 15) & ~15);
+                    const uint32_t buf = tcount & 1;
+                    const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE + w * Cfg::N;
+                    // this accumulator set must have been drained by the epilogue two tiles ago
+#ifdef Q36_TCPROF
+                    long long pf_a = clock64();
+#endif
+                    if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
+#ifdef Q36_TCPROF
+                    pf_acc += clock64() - pf_a;
+#endif
+                    tc_fence_after();
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        const int s = it % Cfg::STAGES;
+                        const uint32_t ph = (it / Cfg::STAGES) & 1;
+#ifdef Q36_TCPROF
+                        long long pf_b = clock64();
+#endif
+                        if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
+#ifdef Q36_TCPROF
+                        pf_full += clock64() - pf_b;
+#endif
+                        tc_fence_after();
+                        const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                        const uint32_t t_sfa = tmem + Cfg::sf_col(s) + 4 * w, t_sfb = tmem + Cfg::sf_col(s) + 4 * NA;
+    #pragma unroll
+                        for (int kb = 0; kb < 4; kb++) {
+                            const uint32_t sfid = (uint32_t)kb << 30;
+                            tc_mma(d_tmem, desc_sw128(sb + w * Cfg::A_BYTES + kb * 32), desc_sw128(sb + NA * Cfg::A_BYTES + kb * 32),
+                                   idesc_mx(n_mma, kb), t_sfa | sfid, t_sfb | sfid, (ks | kb) ? 1u : 0u);
+                        }
+                        tc_commit(empty0 + 8 * s);   // stage reusable once every issuer's MMAs have read it
+                    }
+                    if (ok) tc_commit(acc_full0 + 8 * buf);
+                }
+#ifdef Q36_TCPROF
+                if (NA == 2 && w == 0 && (blockIdx.x == 0 || blockIdx.x == 77))
+                    printf("issuer cta %d: tiles %u total %lld wait_full %lld wait_acc %lld\n", blockIdx.x, tcount, clock64() - pf_t0, pf_full, pf_acc);
+#endif
+            }
+        } else {
+            // --------------------------------------------------- scale loaders (warps 4..7)
+            // The scale image of an operand for one K step is 32 lanes x 4 columns in each TMEM lane quarter: lane l,
+            // column j, byte kb = scale of row l + 32 * j for K block kb -- one aligned word of the row's 16 staged
+            // bytes.  Each of the four warps writes the image into its own lane quarter (the four copies the MMA
+            // reads), lane = thread: four rows' words per operand per K step, straight from the staged item.
+            const int q = warp & 3;
             uint32_t it = 0, item = 0;
             bool ok = true;
             for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
                 const TcTile t = get_tile(ti);
-                const bool sh = t.g >= n_routed;
-                const CUtensorMap *ma0 = sh ? &maps.s0 : &maps.a0, *ma1 = sh ? &maps.s1 : &maps.a1;
-                const CUtensorMap *fa0 = sh ? &maps.fs0 : &maps.fa0, *fa1 = sh ? &maps.fs1 : &maps.fa1;
-                const int ge = sh ? 0 : t.g;
-                const bool full_box = t.nrows >= Cfg::B_FULL_MIN;
-                const int slabs = (t.nrows + 15) / 16;
-                const uint32_t tx = NA * Cfg::A_TX_BYTES + (full_box ? Cfg::N * 128 : slabs * 2048);
-                for (int ks = 0; ks < k_steps; ks++, it++) {
-                    if ((ks & 3) == 0) {   // the scale bytes of the next four K steps
-                        const uint32_t sl = item % Cfg::SFR_SLOTS;
-                        if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / Cfg::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                        const uint32_t dst = smem_u32(sfr + sl * Cfg::SFR_BYTES);
-                        mbar_expect_tx(sfr_full0 + 8 * sl, NA * Cfg::SFR_PART + Cfg::N * 16);
-                        tma_load_3d(dst, fa0, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
-                        if (NA == 2) tma_load_3d(dst + Cfg::SFR_PART, fa1, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
-                        tma_load_2d(dst + NA * Cfg::SFR_PART, &maps.fb, 4 * ks, t.row0, sfr_full0 + 8 * sl);
-                        item++;
+                for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
+                    const uint32_t sl = item % Cfg::SFR_SLOTS;
+                    if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                    const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + lane * 16;
+                    // rows beyond the tile's: scale 1.0 instead of stale bytes (a 0xff byte would be a NaN)
+                    bool bval[4];
+    #pragma unroll
+                    for (int j = 0; j < 4; j++) bval[j] = lane + 32 * j < t.nrows;
+    #pragma unroll
+                    for (int x = 0; x < 4; x++) {                 // K step x of the item: word x of the rows l + 32 j
+                        uint32_t wa0[4], wa1[4], wb[4];
+    #pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            wa0[j] = *reinterpret_cast<const uint32_t *>(src + j * 512 + 4 * x);
+                            wa1[j] = (NA == 2) ? *reinterpret_cast<const uint32_t *>(src + Cfg::SFR_PART + j * 512 + 4 * x) : 0u;
+                            wb[j] = bval[j] ? *reinterpret_cast<const uint32_t *>(src + NA * Cfg::SFR_PART + j * 512 + 4 * x) : 0x7f7f7f7fu;
+                        }
+                        const int s = it % Cfg::STAGES;
+                        const uint32_t ph = (it / Cfg::STAGES) & 1;
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        tc_fence_after();
+                        const uint32_t tq = tmem + Cfg::sf_col(s) + ((uint32_t)(q * 32) << 16);
+                        tc_st4(tq, wa0[0], wa0[1], wa0[2], wa0[3]);
+                        if (NA == 2) tc_st4(tq + 4, wa1[0], wa1[1], wa1[2], wa1[3]);
+                        tc_st4(tq + 4 * NA, wb[0], wb[1], wb[2], wb[3]);
+                        tc_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full0 + 8 * s);
+                        it++;
                     }
-                    const int s = it % Cfg::STAGES;
-                    const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                    const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    mbar_expect_tx(full0 + 8 * s, tx);
-                    tma_load_3d(sb, ma0, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
-                    if (NA == 2) tma_load_3d(sb + Cfg::A_BYTES, ma1, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
-                    if (full_box) {
-                        tma_load_2d(sb + NA * Cfg::A_BYTES, &maps.bfull, ks * TC_KSTEP, t.row0, full0 + 8 * s);
-                    } else {
-                        for (int i = 0; i < slabs; i++)
-                            tma_load_2d(sb + NA * Cfg::A_BYTES + i * 2048, &maps.b16, ks * TC_KSTEP, t.row0 + 16 * i, full0 + 8 * s);
-                    }
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
                 }
             }
         }
-    } else if (warp <= Cfg::ISSUERS) {
-        // ----------------------------------------------------- MMA issuers
-        // NA = 2: issuer 0 drives the gate matrix, issuer 1 the up matrix of the SAME stage.  The scale images are in
-        // TMEM already when the stage is full: the loader warps store them there (tcgen05.st), so that no
-        // tcgen05.cp sits between the MMAs in the tensor pipe (four of them cost as much as the eight MMAs of a K step).
-        if (lane == 0) {
-            const int w = warp - 1;
-            uint32_t it = 0, tcount = 0;
-            bool ok = true;
-            for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
-                const TcTile t = get_tile(ti);
-                const int n_mma = (t.nrows >= Cfg::B_FULL_MIN) ? Cfg::N : max(16, (t.nrows + 15) & ~15);
-                const uint32_t buf = tcount & 1;
-                const uint32_t d_tmem = tmem + buf * Cfg::ACC_STRIDE + w * Cfg::N;
-                // this accumulator set must have been drained by the epilogue two tiles ago
-                if (!(ok = mbar_wait(acc_empty0 + 8 * buf, ((tcount >> 1) & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
-                tc_fence_after();
-                for (int ks = 0; ks < k_steps; ks++, it++) {
-                    const int s = it % Cfg::STAGES;
-                    const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(full0 + 8 * s, ph, &abort_flag, status, 0x300 + s))) break;
-                    tc_fence_after();
-                    const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint32_t t_sfa = tmem + Cfg::sf_col(s) + 4 * w, t_sfb = tmem + Cfg::sf_col(s) + 4 * NA;
-#pragma unroll
-                    for (int kb = 0; kb < 4; kb++) {
-                        const uint32_t sfid = (uint32_t)kb << 30;
-                        tc_mma(d_tmem, desc_sw128(sb + w * Cfg::A_BYTES + kb * 32), desc_sw128(sb + NA * Cfg::A_BYTES + kb * 32),
-                               idesc_mx(n_mma, kb), t_sfa | sfid, t_sfb | sfid, (ks | kb) ? 1u : 0u);
-                    }
-                    tc_commit(empty0 + 8 * s);   // stage reusable once every issuer's MMAs have read it
-                }
-                if (ok) tc_commit(acc_full0 + 8 * buf);
-            }
-        }
-    } else if (warp < 1 + Cfg::ISSUERS + Cfg::EPI_WARPS) {
+    } else {
+        if (Cfg::REBALANCE) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_EPI));
         // -------------------------------------------------------- epilogue
         const int q = warp & 3;                  // TMEM lane quarter this warp may read
-        const int half = (warp - 1 - Cfg::ISSUERS) >> 2;   // which of the quarter's two warps: even or odd 32-column chunks
+        constexpr int SUBS = Cfg::EPI_WARPS / 4; // warps per quarter
+        const int sub = (warp - Cfg::EPI_WARP0) >> 2;
         uint32_t tcount = 0;
         bool ok = true;
+#ifdef Q36_TCPROF
+        long long pf_wait = 0, pf_busy = 0;
+#endif
         for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
             const TcTile t = get_tile(ti);
             const uint32_t buf = tcount & 1;
             const uint32_t tq = tmem + buf * Cfg::ACC_STRIDE + ((uint32_t)(q * 32) << 16);
+#ifdef Q36_TCPROF
+            long long pf_a = clock64();
+#endif
             if (!(ok = mbar_wait(acc_full0 + 8 * buf, (tcount >> 1) & 1, &abort_flag, status, 0x400 + buf, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+#ifdef Q36_TCPROF
+            long long pf_b = clock64();
+            pf_wait += pf_b - pf_a;
+#endif
             tc_fence_after();
             const int mrow = t.mt * TC_M + q * 32 + lane;   // weight row (output feature) of this thread
-            for (int c0 = 32 * half; c0 < t.nrows; c0 += 64) {
-                uint32_t g[32];
-                tc_ld32(tq + c0, g);
-                if (NA == 2) {
-                    uint32_t u[32];
-                    tc_ld32(tq + Cfg::N + c0, u);
+            if (NA == 2) {
+                const int blk = mrow / Q36_QK;               // this warp's 32 rows are one scale block
+                for (int c0 = 16 * sub; c0 < t.nrows; c0 += 16 * SUBS) {   // sixteen token columns per batch
+                    uint32_t g[16], u[16];
+                    tc_ld16(tq + c0, g);
+                    tc_ld16(tq + Cfg::N + c0, u);
                     tc_ld_wait();
-                    const int blk = mrow / Q36_QK;           // this warp's 32 rows are one scale block
+                    float gg[16], uu[16];
 #pragma unroll
-                    for (int j0 = 0; j0 < 32; j0 += 16) {
-                        if (c0 + j0 < t.nrows) {             // warp-uniform; sixteen columns per batch for ILP
-                            float gg[16], uu[16];
-#pragma unroll
-                            for (int c = 0; c < 16; c++) { gg[c] = __uint_as_float(g[j0 + c]); uu[c] = __uint_as_float(u[j0 + c]); }
-                            swiglu_quant_store<16>(gg, uu, t.nrows - c0 - j0, (size_t)(t.row0 + c0 + j0), Hq, Hs, M_total, blk, lane);
-                        }
-                    }
-                } else {
+                    for (int c = 0; c < 16; c++) { gg[c] = __uint_as_float(g[c]); uu[c] = __uint_as_float(u[c]); }
+                    swiglu_quant_store<16>(gg, uu, t.nrows - c0, (size_t)(t.row0 + c0), Hq, Hs, M_total, blk, lane);
+                }
+            } else {
+                for (int c0 = 32 * sub; c0 < t.nrows; c0 += 32 * SUBS) {
+                    uint32_t g[32];
+                    tc_ld32(tq + c0, g);
                     tc_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; j++)
@@ -297,56 +403,14 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+#ifdef Q36_TCPROF
+            pf_busy += clock64() - pf_b;
+#endif
         }
-    } else {
-        // --------------------------------------------------- scale loaders
-        // The scale image of an operand for one K step is 32 lanes x 4 columns in each TMEM lane quarter: lane l,
-        // column j, byte kb = scale of row l + 32 * j for K block kb -- one aligned word of the row's 16 staged
-        // bytes.  Each of the four warps writes the image into its own lane quarter (the four copies the MMA
-        // reads), lane = thread: four rows' words per operand per K step, straight from the staged item.
-        const int q = warp & 3;
-        uint32_t it = 0, item = 0;
-        bool ok = true;
-        for (int ti = blockIdx.x; ti < n_tiles && ok; ti += gridDim.x) {
-            const TcTile t = get_tile(ti);
-            for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
-                const uint32_t sl = item % Cfg::SFR_SLOTS;
-                if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / Cfg::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                const uint8_t *src = sfr + sl * Cfg::SFR_BYTES + lane * 16;
-                uint32_t wa0[4][4], wa1[4][4], wb[4][4];      // [row l + 32 j][K step of the item]
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint4 a0 = *reinterpret_cast<const uint4 *>(src + j * 512);
-                    wa0[j][0] = a0.x; wa0[j][1] = a0.y; wa0[j][2] = a0.z; wa0[j][3] = a0.w;
-                    if (NA == 2) {
-                        const uint4 a1 = *reinterpret_cast<const uint4 *>(src + Cfg::SFR_PART + j * 512);
-                        wa1[j][0] = a1.x; wa1[j][1] = a1.y; wa1[j][2] = a1.z; wa1[j][3] = a1.w;
-                    }
-                    uint4 b = *reinterpret_cast<const uint4 *>(src + NA * Cfg::SFR_PART + j * 512);
-                    if (lane + 32 * j >= t.nrows) b = make_uint4(0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
-                    wb[j][0] = b.x; wb[j][1] = b.y; wb[j][2] = b.z; wb[j][3] = b.w;
-                }
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    const int s = it % Cfg::STAGES;
-                    const uint32_t ph = (it / Cfg::STAGES) & 1;
-                    if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
-                    tc_fence_after();
-                    const uint32_t tq = tmem + Cfg::sf_col(s) + ((uint32_t)(q * 32) << 16);
-                    tc_st4(tq, wa0[0][x], wa0[1][x], wa0[2][x], wa0[3][x]);
-                    if (NA == 2) tc_st4(tq + 4, wa1[0][x], wa1[1][x], wa1[2][x], wa1[3][x]);
-                    tc_st4(tq + 4 * NA, wb[0][x], wb[1][x], wb[2][x], wb[3][x]);
-                    tc_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(full0 + 8 * s);
-                    it++;
-                }
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
-            }
-        }
+#ifdef Q36_TCPROF
+        if (NA == 2 && lane == 0 && (warp == Cfg::EPI_WARP0 || warp == Cfg::EPI_WARP0 + 13) && (blockIdx.x == 0 || blockIdx.x == 77))
+            printf("epilogue cta %d warp %d: tiles %u wait %lld busy %lld\n", blockIdx.x, warp, tcount, pf_wait, pf_busy);
+#endif
     }
 
     // ------------------------------------------------------------ teardown
@@ -357,7 +421,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
         for (int i = 0; i < 200; i++) __nanosleep(1000);
         if (threadIdx.x == 0) atomicCAS(status, 0, 1);
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS) : "memory");
     }
@@ -797,6 +861,20 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     if ((rc = make_map_scales(&maps.fb, Bs, R_max, nb, 0, 0, Cfg::N))) return rc;
     static bool attr_done[MAX_DEVICES] = {false};   // one array per instantiation
     if ((rc = ensure_smem_attr((const void *)k_grouped_mma<NA>, Cfg::SMEM_BYTES, attr_done))) return rc;
+    if (Cfg::REBALANCE) {
+        // the epilogue warps' setmaxnreg.inc waits for registers the first eight warps give back: never launch a build
+        // whose register pool (registers per thread at launch x threads) cannot cover both groups' new sizes
+        static int regs[MAX_DEVICES] = {0};
+        const int dv = current_device();
+        if (dv < 0) return Q36_MOE_ECUDA;
+        int &nr = regs[dv];
+        if (!nr) {
+            cudaFuncAttributes fa;
+            if (cudaFuncGetAttributes(&fa, (const void *)k_grouped_mma<NA>) != cudaSuccess) return Q36_MOE_ECUDA;
+            nr = fa.numRegs;
+        }
+        if ((nr + 7) / 8 * 8 * Cfg::THREADS < 32 * (Cfg::EPI_WARP0 * Cfg::REGS_LOW + Cfg::EPI_WARPS * Cfg::REGS_EPI)) return Q36_MOE_EUNSUPPORTED;
+    }
     const int m_tiles = M / TC_M;
     const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
     const int grid = (int)min((long)sm_count(), max_tiles);

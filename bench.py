@@ -523,7 +523,7 @@ def roofline_decode(moe, layers, dX, dL, T, path, hbm_peak, peak_kind, dev):
     import torch
     NL = len(layers)
     use = moe.PATH_GEMV if path == moe.PATH_GEMV else moe.PATH_TC
-    fused = use == moe.PATH_TC and bool(moe.lib.q36_moe_one_launch_fits(T * (K8 + 1), E, D, FF)) and T * (K8 + 1) <= 6300
+    fused = use == moe.PATH_TC and bool(moe.lib.q36_moe_one_launch_fits(T * (K8 + 1), E, D, FF)) and T * (K8 + 1) <= moe.lib.q36_moe_one_launch_rows()
     n, R = T * K8, T * (K8 + 1)
     soffs = torch.tensor([n, n + T], dtype=torch.int32, device=dev)
     touched, staged = [], []

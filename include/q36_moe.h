@@ -196,6 +196,9 @@ uint64_t q36_moe_ffn_ws_bytes(int n_group, int R_max, int D, int FF);
  * grouped-GEMM launches run): it needs D, FF <= 2048 and multiples of 512, and
  * a per-block tile table that holds the call. */
 int q36_moe_one_launch_fits(int R_max, int n_group, int D, int FF);
+/* The row count (sorted rows incl. the shared expert's) up to which the
+ * whole-layer entries prefer that kernel when it fits: measured, 4096. */
+int q36_moe_one_launch_rows(void);
 /* Sg/Su/Sd (or NULL): one extra group, the shared expert, with its own planes
  * and the row range [soffs[0], soffs[1]) (device ints).  stages: bit 0 runs
  * gate/up + SwiGLU, bit 1 runs down; 3 = both (the intermediate Hq/Hs is the
@@ -205,7 +208,7 @@ int q36_moe_one_launch_fits(int R_max, int n_group, int D, int FF);
  * max_group_rows: an upper bound on the rows of any single group when the
  * caller knows one (decode: the number of tokens), else 0.  With the
  * tensor-core path, stages == 3 and a bound given, gate/up and down run as
- * ONE persistent launch (token tiles of 16 rows) up to 6300 rows in all,
+ * ONE persistent launch (token tiles of 16 rows) up to 4096 rows in all,
  * where the two launches with their 112/128-row token tiles take over. */
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group,
                               const int *goffs, const void *Sg, const void *Su, const void *Sd,

@@ -75,7 +75,7 @@ static LayerWs carve(void *base, int T, int E, int k, int D, int FF) {
 // against 198: the lines cross near 800 tokens (9 rows per token); the environment variable is there for experiments.
 int fused_rows_limit() {
     static int v = -1;
-    if (v < 0) { const char *e = getenv("Q36_FUSE_ROWS"); v = e ? atoi(e) : 6300; }
+    if (v < 0) { const char *e = getenv("Q36_FUSE_ROWS"); v = e ? atoi(e) : 4096; }
     return v;
 }
 
@@ -264,6 +264,8 @@ int q36_moe_one_launch_fits(int R_max, int n_group, int D, int FF) {
     if (R_max <= 0 || n_group <= 0 || D <= 0 || FF <= 0) return 0;
     return ffn_fused_small_fits(R_max, n_group, D, FF) ? 1 : 0;
 }
+
+int q36_moe_one_launch_rows(void) { return fused_rows_limit(); }
 
 int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, int n_group, const int *goffs,
                               const void *Sg, const void *Su, const void *Sd, const int *soffs, int R_max,

@@ -158,10 +158,10 @@ class NativeEP:
         self.moe, self.layers, self.world, self.rank, self.T = moe, layers, world, rank, T
         ly = layers[0]
         # kernels per layer step: front (cluster at decode sizes, else router + dispatch x3 + quantise), send, the
-        # received slots' plan, unpack, FFN (one launch up to 6300 rows, else plan + two), return, combine
+        # received slots' plan, unpack, FFN (one launch up to q36_moe_one_launch_rows() rows, else two), return, combine
         small_front = T <= 16 and T * ly.k <= 128
         S = world * (cap_rows or T * ly.k)
-        one_launch = S + T <= 6300
+        one_launch = S + T <= moe.lib.q36_moe_one_launch_rows()
         self.launches_per_layer = (1 if small_front else (2 if T * ly.k <= 1024 else 6)) + 1 + (1 if S <= 1024 else 5) + 1 + \
             (1 if one_launch else 2) + 1 + 1
         dev = ly.device

@@ -58,6 +58,7 @@ _SIGS = {
     "q36_moe_quant_scatter": (i32, [vp, i32, vp, i32, i32, vp, vp, i32, i32, vp]),
     "q36_moe_ffn_ws_bytes": (u64, [i32, i32, i32, i32]),
     "q36_moe_one_launch_fits": (i32, [i32, i32, i32, i32]),
+    "q36_moe_one_launch_rows": (i32, []),
     "q36_moe_expert_ffn_sorted": (i32, [vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32,
                                         i32, i32, vp, u64, vp]),
     "q36_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),

@@ -113,6 +113,7 @@ int ensure_smem_attr(const void *kernel, int bytes, bool *done);
 // moe_tc_fused.cu: gate/up and down of decode-sized groups (every group <= 16 rows) in ONE persistent launch
 bool ffn_fused_small_fits(int R_max, int n_group, int D, int FF);   // does launch_ffn_fused_small take this call?
 int ffn_fused_small_grid(int R_max, int n_group, int D, int FF);   // CTAs of that launch
+int gateup_tile_rows();           // token rows per tile a two-launch call's plan must be cut in (0: defaults)
 int fused_rows_limit();            // policy: rows up to which that kernel is preferred when groups may exceed 16 rows   // largest R_max launch_ffn_fused_small accepts
 int launch_ffn_fused_small(const void *Wg, const void *Wu, const void *Wd, const void *Sg, const void *Su,
                            const void *Sd, int n_group, int R_max, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq,

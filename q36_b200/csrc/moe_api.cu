@@ -125,12 +125,12 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_front_small(logits, E, k, route_scale, T, logit_stride, se0, se1, w.idx, w.wt, w.ecount, w.eoffs,
                                      w.elist, w.pos, w.soffs, n, shared ? n + T : n, use_tc ? w.plan : nullptr, D, FF,
                                      w.status, fused_quant ? X : nullptr, x_is_bf16, w.Xq, w.Xs, shared ? n : -1,
-                                     decode_kernel ? 16 : 0, st)))
+                                     decode_kernel ? 16 : gateup_tile_rows(), st)))
             return rc;
     } else {
         if ((rc = launch_router_topk(logits, E, k, w.idx, w.wt, route_scale, 1, T, logit_stride, st))) return rc;
         if ((rc = launch_dispatch(w.idx, n, E, se0, se1, w.ecount, w.eoffs, w.elist, w.pos, w.disp, w.soffs, n,
-                                  shared ? n + T : n, st, use_tc ? w.plan : nullptr, D, FF, decode_kernel ? 16 : 0)))   // (+ the work plan)
+                                  shared ? n + T : n, st, use_tc ? w.plan : nullptr, D, FF, decode_kernel ? 16 : gateup_tile_rows())))   // (+ the work plan)
             return rc;
     }
     if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
@@ -293,7 +293,7 @@ int q36_moe_expert_ffn_sorted(const void *Wg, const void *Wu, const void *Wd, in
     void *plan = p + 256;
     const bool one_launch = stages == 3 && max_group_rows > 0 && ffn_fused_small_fits(R_max, n_group, D, FF) &&
                             (max_group_rows <= 16 || R_max <= fused_rows_limit());
-    if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : 0, st))) return rc;
+    if ((rc = launch_tc_plan(goffs, n_group, shared ? soffs : nullptr, D, FF, plan, status, one_launch ? 16 : gateup_tile_rows(), st))) return rc;
     if (one_launch)
         return launch_ffn_fused_small(Wg, Wu, Wd, shared ? Sg : nullptr, shared ? Su : nullptr, shared ? Sd : nullptr, n_group,
                                       R_max, Xq_rows, Xs_rows, Hq_rows, Hs_rows, Y_rows, D, FF, plan, status, nullptr, st);

@@ -616,13 +616,13 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         if (small_plan) {
             if ((rc = launch_ep_recv_plan(c->win, L.hdr[0], L.hdr[1], L.rows[0], L.rows[1], ctl, world, C, rowb, D + nbs, c->spin_limit,
                                           w.status, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.soffs, R, shared ? R + T : R,
-                                          w.plan, D, FF, one_launch ? 16 : 0, w.counts, st)))
+                                          w.plan, D, FF, one_launch ? 16 : gateup_tile_rows(), w.counts, st)))
                 return rc;
         } else {
             launch_k(k_ep_wait_eids, dim3((S + 255) / 256), dim3(256), 0, st, (const uint8_t *)c->win, L.hdr[0], L.hdr[1], L.rows[0],
                      L.rows[1], (const int *)ctl, world, C, rowb, D + nbs, c->spin_limit, w.status, w.reid, w.counts);
             if ((rc = launch_dispatch(w.reid, S, E, se0, se1, w.lcount, w.loffs, w.llist, w.lpos, w.ldisp, w.soffs, R, shared ? R + T : R, st,
-                                      w.plan, D, FF, one_launch ? 16 : 0)))   // (+ the work plan)
+                                      w.plan, D, FF, one_launch ? 16 : gateup_tile_rows())))   // (+ the work plan)
                 return rc;
         }
         launch_k(k_ep_unpack, dim3(min(R + T, 8 * sm_count())), dim3(128), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,

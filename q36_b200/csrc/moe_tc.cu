@@ -427,6 +427,354 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
     }
 }
 
+// ------------------------------------------- gate/up, tokens as the 128-row operand
+// k_grouped_mma<2> keeps weights as the 128-row operand and tokens as N <= 112: eight MMAs per K step from two
+// threads, each of which gets one through per ~160 cycles among the epilogue warps of its scheduler (measured: the
+// issuing threads, not the tensor pipe, set the pace).  Here a tile is 128 TOKEN rows (the M operand, E4M3) against
+// the 128 gate rows + 128 up rows of one ff tile as ONE N = 256 operand (E2M1): four MMAs per K step from one
+// thread, each 128 cycles of tensor pipe, so one thread issues at the pipe's rate.  An accumulator lane is a
+// token and its columns are ff rows: the 32 values of a token's scale block sit in ONE thread of the epilogue (no
+// cross-lane maximum, one exponent per thread, two 16-byte stores).  The 256 accumulator columns exist once; the
+// epilogue warps release them as soon as they hold the values in registers, so their arithmetic overlaps the next
+// tile's MMAs.
+struct GuWide {
+    static constexpr int N = 128;                       // token rows per tile (UMMA M)
+    static constexpr int STAGES = 4;
+    static constexpr int A_BYTES = N * 128;             // token rows of one K step
+    static constexpr int B_HALF = TC_M * 128;           // gate (or up) rows of one K step, padded 4-bit form
+    static constexpr int B_TX = TC_M * 64;              // ... and what its copy signals (packed bytes)
+    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_HALF;              // 48 KB
+    static constexpr int SFR_SLOTS = 4, SFR_PART = 128 * 16, SFR_BYTES = 3 * SFR_PART;   // tokens | gate | up, four K steps each
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SFR_SLOTS * SFR_BYTES + 1024 + 512;
+    static constexpr int ACC_COLS = 256, SF_COLS = 12, TMEM_COLS = 512;   // scale columns of stage s: tokens 4 | gate 4 | up 4
+    __host__ __device__ static constexpr int sf_col(int s) { return ACC_COLS + SF_COLS * s; }
+    static constexpr int B_FULL_MIN = 49;               // token tiles of at least this many rows use one 128-row box
+    static constexpr int EPI_WARP0 = 8, EPI_WARPS = 16, THREADS = 32 * (EPI_WARP0 + EPI_WARPS);
+    static constexpr int REGS_LOW = 32, REGS_EPI = 104;
+};
+
+// instruction descriptor of that MMA: A = E4M3 (0), B = E2M1 (5), both K-major, UE8M0 scales, M = 128, N = 256
+__device__ __forceinline__ uint32_t idesc_mx_wide(int kb) {
+    return ((uint32_t)kb << 4) | (0u << 7) | (5u << 10) | ((uint32_t)(256 >> 3) << 17) | (1u << 23) |
+           ((uint32_t)(128 >> 4) << 24) | ((uint32_t)kb << 29);
+}
+
+__global__ void __launch_bounds__(GuWide::THREADS, 1)
+k_gateup_wide(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *__restrict__ plan, uint8_t *__restrict__ Hq,
+              uint8_t *__restrict__ Hs, int FF, int K, int *__restrict__ status) {
+    using C = GuWide;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sfr = smem + C::STAGES * C::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sfr + C::SFR_SLOTS * C::SFR_BYTES);
+    // bars: full[STAGES], empty[STAGES], acc_full, acc_empty, sfr_full[SLOTS], sfr_empty[SLOTS]
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_flag;
+    __shared__ int s_row0[DISPATCH_MAX_GROUPS + 1], s_cnt[DISPATCH_MAX_GROUPS + 1], s_base[DISPATCH_MAX_GROUPS + 2];
+    __shared__ unsigned short s_order[DISPATCH_MAX_GROUPS + 1];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
+    const uint32_t acc_full = smem_u32(bars + 2 * C::STAGES), acc_empty = acc_full + 8;
+    const uint32_t sfr_full0 = acc_empty + 8, sfr_empty0 = sfr_full0 + 8 * C::SFR_SLOTS;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full0 + 8 * s, 2 + 4);      // each producer's expect_tx arrive + one arrive per scale warp
+            mbar_init(empty0 + 8 * s, 1);         // the issuer's tcgen05.commit
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, C::EPI_WARPS);
+        for (int b = 0; b < C::SFR_SLOTS; b++) {
+            mbar_init(sfr_full0 + 8 * b, 1);
+            mbar_init(sfr_empty0 + 8 * b, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    Q36_GDS();   // from here on: global memory written by earlier kernels
+
+    const int n_tiles = plan->n_tiles[0];
+    const int G = plan->n_groups;
+    const int k_steps = K / TC_KSTEP;
+    const int m_tiles = FF / TC_M;
+    const bool plan_ok = plan->tile_rows == C::N;      // the plan must have been cut in 128-row token tiles
+    for (int i = threadIdx.x; i <= G; i += blockDim.x) {
+        s_base[i] = plan->base[0][i];
+        if (i < G) { s_order[i] = (unsigned short)plan->order[i]; s_row0[i] = plan->row0[i]; s_cnt[i] = plan->cnt[i]; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base_s;
+    if (!plan_ok && threadIdx.x == 0) atomicCAS(status, 0, 0xE00);
+    const int my_first = plan_ok ? (int)blockIdx.x : n_tiles;
+
+    auto get_tile = [&](int ti) {
+        int lo = 0, hi = G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (s_base[mid] <= ti) lo = mid; else hi = mid - 1;
+        }
+        const int g = s_order[lo], local = ti - s_base[lo];
+        const int nt = local / m_tiles, mt = local - nt * m_tiles;
+        return TcTile{g, mt, s_row0[g] + nt * C::N, min(C::N, s_cnt[g] - nt * C::N)};
+    };
+
+    if (warp < C::EPI_WARP0) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_LOW));
+        if (warp == 0) {
+            // ---------------------------------------- TMA producer: weights (gate rows, then up rows of the ff tile)
+            // One thread needs ~360 cycles per copy (wait, expect_tx, issue) whatever its size: two copies per K step from
+            // one thread are slower than the step's MMAs (512 cycles).  Lanes 0 and 1 issue the gate and the up copy in
+            // the same instruction.
+            if (lane < 2) {
+                uint32_t it = 0;
+                bool ok = true;
+#ifdef Q36_TCPROF
+                long long pf_w = 0, pf_x, pf_t0 = clock64();
+#endif
+                for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x) {
+                    const TcTile t = get_tile(ti);
+                    const bool sh = t.g >= n_routed;
+                    const CUtensorMap *mm = sh ? (lane ? &maps.s1 : &maps.s0) : (lane ? &maps.a1 : &maps.a0);
+                    const int ge = sh ? 0 : t.g;
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        const int s = it % C::STAGES;
+#ifdef Q36_TCPROF
+                        pf_x = clock64();
+#endif
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+#ifdef Q36_TCPROF
+                        pf_w += clock64() - pf_x;
+#endif
+                        const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES) + C::A_BYTES + lane * C::B_HALF;
+                        if (lane == 0) mbar_expect_tx(full0 + 8 * s, 2 * C::B_TX);
+                        __syncwarp(3u);                      // the expected bytes are registered before either copy can complete
+                        tma_load_3d(sb, mm, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                    }
+                }
+#ifdef Q36_TCPROF
+                if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == 77)) printf("wide prodA cta %d: total %lld wait_empty %lld\n", blockIdx.x, clock64() - pf_t0, pf_w);
+#endif
+            }
+        } else if (warp == 1) {
+            // ---------------------------------------- TMA producer: token rows
+            if (lane == 0) {
+                uint32_t it = 0;
+                bool ok = true;
+                for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x) {
+                    const TcTile t = get_tile(ti);
+                    const bool full_box = t.nrows >= C::B_FULL_MIN;
+                    const int slabs = (t.nrows + 15) / 16;
+                    const uint32_t tx = full_box ? C::A_BYTES : slabs * 2048;
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        const int s = it % C::STAGES;
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x900 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES);
+                        mbar_expect_tx(full0 + 8 * s, tx);
+                        if (full_box) {
+                            tma_load_2d(sb, &maps.bfull, ks * TC_KSTEP, t.row0, full0 + 8 * s);
+                        } else {
+                            for (int i = 0; i < slabs; i++) tma_load_2d(sb + i * 2048, &maps.b16, ks * TC_KSTEP, t.row0 + 16 * i, full0 + 8 * s);
+                        }
+                    }
+                }
+            }
+        } else if (warp == 3) {
+            // ---------------------------------------- TMA producer: scale items (four K steps each), as far ahead as
+            // their ring allows -- issued with the stage copies they arrived one latency late every fourth K step
+            if (lane == 0) {
+                uint32_t item = 0;
+                bool ok = true;
+                for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x) {
+                    const TcTile t = get_tile(ti);
+                    const bool sh = t.g >= n_routed;
+                    const CUtensorMap *fg = sh ? &maps.fs0 : &maps.fa0, *fu = sh ? &maps.fs1 : &maps.fa1;
+                    const int ge = sh ? 0 : t.g;
+                    for (int ks = 0; ks < k_steps; ks += 4, item++) {
+                        const uint32_t sl = item % C::SFR_SLOTS;
+                        if (!(ok = mbar_wait(sfr_empty0 + 8 * sl, ((item / C::SFR_SLOTS) & 1) ^ 1, &abort_flag, status, 0x800 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+                        const uint32_t dst = smem_u32(sfr + sl * C::SFR_BYTES);
+                        mbar_expect_tx(sfr_full0 + 8 * sl, 3 * C::SFR_PART);
+                        tma_load_2d(dst, &maps.fb, 4 * ks, t.row0, sfr_full0 + 8 * sl);
+                        tma_load_3d(dst + C::SFR_PART, fg, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                        tma_load_3d(dst + 2 * C::SFR_PART, fu, 4 * ks, t.mt * TC_M, ge, sfr_full0 + 8 * sl);
+                    }
+                }
+            }
+        } else if (warp == 2) {
+            // ---------------------------------------- the MMA issuer
+            if (lane == 0) {
+                uint32_t it = 0, tcount = 0;
+                bool ok = true;
+#ifdef Q36_TCPROF
+                long long pf_full = 0, pf_acc = 0, pf_t0 = clock64(), pf_x;
+#endif
+                for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
+                    // the accumulator must have been read out by every epilogue warp
+#ifdef Q36_TCPROF
+                    pf_x = clock64();
+#endif
+                    if (!(ok = mbar_wait(acc_empty, (tcount & 1) ^ 1, &abort_flag, status, 0x200))) break;
+#ifdef Q36_TCPROF
+                    pf_acc += clock64() - pf_x;
+#endif
+                    tc_fence_after();
+                    for (int ks = 0; ks < k_steps; ks++, it++) {
+                        const int s = it % C::STAGES;
+#ifdef Q36_TCPROF
+                        pf_x = clock64();
+#endif
+                        if (!(ok = mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, &abort_flag, status, 0x300 + s))) break;
+#ifdef Q36_TCPROF
+                        pf_full += clock64() - pf_x;
+#endif
+                        tc_fence_after();
+                        const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES);
+                        const uint32_t t_sfa = tmem + C::sf_col(s), t_sfb = t_sfa + 4;
+#pragma unroll
+                        for (int kb = 0; kb < 4; kb++) {
+                            const uint32_t sfid = (uint32_t)kb << 30;
+                            tc_mma(tmem, desc_sw128(sb + kb * 32), desc_sw128(sb + C::A_BYTES + kb * 32), idesc_mx_wide(kb),
+                                   t_sfa | sfid, t_sfb | sfid, (ks | kb) ? 1u : 0u);
+                        }
+                        tc_commit(empty0 + 8 * s);
+                    }
+                    if (ok) tc_commit(acc_full);
+                }
+#ifdef Q36_TCPROF
+                if (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147)
+                    printf("wide issuer cta %d: tiles %u total %lld wait_full %lld wait_acc %lld\n", blockIdx.x, tcount, clock64() - pf_t0, pf_full, pf_acc);
+#endif
+            }
+        } else if (warp >= 4) {
+            // ---------------------------------------- scale loaders: lane l writes the words of rows l + 32 j
+            const int q = warp & 3;
+            uint32_t it = 0, item = 0;
+            bool ok = true;
+#ifdef Q36_TCPROF
+            long long pf_w = 0, pf_i = 0, pf_x, pf_t0 = clock64();
+#endif
+            for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x) {
+                for (int kg = 0; kg < k_steps / 4 && ok; kg++, item++) {
+                    const uint32_t sl = item % C::SFR_SLOTS;
+#ifdef Q36_TCPROF
+                    pf_x = clock64();
+#endif
+                    if (!(ok = mbar_wait(sfr_full0 + 8 * sl, (item / C::SFR_SLOTS) & 1, &abort_flag, status, 0x700 + sl, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+#ifdef Q36_TCPROF
+                    pf_i += clock64() - pf_x;
+#endif
+                    const uint8_t *src = sfr + sl * C::SFR_BYTES + lane * 16;
+#pragma unroll
+                    for (int x = 0; x < 4; x++) {
+                        uint32_t wt[4], wg[4], wu[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            wt[j] = *reinterpret_cast<const uint32_t *>(src + j * 512 + 4 * x);
+                            wg[j] = *reinterpret_cast<const uint32_t *>(src + C::SFR_PART + j * 512 + 4 * x);
+                            wu[j] = *reinterpret_cast<const uint32_t *>(src + 2 * C::SFR_PART + j * 512 + 4 * x);
+                        }
+                        const int s = it % C::STAGES;
+#ifdef Q36_TCPROF
+                        pf_x = clock64();
+#endif
+                        if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x500 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+#ifdef Q36_TCPROF
+                        pf_w += clock64() - pf_x;
+#endif
+                        tc_fence_after();
+                        const uint32_t tq = tmem + C::sf_col(s) + ((uint32_t)(q * 32) << 16);
+                        tc_st4(tq, wt[0], wt[1], wt[2], wt[3]);
+                        tc_st4(tq + 4, wg[0], wg[1], wg[2], wg[3]);
+                        tc_st4(tq + 8, wu[0], wu[1], wu[2], wu[3]);
+                        tc_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(full0 + 8 * s);
+                        it++;
+                    }
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(sfr_empty0 + 8 * sl);
+                }
+            }
+#ifdef Q36_TCPROF
+            if (lane == 0 && warp == 4 && (blockIdx.x == 0 || blockIdx.x == 77))
+                printf("wide loader cta %d: total %lld wait_empty %lld wait_item %lld\n", blockIdx.x, clock64() - pf_t0, pf_w, pf_i);
+#endif
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REGS_EPI));
+        // -------------------------------------------- epilogue: warp (q, sub) = tokens 32 q .. + 31, scale block `sub` of the ff tile
+        const int q = warp & 3, sub = (warp - C::EPI_WARP0) >> 2;
+        const int nbh = FF / Q36_QK;
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x, tcount++) {
+            const TcTile t = get_tile(ti);
+            if (!(ok = mbar_wait(acc_full, tcount & 1, &abort_flag, status, 0x400, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+            tc_fence_after();
+            const bool mine = q * 32 < t.nrows;          // warp-uniform: this lane quarter holds rows of the tile
+            uint32_t g[32], u[32];
+            if (mine) {
+                const uint32_t tq = tmem + ((uint32_t)(q * 32) << 16);
+                tc_ld32(tq + 32 * sub, g);
+                tc_ld32(tq + 128 + 32 * sub, u);
+                tc_ld_wait();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);       // the next tile's MMAs may overwrite the columns now
+            if (mine) {
+                float h[32];
+                float amax = 0.f;
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    const float gv = __uint_as_float(g[c]);
+                    h[c] = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[c]);
+                    amax = fmaxf(amax, fabsf(h[c]));
+                }
+                const int e2 = e2_of_amax(amax);
+                const float inv = inv_scale_of_e2(e2);
+                uint32_t w[8];                            // hw order: byte 2 j <- element j, byte 2 j + 1 <- element j + 16
+#pragma unroll
+                for (int x = 0; x < 8; x++) {
+                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h[2 * x] * inv, h[2 * x + 16] * inv), __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h[2 * x + 1] * inv, h[2 * x + 17] * inv), __NV_SATFINITE, __NV_E4M3);
+                    w[x] = lo | (hi << 16);
+                }
+                const int row = q * 32 + lane;
+                if (row < t.nrows) {
+                    const size_t r = (size_t)(t.row0 + row);
+                    const int blk = t.mt * (TC_M / Q36_QK) + sub;
+                    uint4 *dst = reinterpret_cast<uint4 *>(Hq + r * FF + (size_t)blk * Q36_QK);
+                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    Hs[r * nbh + blk] = (uint8_t)(127 + e2);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        for (int i = 0; i < 200; i++) __nanosleep(1000);   // copies that may still be in flight
+        if (threadIdx.x == 0) atomicCAS(status, 0, 1);
+    }
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
 // ----------------------------------------------- down projection, token tile resident
 // The down projection of prefill-sized groups has K = FF = 512: a token tile's whole B operand (128 rows x 512 B
 // = 64 KB) fits in shared memory.  k_grouped_mma<1> re-fetches it for every one of the D / 128 weight-row tiles
@@ -883,10 +1231,60 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     return check_launch();
 }
 
+// Token rows per tile the work plan of a two-launch call must be cut in (0: the 112 / 128 defaults): 128 when the
+// gate/up launch is k_gateup_wide.  Q36_GATEUP_NARROW in the environment keeps k_grouped_mma<2>.
+int gateup_tile_rows() {
+    static const bool narrow = getenv("Q36_GATEUP_NARROW") != nullptr;
+    return narrow ? 0 : GuWide::N;
+}
+
+static int run_gateup_wide(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max, const uint8_t *Xq,
+                           const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int FF, int K, const void *plan, int *status, cudaStream_t st) {
+    using C = GuWide;
+    if (FF % TC_M || K % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
+    const uint64_t estride = (uint64_t)FF * (K / 2) + (uint64_t)FF * (K / Q36_QK), plane = (uint64_t)FF * (K / 2);
+    const int nb = K / Q36_QK;
+    if (!Sg) { Sg = Wg; Su = Wu; }
+    TcMaps maps;
+    int rc;
+    if ((rc = make_map_codes(&maps.a0, Wg, FF, K, n_group, estride))) return rc;
+    if ((rc = make_map_codes(&maps.a1, Wu, FF, K, n_group, estride))) return rc;
+    if ((rc = make_map_codes(&maps.s0, Sg, FF, K, 1, estride))) return rc;
+    if ((rc = make_map_codes(&maps.s1, Su, FF, K, 1, estride))) return rc;
+    if ((rc = make_map_rows(&maps.b16, Xq, R_max, K, 16))) return rc;
+    if ((rc = make_map_rows(&maps.bfull, Xq, R_max, K, C::N))) return rc;
+    if ((rc = make_map_scales(&maps.fa0, (const uint8_t *)Wg + plane, FF, nb, n_group, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fa1, (const uint8_t *)Wu + plane, FF, nb, n_group, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fs0, (const uint8_t *)Sg + plane, FF, nb, 1, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fs1, (const uint8_t *)Su + plane, FF, nb, 1, estride, TC_M))) return rc;
+    if ((rc = make_map_scales(&maps.fb, Xs, R_max, nb, 0, 0, C::N))) return rc;
+    static bool attr_done[MAX_DEVICES] = {false};
+    if ((rc = ensure_smem_attr((const void *)k_gateup_wide, C::SMEM_BYTES, attr_done))) return rc;
+    {   // as for k_grouped_mma<2>: the register pool must cover both warp groups' sizes after setmaxnreg
+        static int regs[MAX_DEVICES] = {0};
+        const int dv = current_device();
+        if (dv < 0) return Q36_MOE_ECUDA;
+        int &nr = regs[dv];
+        if (!nr) {
+            cudaFuncAttributes fa;
+            if (cudaFuncGetAttributes(&fa, (const void *)k_gateup_wide) != cudaSuccess) return Q36_MOE_ECUDA;
+            nr = fa.numRegs;
+        }
+        if ((nr + 7) / 8 * 8 * C::THREADS < 32 * (C::EPI_WARP0 * C::REGS_LOW + C::EPI_WARPS * C::REGS_EPI)) return Q36_MOE_EUNSUPPORTED;
+    }
+    const int m_tiles = FF / TC_M;
+    const long max_tiles = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * m_tiles;
+    const int grid = (int)min((long)sm_count(), max_tiles);
+    launch_k(k_gateup_wide, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Hq, Hs, FF, K, status);
+    return check_launch();
+}
+
 int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void *Su, int n_group, int R_max,
                      int max_group_rows, const uint8_t *Xq, const uint8_t *Xs, uint8_t *Hq, uint8_t *Hs, int D, int FF,
                      const void *plan, int *status, cudaStream_t st) {
     (void)max_group_rows;
+    if (gateup_tile_rows() == GuWide::N)
+        return run_gateup_wide(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, FF, D, plan, status, st);
     return run_grouped<2>(Wg, Wu, Sg, Su, n_group, R_max, Xq, Xs, Hq, Hs, nullptr, FF, D, plan, status, st);
 }
 // K = 512 and D a multiple of DR_MC row tiles: the token-tile-resident kernel

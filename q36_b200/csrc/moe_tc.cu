@@ -801,18 +801,19 @@ struct DownRes {
     static constexpr int OFF_B = STAGES * STAGE_BYTES, OFF_BIMG = OFF_B + B_BYTES, OFF_SFR = OFF_BIMG + BIMG_BYTES,
                          OFF_BS = OFF_SFR + SFR_SLOTS * SFR_BYTES, OFF_BARS = OFF_BS + BS_BYTES;
     static constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;
-    static constexpr int W_PROD_A = 0, W_PROD_B = 1, W_ISSUE0 = 2, W_EPI0 = 4, EPI_WARPS = 8, W_LOAD0 = W_EPI0 + EPI_WARPS;
+    static constexpr int W_PROD_A = 0, W_PROD_B = 1, W_ISSUE0 = 2, W_EPI0 = 4, EPI_WARPS = 16, W_LOAD0 = W_EPI0 + EPI_WARPS;
     static constexpr int THREADS = 32 * (W_LOAD0 + 4);
     static constexpr int ACC_BUFS = 3, ACC_STRIDE = 128, SF_COL0 = ACC_BUFS * ACC_STRIDE, TMEM_COLS = 512;
 };
 static_assert(DownRes::STAGE_BYTES % 1024 == 0 && DownRes::OFF_B % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-constexpr int DR_MC = 8;   // weight-row tiles per work item
+constexpr int DR_MC_MIN = 8;   // weight-row tiles per work item: 16 when the row tiles of a token tile divide by it (the token rows are
+                            // then fetched once per token tile), else 8
 
 struct DownMaps { CUtensorMap a, s, b, fa, fs, fb; };   // routed / shared code planes (2 K steps per box), token rows, scale planes
 
 __global__ void __launch_bounds__(DownRes::THREADS, 1)
 k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPlan *__restrict__ plan, float *__restrict__ Y,
-                int M_total, int *__restrict__ status) {
+                int M_total, int *__restrict__ status, int DR_MC) {
     using C = DownRes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -915,6 +916,9 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
             const uint32_t t_sfa = tmem + C::SF_COL0 + 8 * w, t_sfb = t_sfa + 4;
             uint32_t n = 0;
             bool ok = true;
+#ifdef Q36_TCPROF
+            long long pf_full = 0, pf_acc = 0, pf_b = 0, pf_x, pf_t0 = clock64();
+#endif
             for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
                 const TcTile t = get_item(ii);
                 const int n_mma = max(16, (t.nrows + 15) & ~15);
@@ -926,19 +930,40 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
                     // the slower side (64 KB of f32 rows to store per row tile)
                     const uint32_t buf = q % C::ACC_BUFS, use = q / C::ACC_BUFS;
                     const uint32_t d_tmem = tmem + buf * C::ACC_STRIDE;
+#ifdef Q36_TCPROF
+                    pf_x = clock64();
+#endif
                     if (!(ok = mbar_wait(acc_empty0 + 8 * buf, (use & 1) ^ 1, &abort_flag, status, 0x200 + buf))) break;
+#ifdef Q36_TCPROF
+                    pf_acc += clock64() - pf_x; pf_x = clock64();
+#endif
                     if (first) {                                   // the item's token scale images
                         if (!(ok = mbar_wait(bimg_full, n & 1, &abort_flag, status, 0x210))) break;
                     }
+#ifdef Q36_TCPROF
+                    pf_b += clock64() - pf_x;
+#endif
                     tc_fence_after();
                     for (int h = 0; h < C::KSTEPS / C::KS && ok; h++) {
                         const uint32_t it = q * (C::KSTEPS / C::KS) + h, s = it % C::STAGES;
+#ifdef Q36_TCPROF
+                        pf_x = clock64();
+#endif
                         if (!(ok = mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, &abort_flag, status, 0x300 + s))) break;
+#ifdef Q36_TCPROF
+                        pf_full += clock64() - pf_x;
+#endif
                         const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES);
 #pragma unroll
                         for (int x = 0; x < C::KS; x++) {
                             const int ks = h * C::KS + x;
+#ifdef Q36_TCPROF
+                            pf_x = clock64();
+#endif
                             if (first && !(ok = mbar_wait(bq_full0 + 8 * ks, n & 1, &abort_flag, status, 0x220 + ks))) break;
+#ifdef Q36_TCPROF
+                            pf_b += clock64() - pf_x;
+#endif
                             tc_fence_after();
                             tc_cp_sf(t_sfa, desc_sf(sb + C::KS * C::A_BYTES + x * C::SF_BYTES));
                             tc_cp_sf(t_sfb, desc_sf(smem_u32(smem + C::OFF_BIMG + ks * C::SF_BYTES)));
@@ -959,22 +984,35 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
                 }
                 if (ok) tc_commit(b_empty);     // (arrives when all of this warp's MMAs on the item have read the token rows)
             }
+#ifdef Q36_TCPROF
+            if (w == 0 && (blockIdx.x == 0 || blockIdx.x == 77 || blockIdx.x == 147))
+                printf("down issuer cta %d: items %u total %lld wait_full %lld wait_acc %lld wait_tokens %lld\n", blockIdx.x, n, clock64() - pf_t0, pf_full, pf_acc, pf_b);
+#endif
         }
     } else if (warp < C::W_LOAD0) {
         // ------------------------------ epilogue: accumulators -> f32 rows
         const int qd = warp & 3;                              // TMEM lane quarter this warp may read
-        const int half = (warp - C::W_EPI0) >> 2;             // even or odd 32-column chunks
+        const int half = (warp - C::W_EPI0) >> 2;             // which of the quarter's warps: 32-column chunks in turn
         uint32_t n = 0;
         bool ok = true;
+#ifdef Q36_TCPROF
+        long long pf_w = 0, pf_busy = 0, pf_x, pf_y;
+#endif
         for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x, n++) {
             const TcTile t = get_item(ii);
             for (int j = 0; j < DR_MC && ok; j++) {
                 const uint32_t q = n * DR_MC + j, buf = q % C::ACC_BUFS;
+#ifdef Q36_TCPROF
+                pf_x = clock64();
+#endif
                 if (!(ok = mbar_wait(acc_full0 + 8 * buf, (q / C::ACC_BUFS) & 1, &abort_flag, status, 0x400 + buf, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
+#ifdef Q36_TCPROF
+                pf_y = clock64(); pf_w += pf_y - pf_x;
+#endif
                 tc_fence_after();
                 const uint32_t tq = tmem + buf * C::ACC_STRIDE + ((uint32_t)(qd * 32) << 16);
                 const int mrow = (t.mt + j) * TC_M + qd * 32 + lane;
-                for (int c0 = 32 * half; c0 < t.nrows; c0 += 64) {
+                for (int c0 = 32 * half; c0 < t.nrows; c0 += 8 * C::EPI_WARPS) {
                     uint32_t v[32];
                     tc_ld32(tq + c0, v);
                     tc_ld_wait();
@@ -985,8 +1023,15 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+#ifdef Q36_TCPROF
+                pf_busy += clock64() - pf_y;
+#endif
             }
         }
+#ifdef Q36_TCPROF
+        if (lane == 0 && warp == C::W_EPI0 && (blockIdx.x == 0 || blockIdx.x == 77))
+            printf("down epilogue cta %d: wait %lld busy %lld\n", blockIdx.x, pf_w, pf_busy);
+#endif
     } else {
         // ------------------------------ scale images: thread i owns row i of the token tile and of every weight-row tile
         const int i = threadIdx.x - 32 * C::W_LOAD0;
@@ -1304,9 +1349,10 @@ static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_
     if ((rc = make_map_scales(&maps.fb, Hs, R_max, nb, 0, 0, C::N))) return rc;
     static bool attr_done[MAX_DEVICES] = {false};
     if ((rc = ensure_smem_attr((const void *)k_down_resident, C::SMEM_BYTES, attr_done))) return rc;
-    const long max_items = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * (M / TC_M / DR_MC);
+    const int mc = (M / TC_M) % 16 == 0 ? 16 : DR_MC_MIN;
+    const long max_items = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * (M / TC_M / mc);
     const int grid = (int)min((long)sm_count(), max_items);
-    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status);
+    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc);
     return check_launch();
 }
 
@@ -1314,7 +1360,7 @@ int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int m
                    const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
     (void)max_group_rows;
     static const bool old_down = getenv("Q36_OLD_DOWN") != nullptr;
-    if (!old_down && FF == DownRes::KSTEPS * TC_KSTEP && D % (TC_M * DR_MC) == 0 && n_group + 1 <= DISPATCH_MAX_GROUPS)
+    if (!old_down && FF == DownRes::KSTEPS * TC_KSTEP && D % (TC_M * DR_MC_MIN) == 0 && n_group + 1 <= DISPATCH_MAX_GROUPS)
         return run_down_resident(Wd, Sd, n_group, R_max, Hq, Hs, Y, D, FF, plan, status, st);
     return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
 }

@@ -1,30 +1,28 @@
-// Prefill-sized expert groups: grouped GEMM on the 5th-generation tensor cores.
-//
-//   D[128 weight rows x N tokens] += A[128 x K] (MXFP4 codes + E8M0 scales)
-//                                  * B[N x K]^T (E4M3 codes + UE8M0 scales)
-//   tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale, accumulators in TMEM.
+// Prefill-sized expert groups: grouped GEMMs on the 5th-generation tensor cores
+// (tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale, accumulators in TMEM).
 //
 // Replaces k_gemm_expert_mma (q36_engine.cu:2435-2524; mma.sync m16n8k32
 // block-scaled, an sm_120a-only instruction) for gate/up and k_gemm_expert_tc
 // (:2723-2766) for an MXFP4 down projection.
 //
+// Kernels
+//   k_gateup_wide     gate/up + SwiGLU + requantise: 128 token rows (E4M3) as the 128-row operand against the
+//                     128 gate + 128 up rows of an ff tile as one N = 256 operand (E2M1)
+//   k_grouped_mma<2>  the same with weights as the 128-row operand and up to 112 tokens as N (selectable)
+//   k_down_resident   down for FF = 512: a token tile's rows stay in shared memory, weight-row tiles stream past
+//   k_grouped_mma<1>  down for other shapes
 // Operand staging
-//   A  TMA, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B: the packed code plane
-//      (K/2 bytes per row, GGUF nibble order) is expanded on the fly into the
-//      padded form the tensor core reads (16 codes in 8 B + 8 B gap), 128 B of
-//      shared memory per 128 K-elements, 128B swizzle.
-//   B  TMA, UINT8, boxes of 16 token rows x 128 B, 128B swizzle.  Rows are in
-//      "hw order" inside each 32-block, so that position p of B meets nibble p
-//      of A.
-//   SF four warps copy the E8M0 bytes of the tile's rows from the row-major
-//      scale planes into shared memory in the 32 x 16 B image that
-//      tcgen05.cp.32x128b.warpx4 broadcasts into TMEM: row m of the tile at
-//      byte (m % 32) * 16 + (m / 32) * 4 + kb.
-// Roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
-// warps 2-5 epilogue (TMEM -> registers -> global), warps 6-9 scale loaders.
-// One persistent CTA per SM walks a tile table built on the device (largest
-// groups first).  Every mbarrier wait is bounded; a wait that gives up raises
-// a status word that the host entry point reports as Q36_MOE_EDEVICE.
+//   weights  TMA, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B: the packed code plane (K/2 bytes per row, GGUF nibble
+//            order) is expanded on the fly into the padded form the tensor core reads (16 codes in 8 B + 8 B
+//            gap), 128 B of shared memory per row per 128 K-elements, 128B swizzle.
+//   tokens   TMA, UINT8, boxes of token rows x 128 B, 128B swizzle.  Rows are in "hw order" inside each 32-block,
+//            so that position p of a token row meets nibble p of a weight row.
+//   scales   the E8M0 bytes arrive by TMA from the row-major scale planes (items of four K steps); four warps put
+//            them into TMEM as the image the MMA reads: row m at lane m % 32, column m / 32, byte kb, once per
+//            lane quarter -- by tcgen05.st, or through a 32 x 16 B shared-memory image and tcgen05.cp.32x128b.warpx4.
+// One persistent CTA per SM walks a tile table built on the device (largest groups first); every role is a warp
+// (or four) of its own.  Every mbarrier wait is bounded; a wait that gives up raises a status word that the host
+// entry point reports as Q36_MOE_EDEVICE.  -DQ36_TCPROF adds clock64 sums per role, printed by a few CTAs.
 #include <cuda.h>
 #include <stdlib.h>
 

@@ -64,7 +64,11 @@ def _worker(rank, world, port, q):
                 w = max(w, float((out - ref).norm() / ref.norm()))
             dist.barrier()
             nat.close()
-            worst[f"{name} T={T}{' same' if same else ''}"] = w
+            # the rank's grouped FFN runs over world * T * K received slots + T own rows, the single-GPU layer over
+            # T * (K + 1): when the two fall on different sides of the one-launch row limit, other kernels compute them
+            lim = moe.lib.q36_moe_one_launch_rows()
+            other = (world * T * K + T > lim) != (T * (K + 1) > lim)
+            worst[f"{name} T={T}{' same' if same else ''}{' other-kernels' if other else ''}"] = w
     q.put((rank, worst))
     dist.barrier()
     dist.destroy_process_group()

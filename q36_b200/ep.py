@@ -95,9 +95,10 @@ def _soffs(R: int, T: int, device) -> torch.Tensor:
     return _SOFFS_CACHE[key]
 
 
-def ep_layer(ops, layer, X, logits, world: int, rank: int, E: int, k: int, path: int, group=None):
-    """One expert-parallel layer step for this rank's T tokens.  Returns out [T,D] f32.
-    Launch-only (no host synchronisation), so a whole stack of these can be captured in one CUDA graph."""
+def ep_layer(ops, layer, X, logits, world: int, rank: int, E: int, k: int, path: int, group=None, reduced: bool = False):
+    """One expert-parallel layer step for this rank's T tokens (the same T on every rank).  Returns out [T,D] f32.
+    reduced: the expert ranks sum a token's result rows with the combine weights and return one row per (token,
+    expert rank) instead of one per (token, expert) -- what the native step does for prefill-sized calls."""
     T, D = X.shape
     C = T * k
     per = E // world
@@ -120,10 +121,27 @@ def ep_layer(ops, layer, X, logits, world: int, rank: int, E: int, k: int, path:
     soffs = _soffs(R, T, X.device)
     Y = ops.ffn(layer, loffs[se0:], rows_q, rows_s, soffs, path)                  # [R+T, D] f32
     back = ops.gather_rows(Y, lpos)                                               # result row of every received slot
-    recv_y = torch.empty_like(back)
-    dist.all_to_all_single(recv_y, back, group=group)
     stride = logits.shape[1]
     shg = logits[:, E:] if stride > E else None
+    if reduced:
+        # the weight of every send slot travels with its token index; empty slots carry weight 0 and token -1
+        wt_of_slot = torch.zeros(world * C, dtype=torch.float32, device=X.device)
+        wt_of_slot[ypos.long()] = wt.reshape(-1).float()
+        recv_t, recv_w = torch.empty_like(tok_of_slot), torch.empty_like(wt_of_slot)
+        dist.all_to_all_single(recv_t, tok_of_slot, group=group)
+        dist.all_to_all_single(recv_w, wt_of_slot, group=group)
+        src = torch.arange(world * C, device=X.device) // C                       # source rank of every received slot
+        row = (src * T + recv_t.long().clamp(min=0))                              # (source, token) -> row of the partial sums
+        contrib = back.float() * torch.where(recv_t >= 0, recv_w, torch.zeros_like(recv_w))[:, None]
+        partial = torch.zeros((world * T, D), dtype=torch.float32, device=X.device).index_add_(0, row, contrib)
+        recv_p = torch.empty_like(partial)
+        dist.all_to_all_single(recv_p, partial, group=group)                      # block r: what expert rank r summed for my tokens
+        out = recv_p.reshape(world, T, D).sum(0)
+        SH = Y[R:].float()
+        gate = torch.sigmoid(shg[:, 0].float())[:, None] if shg is not None else 1.0
+        return out + gate * SH
+    recv_y = torch.empty_like(back)
+    dist.all_to_all_single(recv_y, back, group=group)
     return ops.combine(recv_y, ypos, wt, Y[R:], shg, stride, D, k, T)
 
 

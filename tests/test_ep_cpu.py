@@ -100,7 +100,7 @@ class _Shard:
         self.Wg = self.Wu = self.Wd = self.Sg = self.Su = self.Sd = None
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, reduced=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -111,7 +111,7 @@ def _worker(rank, world, port, q):
     L = synth.router_logits(rng, T, E)
     per = E // world
     out = ep.ep_layer(OracleOps(O, w), _Shard(rank * per, (rank + 1) * per), torch.from_numpy(X), torch.from_numpy(L),
-                      world, rank, E, K, path=0)
+                      world, rank, E, K, path=0, reduced=reduced)
     idx, wt = O.router_topk(L, K, n_expert=E)
     want = O.moe_layer(w["gate"], w["up"], w["down"], w["sgate"][0], w["sup"][0], w["sdown"][0], D, FF, X, idx, wt, L[:, E])
     err = float(np.linalg.norm(out.numpy() - want) / np.linalg.norm(want))
@@ -138,13 +138,14 @@ def test_slot_maps_roundtrip():
 
 
 @pytest.mark.timeout(300)
-def test_ep_layer_two_ranks_gloo(oracle):
+@pytest.mark.parametrize("reduced", [False, True])      # one row back per (token, expert) | per (token, expert rank)
+def test_ep_layer_two_ranks_gloo(oracle, reduced):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, reduced)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in procs]

@@ -246,7 +246,7 @@ k_ep_wait_eids(const uint8_t *__restrict__ win, uint64_t hdr0, uint64_t hdr1, ui
 
 // Sorted row r (< R) <- received slot llist[r] (zeros beyond the resident count); rows [R, R + T) <- the rank's
 // own tokens (the shared expert's group).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, const int *ctl, const int *__restrict__ llist,
             const int *__restrict__ loffs_end, const uint8_t *__restrict__ Xq, const uint8_t *__restrict__ Xs, int R, int T, int D,
             uint8_t *__restrict__ rows_q, uint8_t *__restrict__ rows_s, int *status) {
@@ -256,7 +256,11 @@ k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, con
     const bool odd = ((unsigned)ctl[1] + 1u) & 1u;
     const uint8_t *recv = win + (odd ? rows1 : rows0);
     const int n_res = *loffs_end;          // rows that arrived; rows [n_res, R) belong to no group and are never used
-    for (int x = blockIdx.x; x < n_res + T; x += gridDim.x) {
+    // a warp per row, several 16-byte loads in flight per lane (a block per row at a time, each thread one load after
+    // a dependent index load, was bound by latency: 62 rows in turn per block at prefill sizes)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int uq = D / 16, us = nbs / 16;
+    for (int x = blockIdx.x * wpb + warp; x < n_res + T; x += gridDim.x * wpb) {
         const int r = x < n_res ? x : R + (x - n_res);
         const uint8_t *sq, *ss;
         if (r < R) {
@@ -267,8 +271,16 @@ k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, con
             ss = Xs + (size_t)(r - R) * nbs;
         }
         uint4 *dq = reinterpret_cast<uint4 *>(rows_q + (size_t)r * D), *ds = reinterpret_cast<uint4 *>(rows_s + (size_t)r * nbs);
-        for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dq[i] = reinterpret_cast<const uint4 *>(sq)[i];
-        for (int i = threadIdx.x; i < nbs / 16; i += blockDim.x) ds[i] = reinterpret_cast<const uint4 *>(ss)[i];
+        for (int i0 = lane; i0 < uq; i0 += 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + 32 * u < uq) v[u] = reinterpret_cast<const uint4 *>(sq)[i0 + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i0 + 32 * u < uq) dq[i0 + 32 * u] = v[u];
+        }
+        for (int i = lane; i < us; i += 32) ds[i] = reinterpret_cast<const uint4 *>(ss)[i];
     }
     Q36_TR_END(status, 3)
 }
@@ -338,7 +350,10 @@ k_ep_reduce_return(const float *__restrict__ Y, const int *__restrict__ lpos, co
     const int Ts = min(ts[tstride - 4], cap);
     float *dst0 = reinterpret_cast<float *>(peers[s] + (odd ? ret1 : ret0) + (size_t)me * cap * D * 4);
     constexpr int KMAX = 8;
-    for (int t = b; t < Ts; t += nb) {
+    // a warp per token: the chain table -> row position -> rows is three dependent latencies, so a block that took its
+    // tokens one after another was bound by latency; sixteen tokens per block are in flight here
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    for (int t = b * wpb + warp; t < Ts; t += nb * wpb) {
         int p[KMAX];
         float w[KMAX];
         bool any = false;
@@ -350,7 +365,7 @@ k_ep_reduce_return(const float *__restrict__ Y, const int *__restrict__ lpos, co
             w[q] = (q < k) ? tw[(size_t)t * k + q] : 0.f;
         }
         if (!any) continue;
-        for (int i = threadIdx.x * 4; i < D; i += blockDim.x * 4) {
+        for (int i = lane * 4; i < D; i += 128) {
             float4 y[KMAX];
 #pragma unroll
             for (int q = 0; q < KMAX; q++)
@@ -625,7 +640,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
                                       w.plan, D, FF, one_launch ? 16 : gateup_tile_rows())))   // (+ the work plan)
                 return rc;
         }
-        launch_k(k_ep_unpack, dim3(min(R + T, 8 * sm_count())), dim3(128), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,
+        launch_k(k_ep_unpack, dim3(min((R + T + 7) / 8, 16 * sm_count())), dim3(256), 0, st, (const uint8_t *)c->win, L.rows[0], L.rows[1], (const int *)ctl,
                  (const int *)w.llist, (const int *)(w.loffs + E), (const uint8_t *)w.Xq, (const uint8_t *)w.Xs, R, T, D, w.rows_q, w.rows_s, w.status);
         if ((rc = check_launch())) return rc;
         // grouped expert FFN on the local shard (+ shared expert on the own tokens)

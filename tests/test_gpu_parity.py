@@ -507,3 +507,31 @@ def test_the_selectable_earlier_kernels_still_agree_with_the_oracle():
                         "prefill_entry_by_name or prefill_layer_vs_oracle_small or ffn_tc_vs_oracle or ffn_one_launch_matches_two"],
                        env=env, capture_output=True, text=True, timeout=900, cwd=os.path.dirname(here))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("path_name", ["gemv", "tc"])
+def test_benchmark_configuration_0_single_expert_one_token(moe, oracle, torch_cuda, path_name):
+    """The reference's own CPU-runnable case, at full size: ONE expert (gate and up [512 x 2048], down [2048 x 512],
+    GGUF MXFP4 blocks with uniform codes and scale bytes in [118, 130], seed 0), ONE bf16 N(0,1) token.  Dequantised
+    weights bit-exact against the reference's C dequantiser; the quantised activation bit-exact; the expert's output
+    against the oracle's float64 product over those values."""
+    torch = torch_cuda
+    w = synth.layer(0, n_expert=1, D=D, FF=FF)
+    rng = np.random.default_rng(0)
+    x = synth.activations(rng, 1, D)
+    Wg, Wu, Wd = (moe.upload_mxfp4(w[k], K, M, 0, 1) for k, K, M in (("gate", D, FF), ("up", D, FF), ("down", FF, D)))
+    for name, W, M, K in (("gate", Wg, FF, D), ("up", Wu, FF, D), ("down", Wd, D, FF)):      # 3 x 32,768 blocks
+        np.testing.assert_array_equal(moe.dequant_mxfp4(W, M, K).cpu().numpy(), oracle.deq_matrix(w[name][0], M, K))
+    Xq, Xs = moe.quant_scatter(torch.from_numpy(x).cuda().to(torch.bfloat16), None, 0, 0, 1)
+    xq, xs = oracle.quant_e4m3(x)
+    np.testing.assert_array_equal(from_hw(Xq.cpu().numpy()), xq)
+    np.testing.assert_array_equal(Xs.cpu().numpy(), xs)
+    goffs = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    path = moe.PATH_GEMV if path_name == "gemv" else moe.PATH_TC
+    Hq, Hs, Y = moe.expert_ffn_sorted(Wg, Wu, Wd, 1, goffs, Xq, Xs, D, FF, path)
+    xd = oracle.dequant_e4m3(xq, xs)[0]
+    y, h, hq, hs = oracle.expert_ffn(w["gate"][0], w["up"][0], w["down"][0], D, FF, xd)
+    assert rel_l2(Y.cpu().numpy()[0], y) < TOL
+    y2, *_ = oracle.expert_ffn(w["gate"][0], w["up"][0], w["down"][0], D, FF, xd, hq_in=from_hw(Hq.cpu().numpy())[0],
+                               hs_in=Hs.cpu().numpy()[0])
+    assert rel_l2(Y.cpu().numpy()[0], y2) < TOL_STAGE

@@ -174,6 +174,24 @@ __device__ __forceinline__ void swiglu_quant_store(const float (&g)[NC], const f
     }
 }
 
+// Result rows between the down projection and the combine are staged as f32, or -- prefill-sized calls of the
+// whole-layer entries -- as bf16 (half the bytes of the largest round trip through HBM of such a layer; 1e-3 instead
+// of 1e-7 against a float64 product, inside the 1e-2 the path is held to).  Four consecutive elements from element e.
+__device__ __forceinline__ float4 ld_y4(const void *Y, size_t e, int y_bf16) {
+    if (!y_bf16) return *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(Y) + e);
+    const uint2 v = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(Y) + e);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+}
+__device__ __forceinline__ void st_y(void *Y, size_t e, float v, int y_bf16) {
+    if (y_bf16) reinterpret_cast<__nv_bfloat16 *>(Y)[e] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float *>(Y)[e] = v;
+}
+// row r of such a buffer
+__host__ __device__ __forceinline__ const float *y_row(const void *Y, size_t r, int D, int y_bf16) {
+    return reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(Y) + r * (size_t)D * (y_bf16 ? 2 : 4));
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -68,7 +68,7 @@ int launch_gateup_gemv(const void *Wg, const void *Wu, int n_group, const int *g
 int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *Sd, const int *soffs,
                      const uint8_t *Hq, const uint8_t *Hs, float *Y, int D, int FF, cudaStream_t st);
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
-                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st);
+                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st, int y_bf16 = 0);
 int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,
                        cudaStream_t st);
 int launch_dequant_mxfp4(const void *W, int M, int K, float *out, cudaStream_t st);
@@ -80,7 +80,7 @@ int launch_pre_norm_router(float *h, const float *a, const float *norm_w, float 
                            int gate_row, float *x, float *logits, int logit_stride, int T, int D, cudaStream_t st);
 int launch_combine_add_rmsnorm(float *moe_out, const float *Y, const int *pos, const float *wt, const float *SH,
                                const float *shgate, int shgate_stride, float *h, const float *w_next, float eps, float *x_next,
-                               int D, int k, int T, bool early_meta, cudaStream_t st);
+                               int D, int k, int T, bool early_meta, cudaStream_t st, int y_bf16 = 0);
 
 // moe_tc.cu
 // One plan per grouped-FFN call (groups = n_group routed + the shared expert's when soffs != NULL), then the
@@ -95,7 +95,10 @@ int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void 
 // a 32-thread kernel that waits (1024 polls) on a barrier nobody completes, records the give-up in status[0] and returns
 int launch_wait_timeout(int *status, cudaStream_t st);
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq, const uint8_t *Hs,
-                   float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st);
+                   float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st, int y_bf16 = 0);
+// 1 when prefill-sized calls of the whole-layer entries stage their result rows as bf16 (Q36_Y_F32=1 in the
+// environment keeps f32)
+int stage_y_bf16();
 
 // host helpers of moe_tc.cu shared with moe_tc_fused.cu
 int make_map_codes(CUtensorMap *m, const void *base, int M, int K, int n_group, uint64_t expert_stride);

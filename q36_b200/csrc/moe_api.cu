@@ -136,6 +136,8 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     if (!fused_quant && (rc = launch_quant(X, x_is_bf16, w.Xq, w.Xs, T, D, w.pos, k, shared ? n : -1, true, st))) return rc;
     const int ng = se1 - se0;
     const int *goffs = w.eoffs + se0;
+    // the two grouped-GEMM launches stage their result rows as bf16 for the combine (see ld_y4)
+    const int ybf = (use_tc && !decode_kernel) ? stage_y_bf16() : 0;
     if (!use_tc) {
         if ((rc = launch_gateup_gemv(Wg, Wu, ng, goffs, shared ? Sg : nullptr, shared ? Su : nullptr, w.soffs, w.Xq,
                                      w.Xs, w.Hq, w.Hs, D, FF, st)))
@@ -151,7 +153,7 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
         if ((rc = launch_gateup_tc(Wg, Wu, shared ? Sg : nullptr, shared ? Su : nullptr, ng, R, T, w.Xq, w.Xs, w.Hq, w.Hs,
                                    D, FF, w.plan, w.status + 0, st)))
             return rc;
-        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, ng, R, T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+        if ((rc = launch_down_tc(Wd, shared ? Sd : nullptr, ng, R, T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st, ybf)))
             return rc;
         }
     }
@@ -159,11 +161,11 @@ static int layer_impl(const void *Wg, const void *Wu, const void *Wd, const void
     // (behind the decode kernel the combine may read the routing results before its grid dependency resolves:
     // that kernel lets its successor start only after it has seen the front end complete)
     if (post.h) {
-        if ((rc = launch_combine_add_rmsnorm(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride,
-                                             post.h, post.w_next, post.eps, post.x_next, D, k, T, decode_kernel, st)))
+        if ((rc = launch_combine_add_rmsnorm(out, w.Y, w.pos, w.wt, shared ? y_row(w.Y, n, D, ybf) : nullptr, shg, logit_stride,
+                                             post.h, post.w_next, post.eps, post.x_next, D, k, T, decode_kernel, st, ybf)))
             return rc;
-    } else if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? w.Y + (size_t)n * D : nullptr, shg, logit_stride, D, k,
-                                    T, decode_kernel, st)))
+    } else if ((rc = launch_combine(out, w.Y, w.pos, w.wt, shared ? y_row(w.Y, n, D, ybf) : nullptr, shg, logit_stride, D, k,
+                                    T, decode_kernel, st, ybf)))
         return rc;
     if (idx_out && (rc = ck(cudaMemcpyAsync(idx_out, w.idx, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;
     if (wt_out && (rc = ck(cudaMemcpyAsync(wt_out, w.wt, (size_t)n * 4, cudaMemcpyDeviceToDevice, st)))) return rc;

@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(256)
 k_combine_add_rmsnorm(float *__restrict__ moe_out, const float *__restrict__ Y, const int *__restrict__ pos,
                       const float *__restrict__ wt, const float *__restrict__ SH, const float *__restrict__ shgate,
                       int shgate_stride, float *__restrict__ h, const float *__restrict__ w_next, float eps,
-                      float *__restrict__ x_next, int D, int k) {
+                      float *__restrict__ x_next, int D, int k, int y_bf16) {
     if (!EARLY_META) Q36_GDS();
     else cudaTriggerProgrammaticLaunchCompletion();
     __shared__ float part[8];
@@ -202,10 +202,10 @@ k_combine_add_rmsnorm(float *__restrict__ moe_out, const float *__restrict__ Y, 
         if (i >= n4) continue;
         float4 y[KMAX];
         float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (SH) ysh = reinterpret_cast<const float4 *>(SH + (size_t)t * D)[i];
+        if (SH) ysh = ld_y4(SH, (size_t)t * D + 4 * (size_t)i, y_bf16);
 #pragma unroll
         for (int s = 0; s < KMAX; s++)
-            y[s] = (p[s] >= 0) ? reinterpret_cast<const float4 *>(Y + (size_t)p[s] * D)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            y[s] = (p[s] >= 0) ? ld_y4(Y, (size_t)p[s] * D + 4 * (size_t)i, y_bf16) : make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 hv = reinterpret_cast<const float4 *>(h + (size_t)t * D)[i];
         float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -258,15 +258,15 @@ int launch_pre_norm_router(float *h, const float *a, const float *norm_w, float 
 
 int launch_combine_add_rmsnorm(float *moe_out, const float *Y, const int *pos, const float *wt, const float *SH,
                                const float *shgate, int shgate_stride, float *h, const float *w_next, float eps, float *x_next,
-                               int D, int k, int T, bool early_meta, cudaStream_t st) {
+                               int D, int k, int T, bool early_meta, cudaStream_t st, int y_bf16) {
     if (T <= 0) return Q36_MOE_OK;
     if (k <= 0 || k > 8 || D % 4 || D > 256 * 4 * ROW_F4) return Q36_MOE_EINVAL;
     if (early_meta)
         launch_k(k_combine_add_rmsnorm<true>, dim3(T), dim3(256), 0, st, moe_out, Y, pos, wt, SH, shgate, shgate_stride, h, w_next,
-                 eps, x_next, D, k);
+                 eps, x_next, D, k, y_bf16);
     else
         launch_k(k_combine_add_rmsnorm<false>, dim3(T), dim3(256), 0, st, moe_out, Y, pos, wt, SH, shgate, shgate_stride, h, w_next,
-                 eps, x_next, D, k);
+                 eps, x_next, D, k, y_bf16);
     return check_launch();
 }
 

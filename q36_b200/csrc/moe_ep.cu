@@ -291,7 +291,7 @@ k_ep_unpack(const uint8_t *__restrict__ win, uint64_t rows0, uint64_t rows1, con
 __global__ void __launch_bounds__(1024)
 k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int *__restrict__ counts, int world, int cap, int D,
             uint8_t *const *__restrict__ peers, int me, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1, int *ctl,
-            int slot_major_dst, int nb, int *status) {
+            int slot_major_dst, int nb, int *status, int y_bf16) {
     Q36_GDS();
     Q36_TR_BEGIN(status, 5)
     const int s = blockIdx.x / nb, b = blockIdx.x % nb;
@@ -312,7 +312,7 @@ k_ep_return(const float *__restrict__ Y, const int *__restrict__ lpos, const int
             if (x < total) {
                 const int q = x / f4, i = x - q * f4, j = b + nb * q;
                 const int p = lpos[s * cap + j];
-                v[u] = (p >= 0) ? reinterpret_cast<const float4 *>(Y + (size_t)p * D)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[u] = (p >= 0) ? ld_y4(Y, (size_t)p * D + 4 * (size_t)i, y_bf16) : make_float4(0.f, 0.f, 0.f, 0.f);
                 dptr[u] = dst0 + (size_t)j * f4 + i;
             }
         }
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(512)
 k_ep_reduce_return(const float *__restrict__ Y, const int *__restrict__ lpos, const uint8_t *__restrict__ win, uint64_t tslot0,
                    uint64_t tslot1, uint64_t twt0, uint64_t twt1, int tstride, int k, int world, int cap, int D,
                    uint8_t *const *__restrict__ peers, int me, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1, int *ctl,
-                   int nb, int *status) {
+                   int nb, int *status, int y_bf16) {
     Q36_GDS();
     Q36_TR_BEGIN(status, 5)
     const int s = blockIdx.x / nb, b = blockIdx.x % nb;
@@ -369,7 +369,7 @@ k_ep_reduce_return(const float *__restrict__ Y, const int *__restrict__ lpos, co
             float4 y[KMAX];
 #pragma unroll
             for (int q = 0; q < KMAX; q++)
-                y[q] = (p[q] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[q] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                y[q] = (p[q] >= 0) ? ld_y4(Y, (size_t)p[q] * D + i, y_bf16) : make_float4(0.f, 0.f, 0.f, 0.f);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int q = 0; q < KMAX; q++) {
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(256)
 k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t ret0, uint64_t ret1, uint64_t rhdr0, uint64_t rhdr1,
              int *ctl, int world, unsigned limit, int *status, const int *__restrict__ ypos, const float *__restrict__ wt,
              const float *__restrict__ SH, const float *__restrict__ shgate, int shgate_stride, int D, int k, unsigned expected,
-             int reduced, int cap) {
+             int reduced, int cap, int sh_bf16) {
     // reduced: the expert ranks sent one weighted partial row per token (row r * cap + t for rank r): add those of
     // the ranks that ran an entry of the token, in rank order
     // expected: arrivals every expert rank counts in at this rank's result header per call (the CTAs of its FFN
@@ -444,7 +444,7 @@ k_ep_combine(float *__restrict__ out, const uint8_t *__restrict__ win, uint64_t 
         }
         const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
         float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (SH) ysh = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
+        if (SH) ysh = ld_y4(SH, (size_t)t * D + i, sh_bf16);      // (the shared expert's rows come from this rank's own down launch)
 #pragma unroll
         for (int s = 0; s < KMAX; s++)
             y[s] = (p[s] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[s] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -591,6 +591,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
     // rank takes the same decision for equal T)
     const bool one_launch = ffn_fused_small_fits(R + T, per, D, FF) && (world * T <= 16 || R + T <= fused_rows_limit());
     const bool reduced = ep_reduced_return(c, one_launch);
+    const int ybf = one_launch ? 0 : stage_y_bf16();     // the two grouped-GEMM launches stage their result rows as bf16
     int rc;
     if (phase == 0) {
         // route + dispatch over ALL experts (their order is the destination-rank order); quantise the rank's tokens
@@ -655,7 +656,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             if ((rc = launch_gateup_tc(a.Wg, a.Wu, shared ? a.Sg : nullptr, shared ? a.Su : nullptr, per, R + T, R + T, w.rows_q, w.rows_s,
                                        w.Hq, w.Hs, D, FF, w.plan, w.status, st)))
                 return rc;
-            if ((rc = launch_down_tc(a.Wd, shared ? a.Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st)))
+            if ((rc = launch_down_tc(a.Wd, shared ? a.Sd : nullptr, per, R + T, R + T, w.Hq, w.Hs, w.Y, D, FF, w.plan, w.status + 1, st, ybf)))
                 return rc;
         }
         // (two launches: a kernel of its own puts the result rows into their home ranks' windows)
@@ -665,9 +666,9 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
             const int nb = ep_reduce_blocks(c);
             launch_k(k_ep_reduce_return, dim3(world * nb), dim3(512), 0, st, (const float *)w.Y, (const int *)w.lpos, (const uint8_t *)c->win,
                      L.tslot[0], L.tslot[1], L.twt[0], L.twt[1], L.tstride, k, world, C, D, (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1],
-                     L.rhdr[0], L.rhdr[1], ctl, nb, w.status);
+                     L.rhdr[0], L.rhdr[1], ctl, nb, w.status, ybf);
         } else if (!one_launch) launch_k(k_ep_return, dim3(world * nb_ret), dim3(1024), 0, st, (const float *)w.Y, (const int *)w.lpos, (const int *)w.counts, world, C, D,
-                 (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0, nb_ret, w.status);
+                 (uint8_t *const *)c->d_peer, rank, L.ret[0], L.ret[1], L.rhdr[0], L.rhdr[1], ctl, use_nccl ? 1 : 0, nb_ret, w.status, ybf);
         if ((rc = check_launch())) return rc;
         if (use_nccl) {
             if ((rc = all_to_all(api, c, c->stage + L.ret[par], c->win + L.ret[par], (size_t)C * D * 4, st))) return rc;
@@ -685,7 +686,7 @@ static int ep_phase(EpComm *c, int phase, const LayerArgs &a, cudaStream_t st) {
         const float *shg = (shared && a.shgate_col >= 0) ? a.logits + a.shgate_col : nullptr;
         launch_k(k_ep_combine, dim3((D / 4 + 255) / 256, T), dim3(256), 0, st, a.out, (const uint8_t *)c->win, L.ret[0], L.ret[1],
                  L.rhdr[0], L.rhdr[1], ctl, world, c->spin_limit, w.status, (const int *)w.ypos, (const float *)w.wt,
-                 shared ? (const float *)(w.Y + (size_t)R * D) : (const float *)nullptr, shg, a.logit_stride, D, k, expected, reduced ? 1 : 0, C);
+                 shared ? y_row(w.Y, R, D, ybf) : (const float *)nullptr, shg, a.logit_stride, D, k, expected, reduced ? 1 : 0, C, ybf);
         c->calls[2]++;
         return check_launch();
     }

@@ -211,7 +211,7 @@ template <bool EARLY_META>
 __global__ void __launch_bounds__(256)
 k_combine(float *__restrict__ out, const float *__restrict__ Y, const int *__restrict__ pos,
           const float *__restrict__ wt, const float *__restrict__ SH, const float *__restrict__ shgate,
-          int shgate_stride, int D, int k) {
+          int shgate_stride, int D, int k, int y_bf16) {
     if (!EARLY_META) Q36_GDS();
     else cudaTriggerProgrammaticLaunchCompletion();
     const int t = blockIdx.y;
@@ -232,10 +232,10 @@ k_combine(float *__restrict__ out, const float *__restrict__ Y, const int *__res
     const float gs = (SH && shgate) ? sigm_f(shgate[(size_t)t * shgate_stride]) : 1.f;
     if (EARLY_META) cudaGridDependencySynchronize();
     float4 ysh = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (SH) ysh = *reinterpret_cast<const float4 *>(SH + (size_t)t * D + i);
+    if (SH) ysh = ld_y4(SH, (size_t)t * D + i, y_bf16);
 #pragma unroll
     for (int s = 0; s < KMAX; s++)
-        y[s] = (p[s] >= 0) ? *reinterpret_cast<const float4 *>(Y + (size_t)p[s] * D + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        y[s] = (p[s] >= 0) ? ld_y4(Y, (size_t)p[s] * D + i, y_bf16) : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int s = 0; s < KMAX; s++) {
@@ -301,12 +301,12 @@ int launch_down_gemv(const void *Wd, int n_group, const int *goffs, const void *
     return check_launch();
 }
 int launch_combine(float *out, const float *Y, const int *pos, const float *wt, const float *SH,
-                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st) {
+                   const float *shgate, int shgate_stride, int D, int k, int T, bool early_meta, cudaStream_t st, int y_bf16) {
     if (T <= 0) return Q36_MOE_OK;
     if (k <= 0 || k > 8) return Q36_MOE_EINVAL;   // the kernel keeps one row per slot in registers
     dim3 grid((D / 4 + 255) / 256, T);
-    if (early_meta) launch_k(k_combine<true>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
-    else launch_k(k_combine<false>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k);
+    if (early_meta) launch_k(k_combine<true>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k, y_bf16);
+    else launch_k(k_combine<false>, dim3(grid), dim3(256), 0, st, out, Y, pos, wt, SH, shgate, shgate_stride, D, k, y_bf16);
     return check_launch();
 }
 int launch_gather_rows(const void *src, const int *index, void *dst, int n_rows, int row_bytes,

@@ -120,7 +120,7 @@ template <int NA>
 __global__ void __launch_bounds__(TcCfg<NA>::THREADS, 1)
 k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *__restrict__ plan,
               uint8_t *__restrict__ Hq, uint8_t *__restrict__ Hs, float *__restrict__ Y, int M_total, int K,
-              int *__restrict__ status) {
+              int *__restrict__ status, int y_bf16) {
     using Cfg = TcCfg<NA>;
     constexpr int W = (NA == 2) ? 0 : 1;
     extern __shared__ uint8_t smem_raw[];
@@ -395,7 +395,7 @@ k_grouped_mma(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                     tc_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; j++)
-                        if (c0 + j < t.nrows) Y[(size_t)(t.row0 + c0 + j) * M_total + mrow] = __uint_as_float(g[j]);
+                        if (c0 + j < t.nrows) st_y(Y, (size_t)(t.row0 + c0 + j) * M_total + mrow, __uint_as_float(g[j]), y_bf16);
                 }
             }
             tc_fence_before();
@@ -811,7 +811,7 @@ struct DownMaps { CUtensorMap a, s, b, fa, fs, fb; };   // routed / shared code 
 
 __global__ void __launch_bounds__(DownRes::THREADS, 1)
 k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPlan *__restrict__ plan, float *__restrict__ Y,
-                int M_total, int *__restrict__ status, int DR_MC) {
+                int M_total, int *__restrict__ status, int DR_MC, int y_bf16) {
     using C = DownRes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -1016,7 +1016,7 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
                     tc_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 32; c++)
-                        if (c0 + c < t.nrows) Y[(size_t)(t.row0 + c0 + c) * M_total + mrow] = __uint_as_float(v[c]);
+                        if (c0 + c < t.nrows) st_y(Y, (size_t)(t.row0 + c0 + c) * M_total + mrow, __uint_as_float(v[c]), y_bf16);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -1228,7 +1228,7 @@ static int make_map_scales(CUtensorMap *m, const void *base, int rows, int nb, i
 template <int NA>
 static int run_grouped(const void *A0, const void *A1, const void *S0, const void *S1, int n_group, int R_max,
                        const uint8_t *Bq, const uint8_t *Bs, uint8_t *Hq, uint8_t *Hs, float *Y, int M, int K,
-                       const void *plan, int *status, cudaStream_t st) {
+                       const void *plan, int *status, cudaStream_t st, int y_bf16 = 0) {
     using Cfg = TcCfg<NA>;
     if (M % TC_M || K % (4 * TC_KSTEP) || n_group + 1 > DISPATCH_MAX_GROUPS) return Q36_MOE_EINVAL;
     const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK);
@@ -1270,7 +1270,7 @@ static int run_grouped(const void *A0, const void *A1, const void *S0, const voi
     const long max_tiles = ((long)(R_max + Cfg::N - 1) / Cfg::N + n_group + 1) * m_tiles;
     const int grid = (int)min((long)sm_count(), max_tiles);
     launch_k(k_grouped_mma<NA>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Hq, Hs,
-             Y, M, K, status);
+             Y, M, K, status, y_bf16);
     return check_launch();
 }
 
@@ -1332,7 +1332,7 @@ int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void 
 }
 // K = 512 and D a multiple of DR_MC row tiles: the token-tile-resident kernel
 static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_max, const uint8_t *Hq, const uint8_t *Hs, float *Y,
-                             int M, int K, const void *plan, int *status, cudaStream_t st) {
+                             int M, int K, const void *plan, int *status, cudaStream_t st, int y_bf16) {
     using C = DownRes;
     const uint64_t estride = (uint64_t)M * (K / 2) + (uint64_t)M * (K / Q36_QK), plane = (uint64_t)M * (K / 2);
     const int nb = K / Q36_QK;
@@ -1350,17 +1350,22 @@ static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_
     const int mc = (M / TC_M) % 16 == 0 ? 16 : DR_MC_MIN;
     const long max_items = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * (M / TC_M / mc);
     const int grid = (int)min((long)sm_count(), max_items);
-    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc);
+    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc, y_bf16);
     return check_launch();
 }
 
+int stage_y_bf16() {
+    static const int on = getenv("Q36_Y_F32") ? 0 : 1;
+    return on;
+}
+
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq,
-                   const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st) {
+                   const uint8_t *Hs, float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st, int y_bf16) {
     (void)max_group_rows;
     static const bool old_down = getenv("Q36_OLD_DOWN") != nullptr;
     if (!old_down && FF == DownRes::KSTEPS * TC_KSTEP && D % (TC_M * DR_MC_MIN) == 0 && n_group + 1 <= DISPATCH_MAX_GROUPS)
-        return run_down_resident(Wd, Sd, n_group, R_max, Hq, Hs, Y, D, FF, plan, status, st);
-    return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st);
+        return run_down_resident(Wd, Sd, n_group, R_max, Hq, Hs, Y, D, FF, plan, status, st, y_bf16);
+    return run_grouped<1>(Wd, nullptr, Sd, nullptr, n_group, R_max, Hq, Hs, nullptr, nullptr, Y, D, FF, plan, status, st, y_bf16);
 }
 
 }  // namespace q36

@@ -495,13 +495,13 @@ def test_prefill_layer_full_size_zipf(moe, oracle, torch_cuda, layer, weights):
 
 
 def test_the_selectable_earlier_kernels_still_agree_with_the_oracle():
-    """k_grouped_mma<2> (gate/up with weights as the 128-row operand) and k_grouped_mma<1> (the generic down kernel)
-    stay in the library behind environment switches read once per process: run the prefill-sized oracle tests in a
-    child process that selects them."""
+    """k_grouped_mma<2> (gate/up with weights as the 128-row operand), k_grouped_mma<1> (the generic down kernel) and
+    f32 staging of the result rows between down and combine stay in the library behind environment switches read
+    once per process: run the prefill-sized oracle tests in a child process that selects them."""
     import os
     import subprocess
     import sys
-    env = dict(os.environ, Q36_GATEUP_NARROW="1", Q36_OLD_DOWN="1")
+    env = dict(os.environ, Q36_GATEUP_NARROW="1", Q36_OLD_DOWN="1", Q36_Y_F32="1")
     here = os.path.dirname(os.path.abspath(__file__))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_parity.py"), "-x", "-q", "-m", "gpu", "-k",
                         "prefill_entry_by_name or prefill_layer_vs_oracle_small or ffn_tc_vs_oracle or ffn_one_launch_matches_two"],

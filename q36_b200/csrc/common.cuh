@@ -175,8 +175,9 @@ __device__ __forceinline__ void swiglu_quant_store(const float (&g)[NC], const f
 }
 
 // Result rows between the down projection and the combine are staged as f32, or -- prefill-sized calls of the
-// whole-layer entries -- as bf16 (half the bytes of the largest round trip through HBM of such a layer; 1e-3 instead
-// of 1e-7 against a float64 product, inside the 1e-2 the path is held to).  Four consecutive elements from element e.
+// whole-layer entries, when asked for (stage_y_bf16) -- as bf16: half the bytes of the largest round trip through HBM
+// of such a layer, for 1.6e-3 instead of 1.5e-7 against a float64 product (the path is held to 1e-2).  Four
+// consecutive elements from element e.
 __device__ __forceinline__ float4 ld_y4(const void *Y, size_t e, int y_bf16) {
     if (!y_bf16) return *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(Y) + e);
     const uint2 v = *reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(Y) + e);

@@ -96,8 +96,8 @@ int launch_gateup_tc(const void *Wg, const void *Wu, const void *Sg, const void 
 int launch_wait_timeout(int *status, cudaStream_t st);
 int launch_down_tc(const void *Wd, const void *Sd, int n_group, int R_max, int max_group_rows, const uint8_t *Hq, const uint8_t *Hs,
                    float *Y, int D, int FF, const void *plan, int *status, cudaStream_t st, int y_bf16 = 0);
-// 1 when prefill-sized calls of the whole-layer entries stage their result rows as bf16 (Q36_Y_F32=1 in the
-// environment keeps f32)
+// 1 when prefill-sized calls of the whole-layer entries stage their result rows as bf16 (Q36_Y_BF16=1 in the
+// environment; the default is f32, which keeps the layer at 1e-7 of a float64 product instead of 1e-3)
 int stage_y_bf16();
 
 // host helpers of moe_tc.cu shared with moe_tc_fused.cu

@@ -1355,7 +1355,7 @@ static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_
 }
 
 int stage_y_bf16() {
-    static const int on = getenv("Q36_Y_F32") ? 0 : 1;
+    static const int on = getenv("Q36_Y_BF16") ? 1 : 0;
     return on;
 }
 

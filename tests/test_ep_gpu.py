@@ -97,5 +97,5 @@ def test_ep_layer_across_gpus(world):
             # same quantised rows, same kernels: only the summation grouping differs from the single-GPU layer -- unless
             # other FFN kernels than the single-GPU layer takes compute the rank's rows: their f32 sums differ in order,
             # so a code of the quantised intermediate may land on the other side of a rounding boundary now and then
-            tol = 5e-3 if "other-kernels" in case else 1e-5
+            tol = 2e-3 if "other-kernels" in case else 1e-5
             assert err < tol, f"world {world} rank {rank} {case}: rel-L2 vs single-GPU layer {err}"

@@ -73,7 +73,7 @@ def test_local_ranks_match_the_single_gpu_layer(moe, full, world, T, same):
                 # other side of a rounding boundary now and then
                 lim = moe.lib.q36_moe_one_launch_rows()
                 other = (world * T * K8 + T > lim) != (T * (K8 + 1) > lim)
-                tol = 5e-3 if other else 1e-5
+                tol = 2e-3 if other else 1e-5
                 assert err < tol, f"call {call} rank {r}: rel-L2 vs single-GPU layer {err}"
     finally:
         loc.close()

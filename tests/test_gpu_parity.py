@@ -304,7 +304,7 @@ def test_prefill_entry_by_name(moe, oracle, torch_cuda, layer, weights):
     """q36_moe_prefill (the drop-in for pf_moe_block): bit-identical to q36_moe_layer with path AUTO at a
     prefill-sized call, and within tolerance of the oracle on sampled tokens."""
     torch = torch_cuda
-    T = 300
+    T = 600                                  # 5400 sorted rows: beyond the one-launch kernel's row limit
     rng = np.random.default_rng(901)
     X = synth.activations(rng, T, D)
     L = synth.router_logits(rng, T, E, zipf=True)
@@ -473,7 +473,7 @@ def test_tc_and_gemv_paths_agree(moe, oracle, torch_cuda, layer, weights):
 
 
 def test_prefill_layer_vs_oracle_small(moe, oracle, torch_cuda, layer, weights):
-    _check_layer(moe, oracle, torch_cuda, layer, weights, 300, moe.PATH_TC, np.random.default_rng(70), zipf=True)
+    _check_layer(moe, oracle, torch_cuda, layer, weights, 600, moe.PATH_TC, np.random.default_rng(70), zipf=True)
 
 
 def test_prefill_layer_full_size_zipf(moe, oracle, torch_cuda, layer, weights):
@@ -494,14 +494,15 @@ def test_prefill_layer_full_size_zipf(moe, oracle, torch_cuda, layer, weights):
     np.testing.assert_array_equal(out_p, out[perm])
 
 
-def test_the_selectable_earlier_kernels_still_agree_with_the_oracle():
-    """k_grouped_mma<2> (gate/up with weights as the 128-row operand), k_grouped_mma<1> (the generic down kernel) and
-    f32 staging of the result rows between down and combine stay in the library behind environment switches read
-    once per process: run the prefill-sized oracle tests in a child process that selects them."""
+@pytest.mark.parametrize("switches", [{"Q36_GATEUP_NARROW": "1", "Q36_OLD_DOWN": "1"}, {"Q36_Y_BF16": "1"}])
+def test_the_selectable_variants_still_agree_with_the_oracle(switches):
+    """k_grouped_mma<2> (gate/up with weights as the 128-row operand) and k_grouped_mma<1> (the generic down kernel),
+    and bf16 staging of the result rows between down and combine, sit behind environment switches read once per
+    process: run the prefill-sized oracle tests in a child process that selects them."""
     import os
     import subprocess
     import sys
-    env = dict(os.environ, Q36_GATEUP_NARROW="1", Q36_OLD_DOWN="1", Q36_Y_F32="1")
+    env = dict(os.environ, **switches)
     here = os.path.dirname(os.path.abspath(__file__))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_gpu_parity.py"), "-x", "-q", "-m", "gpu", "-k",
                         "prefill_entry_by_name or prefill_layer_vs_oracle_small or ffn_tc_vs_oracle or ffn_one_launch_matches_two"],

@@ -809,9 +809,11 @@ constexpr int DR_MC_MIN = 8;   // weight-row tiles per work item: 16 when the ro
 
 struct DownMaps { CUtensorMap a, s, b, fa, fs, fb; };   // routed / shared code planes (2 K steps per box), token rows, scale planes
 
+template <int YBF>      // result rows stored as bf16 (a compile-time choice: the store loop is what paces this kernel)
 __global__ void __launch_bounds__(DownRes::THREADS, 1)
 k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPlan *__restrict__ plan, float *__restrict__ Y,
-                int M_total, int *__restrict__ status, int DR_MC, int y_bf16) {
+                int M_total, int *__restrict__ status, int DR_MC) {
+    constexpr int y_bf16 = YBF;
     using C = DownRes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -1345,12 +1347,14 @@ static int run_down_resident(const void *Wd, const void *Sd, int n_group, int R_
     if ((rc = make_map_scales(&maps.fa, (const uint8_t *)Wd + plane, M, nb, n_group, estride, TC_M))) return rc;
     if ((rc = make_map_scales(&maps.fs, (const uint8_t *)Sd + plane, M, nb, 1, estride, TC_M))) return rc;
     if ((rc = make_map_scales(&maps.fb, Hs, R_max, nb, 0, 0, C::N))) return rc;
-    static bool attr_done[MAX_DEVICES] = {false};
-    if ((rc = ensure_smem_attr((const void *)k_down_resident, C::SMEM_BYTES, attr_done))) return rc;
+    static bool attr_done[MAX_DEVICES] = {false}, attr_done_bf[MAX_DEVICES] = {false};
+    if ((rc = ensure_smem_attr(y_bf16 ? (const void *)k_down_resident<1> : (const void *)k_down_resident<0>, C::SMEM_BYTES,
+                               y_bf16 ? attr_done_bf : attr_done))) return rc;
     const int mc = (M / TC_M) % 16 == 0 ? 16 : DR_MC_MIN;
     const long max_items = ((long)(R_max + C::N - 1) / C::N + n_group + 1) * (M / TC_M / mc);
     const int grid = (int)min((long)sm_count(), max_items);
-    launch_k(k_down_resident, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc, y_bf16);
+    if (y_bf16) launch_k(k_down_resident<1>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc);
+    else launch_k(k_down_resident<0>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, st, maps, n_group, (const TcPlan *)plan, Y, M, status, mc);
     return check_launch();
 }
 

@@ -361,6 +361,9 @@ int q36_moe_gather_rows(const void *src, const int *index, void *dst, int n_rows
  * q36_moe_ep_layer_phase issues one of its three phases (0 route + send, 1 expert work + return, 2 combine): a
  * host thread that drives several local ranks must issue phase p for EVERY rank before phase p + 1 of any, and a
  * caller may put phase 0 of the next call's tokens on another stream to overlap it with phase 1 of this one.
+ * (such calls alternate between two workspaces).  T must be the same on every rank of a call.  Calls with more
+ * rows on a rank than q36_moe_one_launch_rows() return one weighted partial row per (token, expert rank) when
+ * cap_rows >= T_max, else one row per (token, expert) like the smaller calls.
  * Every cross-rank wait is bounded and reports through the status words (0xB00 + source, 0xC00 + source).
  * ws: q36_moe_ep_workspace_bytes(...) bytes with the T_max / cap_rows the window was opened with; its first 256
  * bytes are the status words (q36_moe_ws_reset, q36_moe_ws_status).

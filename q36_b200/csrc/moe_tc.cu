@@ -1137,8 +1137,15 @@ static int encode_cached(CUtensorMap *m, const MapKey &k, CUtensorMapDataType dt
     EncodeTiledFn fn = encode_fn();
     if (!fn) return Q36_MOE_ECUDA;
     const cuuint32_t el[5] = {1, 1, 1, 1, 1};
+    // L2 promotion 256 B: every operand is consumed along K by the same SM, so what a copy pulls into L2 beyond its box is
+    // the next stages' data (measured: decode kernel 26.5 against 26.9 us with 128 B, 27.7 with 64 B; Q36_L2PROMO overrides)
+    static const int promo = getenv("Q36_L2PROMO") ? atoi(getenv("Q36_L2PROMO")) : 256;
+    const CUtensorMapL2promotion l2p = promo == 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                       : promo == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                       : promo == 0  ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                                     : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
     CUresult r = fn(m, dt, (cuuint32_t)rank, const_cast<void *>(k.base), dims, strides, box, el, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    l2p, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { last_cuda_error() = 100000 + (int)r; return Q36_MOE_ECUDA; }
     slot.key = k; slot.map = *m; slot.used = true;
     return Q36_MOE_OK;

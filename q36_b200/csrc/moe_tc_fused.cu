@@ -222,10 +222,12 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const uint64_t w_policy = l2_policy_evict_first();
             for (int j = 0; j < my_tiles && ok; j++) {
                 const FTile t = get_tile(j);
                 const bool sh = t.g >= n_routed;
                 const int ge = sh ? 0 : t.g;
+                const bool once = (int)s_cnt[t.g] <= Cfg::TILE_ROWS;    // a group of one token tile: its weights are read once
                 const CUtensorMap *ma0 = t.kind ? (sh ? &maps.sd : &maps.d) : (sh ? &maps.sg : &maps.g);
                 const CUtensorMap *ma1 = sh ? &maps.su : &maps.u;
                 const int nst = t.kind ? FF / (Cfg::KS * TC_KSTEP) : 2 * (D / (Cfg::KS * TC_KSTEP));   // gate, up, gate, ...
@@ -236,7 +238,10 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                     if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_flag, status, 0x100 + s))) break;
                     const uint32_t sb = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, Cfg::STAGE_TX_A);
-                    tma_load_4d(sb, (!t.kind && (q & 1)) ? ma1 : ma0, 0, t.mt * TC_M, kpair * Cfg::KS, ge, full0 + 8 * s);
+                    // weights that are read once per call: evict-first in L2, so that they do not displace the token rows,
+                    // the intermediate and the scale bytes that other SMs re-read (measured: 25.95 against 26.5 us per launch)
+                    if (once) tma_load_4d_hint(sb, (!t.kind && (q & 1)) ? ma1 : ma0, 0, t.mt * TC_M, kpair * Cfg::KS, ge, full0 + 8 * s, w_policy);
+                    else tma_load_4d(sb, (!t.kind && (q & 1)) ? ma1 : ma0, 0, t.mt * TC_M, kpair * Cfg::KS, ge, full0 + 8 * s);
                 }
             }
         }

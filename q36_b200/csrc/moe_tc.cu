@@ -536,11 +536,13 @@ k_gateup_wide(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
 #ifdef Q36_TCPROF
                 long long pf_w = 0, pf_x, pf_t0 = clock64();
 #endif
+                const uint64_t w_policy = l2_policy_evict_first();
                 for (int ti = my_first; ti < n_tiles && ok; ti += gridDim.x) {
                     const TcTile t = get_tile(ti);
                     const bool sh = t.g >= n_routed;
                     const CUtensorMap *mm = sh ? (lane ? &maps.s1 : &maps.s0) : (lane ? &maps.a1 : &maps.a0);
                     const int ge = sh ? 0 : t.g;
+                    const bool once = s_cnt[t.g] <= C::N;      // a group of one token tile: its weights are read once
                     for (int ks = 0; ks < k_steps; ks++, it++) {
                         const int s = it % C::STAGES;
 #ifdef Q36_TCPROF
@@ -553,7 +555,8 @@ k_gateup_wide(const __grid_constant__ TcMaps maps, int n_routed, const TcPlan *_
                         const uint32_t sb = smem_u32(smem + s * C::STAGE_BYTES) + C::A_BYTES + lane * C::B_HALF;
                         if (lane == 0) mbar_expect_tx(full0 + 8 * s, 2 * C::B_TX);
                         __syncwarp(3u);                      // the expected bytes are registered before either copy can complete
-                        tma_load_3d(sb, mm, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
+                        if (once) tma_load_3d_hint(sb, mm, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s, w_policy);
+                        else tma_load_3d(sb, mm, ks * TC_KSTEP, t.mt * TC_M, ge, full0 + 8 * s);
                     }
                 }
 #ifdef Q36_TCPROF
@@ -870,11 +873,13 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
         if (lane == 0) {
             uint32_t q = 0;
             bool ok = true;
+            const uint64_t w_policy = l2_policy_evict_first();
             for (int ii = blockIdx.x; ii < n_items && ok; ii += gridDim.x) {
                 const TcTile t = get_item(ii);
                 const bool sh = t.g >= n_routed;
                 const CUtensorMap *ma = sh ? &maps.s : &maps.a, *mf = sh ? &maps.fs : &maps.fa;
                 const int ge = sh ? 0 : t.g;
+                const bool once = s_cnt[t.g] <= C::N;      // a group of one token tile: its weights are read once (evict-first in L2)
                 for (int j = 0; j < DR_MC && ok; j++, q++) {
                     const int mrow0 = (t.mt + j) * TC_M;
                     const uint32_t sl = q % C::SFR_SLOTS;
@@ -885,7 +890,8 @@ k_down_resident(const __grid_constant__ DownMaps maps, int n_routed, const TcPla
                         const uint32_t it = q * (C::KSTEPS / C::KS) + h, s = it % C::STAGES;
                         if (!(ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) & 1) ^ 1, &abort_flag, status, 0x100 + s, TC_SPIN_LIMIT, TC_BACKOFF_NS))) break;
                         mbar_expect_tx(full0 + 8 * s, C::KS * C::A_TX);
-                        tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES), ma, 0, mrow0, h * C::KS, ge, full0 + 8 * s);
+                        if (once) tma_load_4d_hint(smem_u32(smem + s * C::STAGE_BYTES), ma, 0, mrow0, h * C::KS, ge, full0 + 8 * s, w_policy);
+                        else tma_load_4d(smem_u32(smem + s * C::STAGE_BYTES), ma, 0, mrow0, h * C::KS, ge, full0 + 8 * s);
                     }
                 }
             }

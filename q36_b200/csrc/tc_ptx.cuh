@@ -70,6 +70,12 @@ __device__ __forceinline__ void tma_load_4d_hint(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w), "l"(policy)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+        ::"r"(dst), "l"(m), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, int x, int y, int z, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"

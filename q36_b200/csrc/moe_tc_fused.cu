@@ -249,6 +249,7 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
         // ----- scale producer: a tile's scale bytes, contiguous runs of the row-major planes, two tiles deep
         if (lane == 0) {
             bool ok = true;
+            const uint64_t s_policy = l2_policy_evict_first();
             for (int j = 0; ok && tile_wait(j, 0x680); j++) {
                 const FTile t = get_tile(j);
                 // (the watcher's acquire ordered the other CTAs' generic-proxy stores of Hq/Hs; this orders them
@@ -264,8 +265,13 @@ k_ffn_fused_small(const __grid_constant__ FusedMaps maps, const uint8_t *__restr
                 const uint8_t *p0 = t.kind ? (sh ? sfSD : sfD) : (sh ? sfSG : sfG);
                 const uint32_t dst = smem_u32(sft + slot * Cfg::SFT_BYTES);
                 mbar_expect_tx(sft_full0 + 8 * slot, a_bytes * (t.kind ? 1 : 2) + b_bytes);
-                bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
-                if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
+                if ((int)s_cnt[t.g] <= Cfg::TILE_ROWS) {      // read once, like the tile's weights: evict-first
+                    bulk_load_hint(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot, s_policy);
+                    if (!t.kind) bulk_load_hint(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot, s_policy);
+                } else {
+                    bulk_load(dst, p0 + arow, a_bytes, sft_full0 + 8 * slot);
+                    if (!t.kind) bulk_load(dst + Cfg::SFT_A, (sh ? sfSU : sfU) + arow, a_bytes, sft_full0 + 8 * slot);
+                }
                 bulk_load(dst + 2 * Cfg::SFT_A, (t.kind ? Hs : Xs) + (size_t)t.row0 * nbk, b_bytes, sft_full0 + 8 * slot);
             }
         }
